@@ -1,0 +1,343 @@
+#!/usr/bin/env python
+"""Benchmark: MobileNetV1-int8 images/s on N B200s (one process per GPU).
+
+  python bench.py --gpus 1 --steps 20 --warmup 5
+  python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+  python bench.py --impl reference          # the reference's own C code on the host cores
+
+A step is one pass of the 29-call layer stack over one batch of synthetic images (1024 per GPU;
+weak scaling: every GPU keeps 1024 images as N grows, nothing is exchanged but the final logits
+gather). `value` is measured with the batch already resident in HBM; `e2e` is the same metric
+through the C ABI with host buffers (pinned input copied in, logits copied out, every step).
+Prints ONE JSON line on rank 0.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+import __graft_entry__ as entry  # noqa: E402
+
+WORKLOAD = "MobileNetV1-1.0 int8, 224x224x3 HWC uint8 inputs U[0,255], int8 weights U[-16,15], " \
+           "32-bit BN k U[1,64] lambda U[-32768,32767], out_shift ceil(log2 K)+11"
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
+        "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 6:
+                continue
+            try:
+                sm.append(float(f[0])); mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ---- CPU arm -----------------------------------------------------------------------------------
+def cpu_chain_seconds(ref, params, x, bits=32):
+    """Runs the layer chain on the compiled reference; returns (seconds in reference code incl.
+    per-image buffer copies, seconds of HWC->CHW layout glue that is not reference code)."""
+    total, glue = 0.0, 0.0
+    cur = x
+    for p in params:
+        if p["op"] == "conv":
+            cur = ref.conv(bits, cur, p["w"], p["k"], p["lam"], out_shift=p["out_shift"],
+                           out_hw=(p["Ho"], p["Wo"]), kernel=(3, 3), pads=(1, 1, 1, 1),
+                           strides=(p["stride"], p["stride"]), variant="HoWo")
+        elif p["op"] == "depthwise":
+            cur = ref.depthwise(bits, cur, p["w"], p["k"], p["lam"], out_shift=p["out_shift"],
+                                out_hw=(p["Ho"], p["Wo"]), kernel=(3, 3), pads=(1, 1, 1, 1),
+                                strides=(p["stride"], p["stride"]), in_is_hwc=True)
+            glue += ref.last_glue_seconds
+        elif p["op"] == "pointwise":
+            cur = ref.pointwise(bits, cur, p["w"], p["k"], p["lam"], out_shift=p["out_shift"])
+        elif p["op"] == "avgpool":
+            cur = ref.avgpool(bits, cur, out_hw=(1, 1), kernel=(p["H"], p["W"]), pads=(0, 0, 0, 0),
+                              strides=(p["H"], p["W"]))
+        elif p["op"] == "linear32":
+            cur = ref.linear_out_32(np.ascontiguousarray(cur.reshape(cur.shape[0], -1)), p["w"])
+        total += ref.last_seconds
+    return total, glue, cur
+
+
+def port_chain_seconds(cpu, params, x, bits=32):
+    """The same chain on the C restatement (no harness timers: wall clock)."""
+    class Timed:
+        last_glue_seconds = 0.0
+        last_seconds = 0.0
+
+        def __getattr__(self, name):
+            fn = getattr(cpu, name)
+
+            def call(*a, **kw):
+                kw.pop("variant", None)
+                t0 = time.time()
+                r = fn(*a, **kw)
+                self.last_seconds = time.time() - t0
+                return r
+            return call
+    return cpu_chain_seconds(Timed(), params, x, bits)
+
+
+def cpu_baseline(params, wl, budget_s=12.0, max_images=1024):
+    """Times the reference's own C implementation (oracle/_ref) on the host cores, one worker
+    thread per core over the images of a bounded sample. Falls back to the C restatement when the
+    compiled reference is not present on this machine."""
+    from oracle import bindings
+    cores = os.cpu_count() or 1
+    if bindings.have_reference(32):
+        ref = bindings.CompiledReference(32, arena_mb=1024, threads=cores)
+        kind, build = "reference", ref.build_info()
+        x = wl.mobilenet_input(7, min(cores, max_images))
+        t, glue, _ = cpu_chain_seconds(ref, params, x)
+        per_round = max(t, 1e-3)
+        rounds = int(max(1, min(budget_s / per_round, max_images / x.shape[0])))
+        n = x.shape[0] * rounds
+        if rounds > 1:
+            x = wl.mobilenet_input(7, n)
+            t, glue, _ = cpu_chain_seconds(ref, params, x)
+        return {"value": n / t, "unit": "images/s", "cores": cores, "kind": kind,
+                "sample": "%d images through all 29 reference calls, %d threads over images, "
+                          "NUM_CORES=1 per image; %.2f s of which %.2f s HWC->CHW glue outside the "
+                          "reference; %s" % (n, cores, t, glue, build)}, (n, t)
+    cpu = bindings.Restatement()          # OpenMP over images and pixels; only a last resort
+    x = wl.mobilenet_input(7, 4)
+    t, _, _ = port_chain_seconds(cpu, params, x)
+    return {"value": 4 / t, "unit": "images/s", "cores": cores, "kind": "port",
+            "sample": "4 images through the C restatement in %.2f s (compiled reference not built "
+                      "here)" % t}, (4, t)
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    pkg = entry.load_package()
+    wl = pkg.workloads
+    params = wl.mobilenet_params(seed=4, bits=32, shift_bias=11)
+    n_img, secs = 0, 0.0
+    base = None
+    for i in range(args.warmup + args.steps):
+        base, (n, t) = cpu_baseline(params, wl, budget_s=4.0, max_images=256)
+        if i >= args.warmup:
+            n_img += n
+            secs += t
+    value = n_img / secs
+    base["value"] = value
+    line = {"impl": "reference", "metric": "MobileNetV1-int8 images/s", "value": value, "unit": "images/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": 1000.0 * secs / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "u8*s8->s32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "per_step": "bounded sample of <=256 images on the host cores"},
+            "cpu_baseline": base,
+            "e2e": {"value": value, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+# ---- GPU arm -----------------------------------------------------------------------------------
+def run_gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: this framework has no CPU path "
+                         "(use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    pkg = entry.load_package()
+    api, wl = pkg.api, pkg.workloads
+    api.set_device(local)
+    api.set_stream(None)
+
+    B = args.batch
+    params = wl.mobilenet_params(seed=4, bits=32, shift_bias=11)
+    net = api.build_mobilenet_v1(params, bits=32, max_batch=B, micro_batch=args.micro)
+    x_host = torch.from_numpy(wl.mobilenet_input(100 + rank, B)).pin_memory()
+    x_dev = x_host.cuda()
+    logits = torch.zeros((B, 1000), dtype=torch.int32, device="cuda")
+    logits_host = torch.zeros((B, 1000), dtype=torch.int32).pin_memory()
+    gathered = torch.zeros((world * B, 1000), dtype=torch.int32, device="cuda") if world > 1 else None
+
+    def step():
+        net.run(x_dev, logits, B)
+        if world > 1:   # the only exchange of the whole path: the final logits gather
+            dist.all_gather_into_tensor(gathered, logits)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = api.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    for _ in range(args.steps):
+        step()
+    ev1.record()
+    barrier()
+    ms = ev0.elapsed_time(ev1)
+    launches = api.launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+
+    # end to end through the C ABI with host buffers
+    for _ in range(2):
+        net.run(x_host, logits_host, B)
+    barrier()
+    ev0.record()
+    for _ in range(args.steps):
+        net.run(x_host, logits_host, B)
+    ev1.record()
+    barrier()
+    ms_e2e = ev0.elapsed_time(ev1)
+
+    # per-layer times (events between layer calls), averaged over a few runs
+    layer_ms = np.zeros(net.num_layers())
+    reps = max(3, min(args.steps, 10))
+    for _ in range(reps):
+        layer_ms += np.array(net.run_timed(x_dev, logits, B))
+    layer_ms /= reps
+    assert api.device_status() == 0, "a bounded wait inside a tensor-core kernel ran out"
+
+    if world > 1:
+        t = torch.tensor([ms, ms_e2e], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, ms_e2e = t.tolist()
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    hbm_peak, peak_kind = peaks()
+    rows = wl.mobilenet_ops_bytes()
+    per_layer = []
+    by_kernel = {}
+    for L, r, t_ms in zip(params, rows, layer_ms):
+        gb = r["bytes"] * B / 1e9
+        gop = r["ops"] * B / 1e9
+        per_layer.append({"layer": L["name"], "ms": round(float(t_ms), 4),
+                          "GOPs": round(gop / (t_ms / 1e3), 1), "GBs": round(gb / (t_ms / 1e3), 1),
+                          "hbm_frac": round(gb / (t_ms / 1e3) / hbm_peak, 3)})
+        kname = {"conv": "conv_generic_kernel", "depthwise": "depthwise_hwc4_kernel",
+                 "pointwise": "igemm_tc_kernel", "avgpool": "avgpool_kernel",
+                 "linear32": "igemm_tc_kernel"}[L["op"]]
+        k = by_kernel.setdefault(kname, {"ms": 0.0, "bytes": 0.0, "launches": 0})
+        k["ms"] += float(t_ms); k["bytes"] += r["bytes"] * B; k["launches"] += 1
+    top = max(by_kernel, key=lambda n: by_kernel[n]["ms"])
+    tk = by_kernel[top]
+    achieved = tk["bytes"] / 1e9 / (tk["ms"] / 1e3)
+    traffic = None
+    tpath = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(tpath):
+        traffic = json.load(open(tpath)).get(top)
+    roofline = {"bound": "hbm", "kernel": top, "achieved": round(achieved, 1), "peak": hbm_peak,
+                "unit": "GB/s", "frac": round(achieved / hbm_peak, 4), "traffic": traffic,
+                "peak_source": "of %s" % peak_kind,
+                "launches_per_step": tk["launches"], "avg_launch_ms": round(tk["ms"] / tk["launches"], 4),
+                "algorithmic_bytes_per_launch": int(tk["bytes"] / tk["launches"]),
+                "share_of_step": round(tk["ms"] / float(layer_ms.sum()), 3)}
+
+    images = B * world * args.steps
+    value = images / (ms / 1e3)
+    line = {"metric": "MobileNetV1-int8 images/s", "value": round(value, 1), "unit": "images/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "u8*s8->s32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "per_gpu_batch": B, "global_batch": B * world,
+                       "micro_batch": args.micro, "parallelism": "batch-sharded x%d, logits all-gather" % world,
+                       "l2": "inputs larger than L2 (154 MB of images per step)"},
+            "clocks": clocks,
+            "e2e": {"value": round(images / (ms_e2e / 1e3), 1), "unit": "images/s",
+                    "h2d_bytes_per_step": int(x_host.numel()), "d2h_bytes_per_step": int(logits_host.numel() * 4)},
+            "gpu_launches": int(launches),
+            "roofline": roofline,
+            "per_layer": per_layer}
+    if world == 1 and not args.no_cpu:
+        line["cpu_baseline"], _ = cpu_baseline(params, wl)
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=1024, help="images per GPU")
+    ap.add_argument("--micro", type=int, default=0, help="images per pass through the stack (0 = all)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,208 @@
+/*
+ * pulpnn_b200.h -- C ABI of the B200 (sm_100a) implementation of the PULP-NN
+ * 8-bit HWC inference kernels.
+ *
+ * Every kernel entry point keeps the name, the parameter list and the
+ * arithmetic of the reference prototype it replaces; the citation beside each
+ * one is the line of 32bit/include/pulp_nn_kernels.h (the 64bit/ header is
+ * identical except that k/lambda are int64_t). The reference ships two source
+ * trees that export the same names with different batch-norm widths; here one
+ * library exports both, suffixed _bn32 / _bn64 (libpulpnn_b200.so), and two
+ * thin libraries (libpulpnn_b200_32.so, libpulpnn_b200_64.so, see
+ * pulpnn_b200_dropin.h) export the unsuffixed reference names.
+ *
+ * Calling convention on the GPU
+ *  - ONE host thread makes the call once; the grid plays the role of the
+ *    reference's cluster of cores. Work is enqueued on the calling thread's
+ *    current stream (pulpnn_set_stream) and the call returns without waiting,
+ *    unless a buffer is in host memory (see below).
+ *  - Pointers may be device pointers (the fast path) or ordinary host
+ *    pointers. Host buffers are staged through device memory owned by the
+ *    library and the call then returns only after the results are back in the
+ *    caller's buffers.
+ *  - The reference processes one image per call. pulpnn_set_batch(n) makes
+ *    every activation pointer address n images stored back to back; weights
+ *    and batch-norm parameters are shared by the batch.
+ *  - Scratch arguments of the reference (pIm2ColBuffer, bufferC, bufferB) are
+ *    accepted and ignored; they may be NULL.
+ *  - The entry points return void like the reference. A call whose arguments
+ *    are invalid or outside the supported domain enqueues nothing and records
+ *    an error for the calling thread (pulpnn_last_error). There is no CPU
+ *    fallback of any kind.
+ */
+#ifndef PULPNN_B200_H
+#define PULPNN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status ------------------------------------------------------------- */
+enum {
+  PULPNN_OK = 0,
+  PULPNN_ERR_INVALID_ARG = 1,   /* NULL pointer, zero dimension, shift out of range ...     */
+  PULPNN_ERR_UNSUPPORTED = 2,   /* outside the domain where the reference is well defined   */
+  PULPNN_ERR_CUDA = 3,          /* a CUDA runtime/driver call failed                        */
+  PULPNN_ERR_NO_DEVICE = 4,     /* no usable GPU: the library never computes on the CPU     */
+  PULPNN_ERR_DEVICE_WAIT = 5    /* a bounded wait inside a kernel ran out (see status word) */
+};
+
+/* ---- per-thread context -------------------------------------------------- */
+int  pulpnn_set_device(int device);          /* also creates the context; returns a status   */
+int  pulpnn_set_stream(void *cuda_stream);   /* cudaStream_t; NULL = the default stream       */
+int  pulpnn_set_batch(int n_images);         /* n >= 1; sticky until changed                  */
+int  pulpnn_get_batch(void);
+int  pulpnn_synchronize(void);               /* waits for the stream; returns a status        */
+int  pulpnn_last_error(void);
+const char *pulpnn_last_error_message(void);
+void pulpnn_clear_error(void);
+/* kernels launched by this library since it was loaded (all threads) */
+unsigned long long pulpnn_launch_count(void);
+/* Reads and clears the device-side status word: 0 = every bounded wait in the
+ * tensor-core kernels completed. Synchronises the stream first. */
+int  pulpnn_device_status(void);
+
+/* Tuning / test switches (value 0 or 1 unless stated). */
+enum {
+  PULPNN_OPT_FORCE_GENERIC = 1,   /* route contractions to the generic CUDA-core kernel      */
+  PULPNN_OPT_MAXPOOL_CLOBBER = 2, /* also reproduce the reference's overwrite of Im_in       */
+  PULPNN_OPT_SPLIT_K = 3          /* 0 = choose automatically, n > 0 = force n K-slices      */
+};
+int  pulpnn_set_option(int option, int value);
+int  pulpnn_get_option(int option);
+
+/* ---- kernel entry points -------------------------------------------------- */
+/* shared parameter list of the convolution family (pulp_nn_kernels.h:56-82) */
+#define PULPNN_CONV_PARAMS(BN_T)                                                              \
+  const uint8_t *pInBuffer, uint8_t *pIm2ColBuffer, const int8_t *bias, uint8_t *pOutBuffer,  \
+  const int8_t *pWeight, BN_T *k, BN_T *lambda, const uint16_t out_mult,                      \
+  const uint16_t out_shift, const uint16_t dim_in_x, const uint16_t dim_in_y,                 \
+  const uint16_t ch_in, const uint16_t dim_out_x, const uint16_t dim_out_y,                   \
+  const uint16_t ch_out, const uint16_t dim_kernel_x, const uint16_t dim_kernel_y,            \
+  const uint16_t padding_y_top, const uint16_t padding_y_bottom,                              \
+  const uint16_t padding_x_left, const uint16_t padding_x_right, const uint16_t stride_x,     \
+  const uint16_t stride_y, int flag_relu, int flag_batch_norm
+
+/* parameter list of the depthwise family (pulp_nn_kernels.h:282-309) */
+#define PULPNN_DW_PARAMS(BN_T)                                                                \
+  const uint8_t *Im_in, uint8_t *bufferC, const int8_t *bias, uint8_t *Im_out,                \
+  const int8_t *wt, uint8_t *bufferB, BN_T *k, BN_T *lambda, uint16_t out_mult,               \
+  uint16_t out_shift, const uint16_t dim_im_in_x, const uint16_t dim_im_in_y,                 \
+  const uint16_t ch_im_in, const uint16_t dim_im_out_x, const uint16_t dim_im_out_y,          \
+  const uint16_t ch_im_out, const uint16_t dim_kernel_x, const uint16_t dim_kernel_y,         \
+  const uint16_t padding_y_top, const uint16_t padding_y_bottom,                              \
+  const uint16_t padding_x_left, const uint16_t padding_x_right, const uint16_t stride_x,     \
+  const uint16_t stride_y, int8_t FLAG_RELU, int8_t FLAG_BATCH_NORM
+
+/* parameter list of the pooling pair (pulp_nn_kernels.h:264-280 and :33-53) */
+#define PULPNN_POOL_GEOMETRY                                                                  \
+  uint16_t dim_im_in_x, uint16_t dim_im_in_y, uint16_t ch_im_in, uint16_t dim_im_out_x,       \
+  uint16_t dim_im_out_y, uint16_t dim_kernel_x, uint16_t dim_kernel_y, uint16_t padding_t,    \
+  uint16_t padding_b, uint16_t padding_l, uint16_t padding_r, uint16_t stride_x,              \
+  uint16_t stride_y
+
+/*
+ * One tree of entry points. SFX is appended to every reference name, BN_T is
+ * the batch-norm parameter type of that tree.
+ *
+ *  pulp_nn_conv_Ho_parallel         pulp_nn_kernels.h:56    zero-padded convolution, HWC in/out,
+ *  pulp_nn_conv_HoWo_parallel       pulp_nn_kernels.h:112   weights [ch_out][ky][kx][ch_in]; the two
+ *                                                           differ in the reference only in how cores
+ *                                                           split the rows, so they share one kernel
+ *  pulp_nn_pointwise_HoWo_parallel  pulp_nn_kernels.h:140   1x1 convolution; kernel/pad/stride
+ *                                                           arguments are ignored as in the reference
+ *  pulp_nn_depthwise_generic        pulp_nn_kernels.h:282   CHW in, HWC out
+ *  pulp_nn_linear                   pulp_nn_kernels.h:224   uint8 output, requantised
+ *  pulp_nn_linear_out_32            pulp_nn_kernels.h:239   raw int32 output; bias is read as int32[]
+ *  pulp_nn_maxpool                  pulp_nn_kernels.h:264   Im_in is left intact unless
+ *                                                           PULPNN_OPT_MAXPOOL_CLOBBER is set
+ *  pulp_nn_avgpool                  pulp_nn_kernels.h:33    lambda/out_add have the tree's width
+ *  pulp_nn_add                      pulp_nn_kernels.h:21
+ *
+ *  pulpnn_depthwise_hwc             extension: pulp_nn_depthwise_generic arithmetic on HWC input
+ *                                   (what every producer in this API emits); no reference counterpart
+ */
+#define PULPNN_DECLARE_TREE(SFX, BN_T)                                                        \
+  void pulp_nn_conv_Ho_parallel##SFX(PULPNN_CONV_PARAMS(BN_T));                               \
+  void pulp_nn_conv_HoWo_parallel##SFX(PULPNN_CONV_PARAMS(BN_T));                             \
+  void pulp_nn_pointwise_HoWo_parallel##SFX(PULPNN_CONV_PARAMS(BN_T));                        \
+  void pulp_nn_depthwise_generic##SFX(PULPNN_DW_PARAMS(BN_T));                                \
+  void pulpnn_depthwise_hwc##SFX(PULPNN_DW_PARAMS(BN_T));                                     \
+  void pulp_nn_linear##SFX(uint8_t *pInBuffer, int8_t *bias, uint8_t *pOutBuffer,             \
+                           int8_t *pWeights, BN_T *k, BN_T *lambda, uint16_t out_mult,        \
+                           int8_t out_shift, uint16_t dim_vec, uint16_t num_o_neurons,        \
+                           int flag_relu, int flag_batch_norm);                               \
+  void pulp_nn_linear_out_32##SFX(uint8_t *pInBuffer, int8_t *bias, int32_t *pOutBuffer,      \
+                                  int8_t *pWeights, uint16_t dim_vec, uint16_t num_o_neurons);\
+  void pulp_nn_maxpool##SFX(uint8_t *Im_in, uint8_t *Im_out, PULPNN_POOL_GEOMETRY);           \
+  void pulp_nn_avgpool##SFX(uint8_t *Im_in, uint8_t *Im_out, BN_T lambda, uint16_t out_shift, \
+                            BN_T out_add, PULPNN_POOL_GEOMETRY, int flag_requant);            \
+  void pulp_nn_add##SFX(uint8_t *Im_in_1, uint8_t *Im_in_2, uint8_t *Im_out,                  \
+                        uint16_t out_mult1, uint16_t out_mult2, uint16_t out_shift,           \
+                        uint16_t dim_im_in_h, uint16_t dim_im_in_w, uint16_t ch_im_in);
+
+PULPNN_DECLARE_TREE(_bn32, int32_t)
+PULPNN_DECLARE_TREE(_bn64, int64_t)
+
+/* ---- sequential network runner --------------------------------------------
+ * The reference is a kernel library; its user chains the calls. This runner is
+ * that chain for one GPU: layers are appended in order, parameters are copied
+ * to the device once, and run() pushes a batch through every layer with
+ * activations ping-ponging between two device buffers owned by the network.
+ * Depthwise layers use the HWC-input kernel, so no layout change is needed
+ * between layers. Different GPUs run different slices of the batch; nothing is
+ * exchanged between them.
+ */
+typedef struct pulpnn_net pulpnn_net_t;
+
+enum {
+  PULPNN_LAYER_CONV = 0,        /* pulp_nn_conv_Ho_parallel                       */
+  PULPNN_LAYER_POINTWISE = 1,   /* pulp_nn_pointwise_HoWo_parallel                */
+  PULPNN_LAYER_DEPTHWISE = 2,   /* pulpnn_depthwise_hwc                            */
+  PULPNN_LAYER_AVGPOOL = 3,     /* pulp_nn_avgpool, flag_requant = 0              */
+  PULPNN_LAYER_MAXPOOL = 4,     /* pulp_nn_maxpool                                */
+  PULPNN_LAYER_LINEAR_OUT_32 = 5/* pulp_nn_linear_out_32 (must be the last layer) */
+};
+
+typedef struct {
+  int type;                       /* PULPNN_LAYER_*                                     */
+  int dim_in_x, dim_in_y, ch_in;
+  int dim_out_x, dim_out_y, ch_out;
+  int dim_kernel_x, dim_kernel_y;
+  int padding_y_top, padding_y_bottom, padding_x_left, padding_x_right;
+  int stride_x, stride_y;
+  int out_mult, out_shift, flag_relu, flag_batch_norm;
+  const int8_t *weights;          /* host or device memory; copied at add time          */
+  const int8_t *bias;             /* may be NULL (int32 words for LINEAR_OUT_32)        */
+  const void *k, *lambda;         /* ch_out values of the network's batch-norm width    */
+} pulpnn_layer_desc_t;
+
+pulpnn_net_t *pulpnn_net_create(int bn_bits, int max_batch);
+int  pulpnn_net_add_layer(pulpnn_net_t *net, const pulpnn_layer_desc_t *desc);
+/* Freezes the layer list and allocates the activation buffers. micro_batch = 0
+ * lets the library choose how many images travel through the stack together. */
+int  pulpnn_net_finalize(pulpnn_net_t *net, int micro_batch);
+/* input: n_images x (first layer's input) bytes; output: n_images x (last
+ * layer's output). Either may be host or device memory. Enqueues on the calling
+ * thread's stream; synchronises only if a host buffer is involved. */
+int  pulpnn_net_run(pulpnn_net_t *net, const uint8_t *input, void *output, int n_images);
+/* Test hook: run the first n_layers layers only and copy that layer's output. */
+int  pulpnn_net_run_prefix(pulpnn_net_t *net, const uint8_t *input, void *output, int n_images,
+                           int n_layers);
+/* Measurement hook: like pulpnn_net_run on device buffers, with a CUDA event recorded on the
+ * stream between consecutive layer calls; layer_ms[l] receives the milliseconds layer l took
+ * (summed over micro-batches). Synchronises. */
+int  pulpnn_net_run_timed(pulpnn_net_t *net, const uint8_t *input, void *output, int n_images,
+                          float *layer_ms);
+int  pulpnn_net_num_layers(const pulpnn_net_t *net);
+size_t pulpnn_net_layer_output_bytes(const pulpnn_net_t *net, int layer);   /* per image */
+unsigned long long pulpnn_net_launches_per_run(const pulpnn_net_t *net, int n_images);
+void pulpnn_net_destroy(pulpnn_net_t *net);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PULPNN_B200_H */

@@ -1,0 +1,599 @@
+// igemm_tc.cu -- u8 x s8 -> s32 GEMM on the sm_100a tensor cores with the requantisation fused
+// into the epilogue. It carries pointwise convolution and the fully connected layers:
+//
+//     D[m][n] = bias[n] + sum_k A[m][k] * W[n][k]      A: activations, [M][K] uint8, K contiguous
+//                                                       W: weights,     [N][K] int8,  K contiguous
+//
+// (the im2col matrix of a 1x1 convolution is the HWC activation tensor itself, and the reference
+// keeps weights as [ch_out][K], 32bit/src/pulp_nn_matmul.c:55-59, so both operands are K-major
+// exactly as they lie in memory).
+//
+// Structure of one CTA (192 threads, persistent over work units = (m-tile, n-tile, k-slice)):
+//   warp 0, one lane   TMA producer: 128 x 128-byte tile of A and BN x 128-byte tile of W per
+//                      stage, 128-byte swizzle, completion on an mbarrier (no multicast)
+//   warp 1, one lane   issues tcgen05.mma.kind::i8 (M=128, N=BN, K=32 per instruction), operands
+//                      from shared-memory descriptors, accumulator in tensor memory; commits free
+//                      the stage and publish the accumulator
+//   warps 2..5         epilogue: tcgen05.ld the accumulator (lane = output row), add bias,
+//                      requantise with per-channel k/lambda held in shared memory, pack to bytes
+//                      and store 16 bytes at a time into the HWC output
+// Two accumulators live in tensor memory so that the epilogue of one tile overlaps the MMAs of
+// the next. Integer accumulation is associative, so splitting K over several CTAs (used when a
+// problem has too few tiles to fill the GPU) gives bit-identical sums; partial sums then go to a
+// scratch buffer and a second kernel adds them and requantises.
+//
+// Every wait on an mbarrier is bounded: after about a second the waiting thread raises a flag in
+// shared memory, records a code in a global status word and all roles fall through to the common
+// exit, which waits (bounded) for outstanding TMA writes and frees the tensor memory.
+#include <cuda.h>
+#include <cstdio>
+#include <mutex>
+
+#include "internal.cuh"
+
+namespace pulpnn {
+
+namespace {
+
+constexpr int BM = 128;            // rows per tile = TMEM lanes
+constexpr int BK = 128;            // bytes of K per stage = one 128-byte swizzle atom
+constexpr int UMMA_K = 32;         // K per tcgen05.mma for 8-bit operands
+constexpr int NUM_THREADS = 192;
+constexpr unsigned long long WAIT_LIMIT_NS = 1000000000ull;
+
+// status codes (or-ed into the global status word)
+constexpr int ST_PRODUCER = 0x1, ST_MMA_FULL = 0x2, ST_MMA_TMEM = 0x4, ST_EPILOGUE = 0x8, ST_DRAIN = 0x10;
+
+// ---- PTX wrappers --------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p)
+{
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count)
+{
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t bytes)
+{
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar)
+{
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
+{
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns()
+{
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait. Returns false when the limit ran out or another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
+                                          int *status, int code)
+{
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_ns();
+  for (unsigned spin = 1;; spin++) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((spin & 255u) == 0) {
+      if (*abort_flag) return false;
+      if (global_ns() - t0 > WAIT_LIMIT_NS) {
+        *abort_flag = 1;
+        if (status) atomicOr(status, code);
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, uint64_t *bar, int x, int y)
+{
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_alloc(uint32_t *slot, uint32_t ncols)
+{
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(ncols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols)
+{
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t *bar)
+{
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+// D(tmem) (+)= A(smem) * B(smem)^T, u8 x s8 -> s32
+__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                        uint32_t accumulate)
+{
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_32(uint32_t taddr, uint32_t (&r)[32])
+{
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile stored with the 128-byte swizzle: rows are
+// 128 bytes apart, groups of 8 rows 1024 bytes apart (stride byte offset), descriptor version 1,
+// layout type 2 = SWIZZLE_128B. Addresses and offsets are encoded in 16-byte units.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr)
+{
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3ffffu) >> 4);          // start address
+  d |= (uint64_t)1 << 16;                            // leading byte offset (unused with swizzle)
+  d |= (uint64_t)(1024 >> 4) << 32;                  // stride byte offset
+  d |= (uint64_t)1 << 46;                            // version
+  d |= (uint64_t)2 << 61;                            // SWIZZLE_128B
+  return d;
+}
+// Instruction descriptor: D = s32 (2 at bit 4), A = unsigned 8-bit (0 at bit 7), B = signed 8-bit
+// (1 at bit 10), both K-major (bits 15, 16 clear), N/8 at bit 17, M/16 at bit 24.
+__host__ __device__ constexpr uint32_t idesc_u8s8(int n)
+{
+  return (2u << 4) | (0u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+__device__ __forceinline__ unsigned pack4_u8(int a, int b, int c, int d)
+{
+  return (unsigned)a | ((unsigned)b << 8) | ((unsigned)c << 16) | ((unsigned)d << 24);
+}
+
+// ---- kernel parameters ---------------------------------------------------------------------
+struct TcParams {
+  void *out;             // uint8 [M][N], int32 [M][N] (EPI_RAW32) or int32 partials [S][M][N]
+  Epilogue epi;
+  int M, N, K;
+  int m_tiles, n_tiles, k_slices, slabs_per_slice, total_slabs;
+  int vec_store;         // 1: rows of the output can be written with 16-byte stores
+  int *status;
+};
+
+template <int BN_TILE, int STAGES>
+struct SmemLayout {
+  static constexpr int A_BYTES = BM * BK;
+  static constexpr int B_BYTES = BN_TILE * BK;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int PARAM_BYTES = BN_TILE * 16;    // k and lambda, up to 8 bytes each; one copy per epilogue warp
+  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES + 4 * PARAM_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;   // barriers + slack for 1024-byte alignment
+};
+
+// MODE: the final epilogue; PARTIAL: store raw int32 partial sums instead (split-K)
+template <int MODE, int BN_TILE, int STAGES, bool PARTIAL>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                const TcParams g)
+{
+  using L = SmemLayout<BN_TILE, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t *params_all = smem + STAGES * L::STAGE_BYTES;
+  uint64_t *full_bar = reinterpret_cast<uint64_t *>(smem + L::BAR_OFFSET);
+  uint64_t *empty_bar = full_bar + STAGES;
+  uint64_t *tmem_full = empty_bar + STAGES;
+  uint64_t *tmem_empty = tmem_full + 2;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tmem_empty + 2);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr uint32_t TMEM_COLS = 2 * BN_TILE < 32 ? 32 : 2 * BN_TILE;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int b = 0; b < 2; b++) { mbar_init(&tmem_full[b], 1); mbar_init(&tmem_empty[b], 4); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int units = g.m_tiles * g.n_tiles * g.k_slices;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer --------------------------------------------
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0; int issued = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
+        const int nt = u % g.n_tiles, r = u / g.n_tiles;
+        const int mt = r % g.m_tiles, ks = r / g.m_tiles;
+        const int slab0 = ks * g.slabs_per_slice;
+        const int slab1 = min(slab0 + g.slabs_per_slice, g.total_slabs);
+        for (int s = slab0; s < slab1; s++) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, g.status, ST_PRODUCER)) { ok = false; break; }
+          uint8_t *a_dst = smem + stage * L::STAGE_BYTES;
+          mbar_arrive_expect_tx(&full_bar[stage], L::STAGE_BYTES);
+          tma_load_2d(a_dst, &map_a, &full_bar[stage], s * BK, mt * BM);
+          tma_load_2d(a_dst + L::A_BYTES, &map_b, &full_bar[stage], s * BK, nt * BN_TILE);
+          issued++;
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (*abort_flag) {
+        // something gave up: make sure no TMA write is still in flight into this CTA's memory
+        const int pending = issued < STAGES ? issued : STAGES;
+        for (int i = 0; i < pending; i++) {
+          int st = stage - 1 - i; uint32_t ph = phase;
+          if (st < 0) { st += STAGES; ph ^= 1; }
+          const unsigned long long t0 = global_ns();
+          while (!mbar_try_wait(&full_bar[st], ph)) {
+            if (global_ns() - t0 > WAIT_LIMIT_NS) { if (g.status) atomicOr(g.status, ST_DRAIN); break; }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ----------------------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = idesc_u8s8(BN_TILE);
+      int stage = 0; uint32_t phase = 0; int acc = 0; uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
+        const int r = u / g.n_tiles;
+        const int ks = r / g.m_tiles;
+        const int slab0 = ks * g.slabs_per_slice;
+        const int slab1 = min(slab0 + g.slabs_per_slice, g.total_slabs);
+        if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, g.status, ST_MMA_TMEM)) break;
+        tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN_TILE);
+        for (int s = slab0; s < slab1; s++) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, g.status, ST_MMA_FULL)) { ok = false; break; }
+          tcgen05_fence_after();
+          const uint32_t a_addr = smem_u32(smem + stage * L::STAGE_BYTES);
+          const uint64_t da = smem_desc_sw128(a_addr), db = smem_desc_sw128(a_addr + L::A_BYTES);
+          // bytes of this slab that lie inside K; the rest of the tile is zero-filled by TMA
+          const int kbytes = min(BK, g.K - s * BK);
+          const int n_mma = (kbytes + UMMA_K - 1) / UMMA_K;
+          for (int j = 0; j < n_mma; j++) {
+            // advancing K inside the swizzle atom = advancing the start address (16-byte units)
+            const uint64_t adv = (uint64_t)((j * UMMA_K) >> 4);
+            umma_i8(d_tmem, da + adv, db + adv, idesc, (s > slab0 || j > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);      // stage reusable once these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(&tmem_full[acc]);          // accumulator complete
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------ epilogue (warps 2..5) ------------------------------------
+    const int quad = warp & 3;                 // TMEM lanes 32*quad .. 32*quad+31
+    // each epilogue warp keeps its own copy of the per-channel parameters, so staging them needs
+    // no barrier between warps (a warp that gave up can never strand the others)
+    uint8_t *params = params_all + quad * L::PARAM_BYTES;
+    int acc = 0; uint32_t acc_phase = 0;
+    const Epilogue &e = g.epi;
+    int *p_bias = reinterpret_cast<int *>(params);                 // non-BN modes
+    int *p_k32 = reinterpret_cast<int *>(params);                  // EPI_BN32: k, lambda'
+    int *p_l32 = p_k32 + BN_TILE;
+    long long *p_k64 = reinterpret_cast<long long *>(params);      // EPI_BN64
+    long long *p_l64 = p_k64 + BN_TILE;
+    int staged_nt = -1;
+    for (int u = blockIdx.x; u < units; u += gridDim.x) {
+      const int nt = u % g.n_tiles, r = u / g.n_tiles;
+      const int mt = r % g.m_tiles, ks = r / g.m_tiles;
+      const int n0 = nt * BN_TILE;
+      if (!PARTIAL && nt != staged_nt) {
+        // per-channel parameters of this n-tile -> shared memory. The bias is folded into
+        // lambda: k*(acc+b)+lambda == k*acc + (k*b+lambda) in wrap-around arithmetic.
+        __syncwarp();
+        for (int i = lane; i < BN_TILE; i += 32) {
+          const int n = n0 + i;
+          const bool v = n < g.N;
+          if (MODE == EPI_BN32) {
+            const int k = v ? __ldg(reinterpret_cast<const int *>(e.k) + n) : 0;
+            const int l = v ? __ldg(reinterpret_cast<const int *>(e.lambda) + n) : 0;
+            const int b = (v && e.bias) ? (int)__ldg(reinterpret_cast<const int8_t *>(e.bias) + n) : 0;
+            p_k32[i] = k;
+            p_l32[i] = (int)((unsigned)k * (unsigned)b + (unsigned)l);
+          } else if (MODE == EPI_BN64) {
+            const long long k = v ? __ldg(reinterpret_cast<const long long *>(e.k) + n) : 0;
+            const long long l = v ? __ldg(reinterpret_cast<const long long *>(e.lambda) + n) : 0;
+            const long long b = (v && e.bias) ? (long long)__ldg(reinterpret_cast<const int8_t *>(e.bias) + n) : 0;
+            p_k64[i] = k;
+            p_l64[i] = (long long)((unsigned long long)k * (unsigned long long)b + (unsigned long long)l);
+          } else if (MODE == EPI_RAW32) {
+            p_bias[i] = (v && e.bias) ? __ldg(reinterpret_cast<const int *>(e.bias) + n) : 0;
+          } else {
+            p_bias[i] = (v && e.bias) ? (int)__ldg(reinterpret_cast<const int8_t *>(e.bias) + n) : 0;
+          }
+        }
+        __syncwarp();
+        staged_nt = nt;
+      }
+      if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag, g.status, ST_EPILOGUE)) break;
+      tcgen05_fence_after();
+      const int m = mt * BM + quad * 32 + lane;
+      const bool row_ok = m < g.M;
+      const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN_TILE);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN_TILE; c0 += 32) {
+        if (n0 + c0 >= g.N) break;             // uniform across the warp
+        uint32_t v[32];
+        tmem_ld_32(t_row + (uint32_t)c0, v);
+        tmem_wait_ld();
+        if (PARTIAL || MODE == EPI_RAW32) {
+          int *orow = reinterpret_cast<int *>(g.out) +
+                      ((size_t)(PARTIAL ? ks : 0) * g.M + (size_t)(row_ok ? m : 0)) * g.N + n0 + c0;
+          if (row_ok) {
+            if (g.vec_store) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 4) {
+                if (n0 + c0 + i < g.N) {
+                  int4 o;
+                  o.x = (int)v[i]; o.y = (int)v[i + 1]; o.z = (int)v[i + 2]; o.w = (int)v[i + 3];
+                  if (!PARTIAL) { o.x += p_bias[c0 + i]; o.y += p_bias[c0 + i + 1]; o.z += p_bias[c0 + i + 2]; o.w += p_bias[c0 + i + 3]; }
+                  *reinterpret_cast<int4 *>(orow + i) = o;
+                }
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; i++)
+                if (n0 + c0 + i < g.N) orow[i] = (int)v[i] + (PARTIAL ? 0 : p_bias[c0 + i]);
+            }
+          }
+        } else {
+          unsigned w[8];
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            int q[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+              const int a = (int)v[i + j];
+              if (MODE == EPI_BN32)
+                q[j] = clip_u8((int)((unsigned)p_k32[c0 + i + j] * (unsigned)a + (unsigned)p_l32[c0 + i + j]) >> e.shift);
+              else if (MODE == EPI_BN64)
+                q[j] = clip_u8((int)((long long)((unsigned long long)p_k64[c0 + i + j] * (unsigned long long)(long long)a +
+                                                 (unsigned long long)p_l64[c0 + i + j]) >> e.shift));
+              else if (MODE == EPI_MULT)
+                q[j] = clip_u8((int)(short)((int)((unsigned)e.out_mult * (unsigned)(a + p_bias[c0 + i + j])) >> e.shift));
+              else
+                q[j] = clip_u8((a + p_bias[c0 + i + j]) >> e.shift);
+            }
+            w[i >> 2] = pack4_u8(q[0], q[1], q[2], q[3]);
+          }
+          if (row_ok) {
+            uint8_t *orow = reinterpret_cast<uint8_t *>(g.out) + (size_t)m * g.N + n0 + c0;
+            if (g.vec_store) {
+              if (n0 + c0 < g.N) *reinterpret_cast<uint4 *>(orow) = make_uint4(w[0], w[1], w[2], w[3]);
+              if (n0 + c0 + 16 < g.N) *reinterpret_cast<uint4 *>(orow + 16) = make_uint4(w[4], w[5], w[6], w[7]);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; i++)
+                if (n0 + c0 + i < g.N) orow[i] = (uint8_t)(w[i >> 2] >> (8 * (i & 3)));
+            }
+          }
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---- split-K reduction: sums the int32 partials, adds the bias and requantises ---------------
+template <int MODE>
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const int *partials, void *out, Epilogue e,
+                                                            int M, int N, int S)
+{
+  const size_t total = (size_t)M * N;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int n = (int)(i % N);
+    int acc = 0;
+    for (int s = 0; s < S; s++) acc += __ldg(partials + (size_t)s * total + i);
+    if (MODE == EPI_RAW32) {
+      if (e.bias) acc += __ldg(reinterpret_cast<const int *>(e.bias) + n);
+      reinterpret_cast<int *>(out)[i] = acc;
+    } else {
+      if (e.bias) acc += (int)__ldg(reinterpret_cast<const int8_t *>(e.bias) + n);
+      reinterpret_cast<uint8_t *>(out)[i] = (uint8_t)requant<MODE>(acc, n, e);
+    }
+  }
+}
+
+// ---- host side -------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn()
+{
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// [rows][K] byte matrix, K contiguous; box = 128 bytes of K x box_rows rows, 128-byte swizzle.
+// Elements outside the matrix read as zero.
+bool make_map(CUtensorMap *map, const void *base, int rows, int K, int box_rows)
+{
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) { set_error(PULPNN_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver"); return false; }
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)K};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { set_error(PULPNN_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r); return false; }
+  return true;
+}
+
+template <int MODE, int BN_TILE, int STAGES, bool PARTIAL>
+bool launch_cfg(Context &c, const CUtensorMap &ma, const CUtensorMap &mb, const TcParams &g, int grid)
+{
+  using L = SmemLayout<BN_TILE, STAGES>;
+  auto kern = igemm_tc_kernel<MODE, BN_TILE, STAGES, PARTIAL>;
+  static bool attr_set = false;     // per instantiation
+  if (!attr_set) {
+    if (!cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL),
+                 "cudaFuncSetAttribute(igemm_tc)"))
+      return false;
+    attr_set = true;
+  }
+  kern<<<grid, NUM_THREADS, L::TOTAL, c.stream>>>(ma, mb, g);
+  count_launch();
+  return cuda_ok(cudaGetLastError(), "igemm_tc launch");
+}
+
+template <int MODE, bool PARTIAL>
+bool launch_bn(Context &c, const CUtensorMap &ma, const CUtensorMap &mb, const TcParams &g, int bn, int grid)
+{
+  // stage counts keep every configuration above half of an SM's shared memory, so exactly one
+  // CTA (and its 2*BN tensor-memory columns) lives on an SM
+  if (bn == 64)  return launch_cfg<MODE, 64, 6, PARTIAL>(c, ma, mb, g, grid);
+  if (bn == 128) return launch_cfg<MODE, 128, 5, PARTIAL>(c, ma, mb, g, grid);
+  return launch_cfg<MODE, 256, 4, PARTIAL>(c, ma, mb, g, grid);
+}
+
+bool launch_final(Context &c, const CUtensorMap &ma, const CUtensorMap &mb, const TcParams &g, int bn, int grid)
+{
+  switch (g.epi.mode) {
+    case EPI_NONE: return launch_bn<EPI_NONE, false>(c, ma, mb, g, bn, grid);
+    case EPI_MULT: return launch_bn<EPI_MULT, false>(c, ma, mb, g, bn, grid);
+    case EPI_BN32: return launch_bn<EPI_BN32, false>(c, ma, mb, g, bn, grid);
+    case EPI_BN64: return launch_bn<EPI_BN64, false>(c, ma, mb, g, bn, grid);
+    default:       return launch_bn<EPI_RAW32, false>(c, ma, mb, g, bn, grid);
+  }
+}
+
+}  // namespace
+
+bool igemm_tc_supported(const Context &c, const ConvProblem &p)
+{
+  (void)c;
+  if (p.ky != 1 || p.kx != 1 || p.sy != 1 || p.sx != 1 || p.pt != 0 || p.pl != 0) return false;
+  if (p.H != p.Ho || p.W != p.Wo) return false;
+  if (p.Cin < 16 || p.Cin % 16 != 0) return false;      // TMA: row pitch must be a multiple of 16 bytes
+  if ((reinterpret_cast<uintptr_t>(p.in) & 15) || (reinterpret_cast<uintptr_t>(p.w) & 15)) return false;
+  const long long M = (long long)p.B * p.Ho * p.Wo;
+  if (M > 0x7fffffffLL) return false;
+  return true;
+}
+
+bool launch_igemm_tc(Context &c, const ConvProblem &p)
+{
+  TcParams g;
+  g.M = p.B * p.Ho * p.Wo; g.N = p.Cout; g.K = p.Cin;
+  g.epi = p.epi;
+  const int bn = g.N <= 64 ? 64 : (g.N <= 128 ? 128 : 256);
+  g.m_tiles = (g.M + BM - 1) / BM;
+  g.n_tiles = (g.N + bn - 1) / bn;
+  g.total_slabs = (g.K + BK - 1) / BK;
+  const int sms = c.sm_count > 0 ? c.sm_count : 148;
+
+  // split K only when the tiles alone cannot occupy the GPU and there is enough K to share
+  int slices = 1;
+  const int tiles = g.m_tiles * g.n_tiles;
+  if (c.opt_split_k > 0) slices = c.opt_split_k;
+  else if (tiles * 2 <= sms && g.total_slabs >= 8) {
+    slices = sms / tiles;
+    if (slices > g.total_slabs / 4) slices = g.total_slabs / 4;
+    if (slices > 16) slices = 16;
+  }
+  if (slices > g.total_slabs) slices = g.total_slabs;
+  if (slices < 1) slices = 1;
+  g.slabs_per_slice = (g.total_slabs + slices - 1) / slices;
+  g.k_slices = (g.total_slabs + g.slabs_per_slice - 1) / g.slabs_per_slice;
+
+  if (!c.status_word) {
+    if (!cuda_ok(cudaMalloc(&c.status_word, sizeof(int)), "cudaMalloc(status)")) return false;
+    if (!cuda_ok(cudaMemsetAsync(c.status_word, 0, sizeof(int), c.stream), "cudaMemset(status)")) return false;
+  }
+  g.status = c.status_word;
+
+  CUtensorMap ma, mb;
+  if (!make_map(&ma, p.in, g.M, g.K, BM)) return false;
+  if (!make_map(&mb, p.w, g.N, g.K, bn)) return false;
+
+  const int units = tiles * g.k_slices;
+  const int grid = units < sms ? units : sms;
+  const bool raw = p.epi.mode == EPI_RAW32;
+
+  if (g.k_slices == 1) {
+    g.out = p.out;
+    const int align = raw ? 4 : 16;
+    g.vec_store = (g.N % align == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
+    return launch_final(c, ma, mb, g, bn, grid);
+  }
+  const size_t part_bytes = (size_t)g.k_slices * g.M * g.N * sizeof(int);
+  int *partials = static_cast<int *>(ctx_scratch(c, part_bytes));
+  if (!partials) return false;
+  g.out = partials;
+  g.vec_store = (g.N % 4 == 0);
+  // partial sums need no epilogue mode: one instantiation serves them all
+  if (!launch_bn<EPI_NONE, true>(c, ma, mb, g, bn, grid)) return false;
+  const size_t total = (size_t)g.M * g.N;
+  const unsigned blocks = (unsigned)((total + 255) / 256 < (size_t)sms * 8 ? (total + 255) / 256 : (size_t)sms * 8);
+  switch (p.epi.mode) {
+    case EPI_NONE: splitk_reduce_kernel<EPI_NONE><<<blocks, 256, 0, c.stream>>>(partials, p.out, p.epi, g.M, g.N, g.k_slices); break;
+    case EPI_MULT: splitk_reduce_kernel<EPI_MULT><<<blocks, 256, 0, c.stream>>>(partials, p.out, p.epi, g.M, g.N, g.k_slices); break;
+    case EPI_BN32: splitk_reduce_kernel<EPI_BN32><<<blocks, 256, 0, c.stream>>>(partials, p.out, p.epi, g.M, g.N, g.k_slices); break;
+    case EPI_BN64: splitk_reduce_kernel<EPI_BN64><<<blocks, 256, 0, c.stream>>>(partials, p.out, p.epi, g.M, g.N, g.k_slices); break;
+    default:       splitk_reduce_kernel<EPI_RAW32><<<blocks, 256, 0, c.stream>>>(partials, p.out, p.epi, g.M, g.N, g.k_slices); break;
+  }
+  count_launch();
+  return cuda_ok(cudaGetLastError(), "splitk_reduce launch");
+}
+
+}  // namespace pulpnn

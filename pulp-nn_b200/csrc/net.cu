@@ -1,0 +1,396 @@
+// net.cu -- sequential network runner: the chain of kernel calls a user of the reference library
+// writes by hand, held as a list of layers with device-resident parameters and two ping-pong
+// activation buffers. Images are independent, so a batch is pushed through the stack in
+// micro-batches; every layer call goes through the same launchers as the C entry points.
+#include <cstring>
+#include <new>
+#include <vector>
+
+#include "internal.cuh"
+
+using namespace pulpnn;
+
+namespace {
+
+struct Layer {
+  pulpnn_layer_desc_t d;
+  const int8_t *w = nullptr;
+  const void *bias = nullptr, *k = nullptr, *lambda = nullptr;
+  size_t in_bytes = 0, out_bytes = 0;      // per image
+  int mode = EPI_NONE;
+};
+
+bool is_device_ptr(const void *p)
+{
+  cudaPointerAttributes a;
+  if (cudaPointerGetAttributes(&a, p) != cudaSuccess) { cudaGetLastError(); return false; }
+  return a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged;
+}
+
+}  // namespace
+
+struct pulpnn_net {
+  int bn_bits = 32, max_batch = 1, micro = 0;
+  bool finalized = false;
+  std::vector<Layer> layers;
+  std::vector<void *> owned;               // device allocations holding parameters
+  uint8_t *act[2] = {nullptr, nullptr};
+  size_t act_bytes = 0;                    // per buffer
+  uint8_t *stage_in = nullptr; size_t stage_in_cap = 0;
+  uint8_t *stage_out = nullptr; size_t stage_out_cap = 0;
+  cudaStream_t copy_stream = nullptr;
+  cudaEvent_t ev_in[2] = {nullptr, nullptr}, ev_done[2] = {nullptr, nullptr};
+};
+
+namespace {
+
+const void *upload(pulpnn_net *net, const void *src, size_t bytes)
+{
+  if (!src || bytes == 0) return nullptr;
+  void *dev = nullptr;
+  if (!cuda_ok(cudaMalloc(&dev, (bytes + 255) & ~(size_t)255), "cudaMalloc(parameters)")) return nullptr;
+  net->owned.push_back(dev);
+  const cudaMemcpyKind kind = is_device_ptr(src) ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice;
+  if (!cuda_ok(cudaMemcpy(dev, src, bytes, kind), "parameter upload")) return nullptr;
+  return dev;
+}
+
+bool run_layer(Context &c, const pulpnn_net *net, const Layer &L, const uint8_t *in, void *out, int n)
+{
+  const pulpnn_layer_desc_t &d = L.d;
+  Epilogue e;
+  e.k = L.k; e.lambda = L.lambda; e.bias = L.bias; e.mode = L.mode;
+  e.out_mult = (int)(int16_t)(uint16_t)d.out_mult; e.shift = d.out_shift;
+  switch (d.type) {
+    case PULPNN_LAYER_CONV:
+    case PULPNN_LAYER_POINTWISE:
+    case PULPNN_LAYER_LINEAR_OUT_32: {
+      ConvProblem p;
+      p.in = in; p.w = L.w; p.out = out; p.epi = e;
+      p.B = n; p.H = d.dim_in_y; p.W = d.dim_in_x; p.Cin = d.ch_in; p.Ho = d.dim_out_y; p.Wo = d.dim_out_x;
+      p.Cout = d.ch_out;
+      if (d.type == PULPNN_LAYER_CONV) {
+        p.ky = d.dim_kernel_y; p.kx = d.dim_kernel_x; p.pt = d.padding_y_top; p.pl = d.padding_x_left;
+        p.sy = d.stride_y; p.sx = d.stride_x;
+      } else {
+        p.ky = p.kx = 1; p.pt = p.pl = 0; p.sy = p.sx = 1;
+      }
+      return launch_conv(c, p);
+    }
+    case PULPNN_LAYER_DEPTHWISE: {
+      DepthwiseProblem p;
+      p.in = in; p.w = L.w; p.out = static_cast<uint8_t *>(out); p.epi = e;
+      p.B = n; p.H = d.dim_in_y; p.W = d.dim_in_x; p.C = d.ch_in; p.Ho = d.dim_out_y; p.Wo = d.dim_out_x;
+      p.ky = d.dim_kernel_y; p.kx = d.dim_kernel_x; p.pt = d.padding_y_top; p.pl = d.padding_x_left;
+      p.sy = d.stride_y; p.sx = d.stride_x; p.in_is_hwc = true;
+      return launch_depthwise(c, p);
+    }
+    case PULPNN_LAYER_AVGPOOL:
+    case PULPNN_LAYER_MAXPOOL: {
+      PoolProblem p{};
+      p.in = in; p.out = static_cast<uint8_t *>(out);
+      p.B = n; p.H = d.dim_in_y; p.W = d.dim_in_x; p.C = d.ch_in; p.Ho = d.dim_out_y; p.Wo = d.dim_out_x;
+      p.ky = d.dim_kernel_y; p.kx = d.dim_kernel_x; p.pt = d.padding_y_top; p.pb = d.padding_y_bottom;
+      p.pl = d.padding_x_left; p.pr = d.padding_x_right; p.sy = d.stride_y; p.sx = d.stride_x;
+      p.bn_bits = net->bn_bits; p.requant = 0; p.shift = 0; p.lambda = 0; p.out_add = 0;
+      return d.type == PULPNN_LAYER_AVGPOOL ? launch_avgpool(c, p) : launch_maxpool(c, p, nullptr);
+    }
+    default:
+      set_error(PULPNN_ERR_INVALID_ARG, "unknown layer type %d", d.type);
+      return false;
+  }
+}
+
+// pushes images [0, n) that already sit in device memory through layers [0, n_layers)
+bool run_device(Context &c, pulpnn_net *net, const uint8_t *din, uint8_t *dout, int n, int n_layers,
+                std::vector<cudaEvent_t> *marks = nullptr)
+{
+  const int micro = net->micro > 0 ? net->micro : n;
+  const size_t in_b = net->layers.front().in_bytes;
+  const size_t out_b = net->layers[n_layers - 1].out_bytes;
+  for (int i0 = 0; i0 < n; i0 += micro) {
+    const int nb = n - i0 < micro ? n - i0 : micro;
+    const uint8_t *cur = din + (size_t)i0 * in_b;
+    for (int l = 0; l < n_layers; l++) {
+      void *dst = (l == n_layers - 1) ? static_cast<void *>(dout + (size_t)i0 * out_b)
+                                      : static_cast<void *>(net->act[l & 1]);
+      if (marks) {
+        cudaEvent_t ev;
+        if (!cuda_ok(cudaEventCreate(&ev), "cudaEventCreate")) return false;
+        cudaEventRecord(ev, c.stream);
+        marks->push_back(ev);
+      }
+      if (!run_layer(c, net, net->layers[l], cur, dst, nb)) return false;
+      cur = static_cast<const uint8_t *>(dst);
+    }
+  }
+  if (marks) {
+    cudaEvent_t ev;
+    if (!cuda_ok(cudaEventCreate(&ev), "cudaEventCreate")) return false;
+    cudaEventRecord(ev, c.stream);
+    marks->push_back(ev);
+  }
+  return true;
+}
+
+int run_impl(pulpnn_net *net, const uint8_t *input, void *output, int n, int n_layers)
+{
+  Context &c = ctx();
+  if (!ensure_device(c)) return c.err;
+  if (!net || !net->finalized) { set_error(PULPNN_ERR_INVALID_ARG, "network is not finalized"); return c.err; }
+  if (!input || !output || n < 1 || n > net->max_batch || n_layers < 1 || n_layers > (int)net->layers.size()) {
+    set_error(PULPNN_ERR_INVALID_ARG, "pulpnn_net_run: bad arguments (n=%d, max_batch=%d)", n, net->max_batch);
+    return c.err;
+  }
+  const size_t in_b = net->layers.front().in_bytes * n;
+  const size_t out_b = net->layers[n_layers - 1].out_bytes * n;
+  const bool in_dev = is_device_ptr(input), out_dev = is_device_ptr(output);
+  const uint8_t *din = input;
+  uint8_t *dout = static_cast<uint8_t *>(output);
+  if (!in_dev) {
+    if (net->stage_in_cap < in_b) {
+      if (net->stage_in) { cudaStreamSynchronize(c.stream); cudaFree(net->stage_in); }
+      net->stage_in = nullptr; net->stage_in_cap = 0;
+      if (!cuda_ok(cudaMalloc(&net->stage_in, in_b), "cudaMalloc(input staging)")) return c.err;
+      net->stage_in_cap = in_b;
+    }
+    din = net->stage_in;
+  }
+  if (!out_dev) {
+    if (net->stage_out_cap < out_b) {
+      if (net->stage_out) { cudaStreamSynchronize(c.stream); cudaFree(net->stage_out); }
+      net->stage_out = nullptr; net->stage_out_cap = 0;
+      if (!cuda_ok(cudaMalloc(&net->stage_out, out_b), "cudaMalloc(output staging)")) return c.err;
+      net->stage_out_cap = out_b;
+    }
+    dout = net->stage_out;
+  }
+
+  if (in_dev) {
+    if (!run_device(c, net, din, dout, n, n_layers)) return c.err;
+  } else {
+    // Host input: copy in slices on a second stream so that the copy of slice i+1 overlaps the
+    // compute of slice i. A slice is a whole number of micro-batches.
+    const int micro = net->micro > 0 ? net->micro : n;
+    int slice = micro;
+    while (slice < n && slice * 4 < n) slice += micro;          // about four slices
+    const size_t img_in = net->layers.front().in_bytes, img_out = net->layers[n_layers - 1].out_bytes;
+    int idx = 0;
+    for (int i0 = 0; i0 < n; i0 += slice, idx++) {
+      const int nb = n - i0 < slice ? n - i0 : slice;
+      cudaEvent_t ev = net->ev_in[idx & 1];
+      if (!cuda_ok(cudaMemcpyAsync(net->stage_in + (size_t)i0 * img_in, input + (size_t)i0 * img_in,
+                                   (size_t)nb * img_in, cudaMemcpyHostToDevice, net->copy_stream), "H2D copy"))
+        return c.err;
+      cudaEventRecord(ev, net->copy_stream);
+      cudaStreamWaitEvent(c.stream, ev, 0);
+      if (!run_device(c, net, net->stage_in + (size_t)i0 * img_in, dout + (size_t)i0 * img_out, nb, n_layers))
+        return c.err;
+    }
+  }
+  if (!out_dev) {
+    if (!cuda_ok(cudaMemcpyAsync(output, dout, out_b, cudaMemcpyDeviceToHost, c.stream), "D2H copy")) return c.err;
+  }
+  if (!in_dev || !out_dev) {
+    if (!cuda_ok(cudaStreamSynchronize(c.stream), "cudaStreamSynchronize")) return c.err;
+  }
+  return PULPNN_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+pulpnn_net_t *pulpnn_net_create(int bn_bits, int max_batch)
+{
+  Context &c = ctx();
+  if (!ensure_device(c)) return nullptr;
+  if ((bn_bits != 32 && bn_bits != 64) || max_batch < 1) {
+    set_error(PULPNN_ERR_INVALID_ARG, "pulpnn_net_create: bn_bits must be 32 or 64 and max_batch >= 1");
+    return nullptr;
+  }
+  pulpnn_net *net = new (std::nothrow) pulpnn_net;
+  if (!net) return nullptr;
+  net->bn_bits = bn_bits;
+  net->max_batch = max_batch;
+  return net;
+}
+
+int pulpnn_net_add_layer(pulpnn_net_t *net, const pulpnn_layer_desc_t *desc)
+{
+  Context &c = ctx();
+  if (!net || !desc || net->finalized) { set_error(PULPNN_ERR_INVALID_ARG, "pulpnn_net_add_layer: bad arguments"); return c.err; }
+  if (!ensure_device(c)) return c.err;
+  Layer L;
+  L.d = *desc;
+  const pulpnn_layer_desc_t &d = L.d;
+  if (d.dim_in_x < 1 || d.dim_in_y < 1 || d.ch_in < 1 || d.dim_out_x < 1 || d.dim_out_y < 1 || d.ch_out < 1) {
+    set_error(PULPNN_ERR_INVALID_ARG, "layer %zu: zero dimension", net->layers.size());
+    return c.err;
+  }
+  L.in_bytes = (size_t)d.dim_in_x * d.dim_in_y * d.ch_in;
+  L.out_bytes = (size_t)d.dim_out_x * d.dim_out_y * d.ch_out * (d.type == PULPNN_LAYER_LINEAR_OUT_32 ? 4 : 1);
+  if (!net->layers.empty() && net->layers.back().out_bytes != L.in_bytes) {
+    set_error(PULPNN_ERR_INVALID_ARG, "layer %zu: input size %zu does not match the previous output %zu",
+              net->layers.size(), L.in_bytes, net->layers.back().out_bytes);
+    return c.err;
+  }
+  if (!net->layers.empty() && net->layers.back().d.type == PULPNN_LAYER_LINEAR_OUT_32) {
+    set_error(PULPNN_ERR_INVALID_ARG, "an int32-output layer must be the last one");
+    return c.err;
+  }
+  const size_t bn_sz = net->bn_bits / 8;
+  const int bn_mode = net->bn_bits == 32 ? EPI_BN32 : EPI_BN64;
+  size_t wbytes = 0;
+  switch (d.type) {
+    case PULPNN_LAYER_CONV:
+      wbytes = (size_t)d.ch_out * d.dim_kernel_x * d.dim_kernel_y * d.ch_in;
+      L.mode = (d.flag_batch_norm && d.flag_relu) ? bn_mode : (d.flag_relu == 1 ? EPI_MULT : EPI_NONE);
+      if ((d.dim_out_x - 1) * d.stride_x + d.dim_kernel_x > d.dim_in_x + d.padding_x_left + d.padding_x_right ||
+          (d.dim_out_y - 1) * d.stride_y + d.dim_kernel_y > d.dim_in_y + d.padding_y_top + d.padding_y_bottom) {
+        set_error(PULPNN_ERR_UNSUPPORTED, "layer %zu: inconsistent output size", net->layers.size());
+        return c.err;
+      }
+      break;
+    case PULPNN_LAYER_POINTWISE:
+      wbytes = (size_t)d.ch_out * d.ch_in;
+      L.mode = (d.flag_batch_norm && d.flag_relu) ? bn_mode : (d.flag_relu == 1 ? EPI_MULT : EPI_NONE);
+      if (d.dim_in_x != d.dim_out_x || d.dim_in_y != d.dim_out_y) {
+        set_error(PULPNN_ERR_UNSUPPORTED, "layer %zu: pointwise needs dim_in == dim_out", net->layers.size());
+        return c.err;
+      }
+      break;
+    case PULPNN_LAYER_DEPTHWISE:
+      wbytes = (size_t)d.ch_in * d.dim_kernel_x * d.dim_kernel_y;
+      L.mode = (d.flag_batch_norm && d.flag_relu) ? bn_mode : (d.flag_relu ? EPI_MULT : EPI_NONE);
+      if (d.ch_in != d.ch_out) { set_error(PULPNN_ERR_UNSUPPORTED, "layer %zu: depthwise needs ch_in == ch_out", net->layers.size()); return c.err; }
+      break;
+    case PULPNN_LAYER_LINEAR_OUT_32:
+      wbytes = (size_t)d.ch_out * L.in_bytes;
+      L.d.ch_in = (int)L.in_bytes; L.d.dim_in_x = L.d.dim_in_y = 1;
+      L.mode = EPI_RAW32;
+      break;
+    case PULPNN_LAYER_AVGPOOL:
+    case PULPNN_LAYER_MAXPOOL:
+      if (d.ch_in != d.ch_out) { set_error(PULPNN_ERR_UNSUPPORTED, "layer %zu: pooling needs ch_in == ch_out", net->layers.size()); return c.err; }
+      break;
+    default:
+      set_error(PULPNN_ERR_INVALID_ARG, "layer %zu: unknown type %d", net->layers.size(), d.type);
+      return c.err;
+  }
+  if (L.mode != EPI_RAW32 && wbytes) {
+    const int hi = L.mode == EPI_BN64 ? 63 : 31;
+    if (d.out_shift < 0 || d.out_shift > hi) { set_error(PULPNN_ERR_INVALID_ARG, "layer %zu: out_shift %d", net->layers.size(), d.out_shift); return c.err; }
+  }
+  if (wbytes) {
+    if (!d.weights) { set_error(PULPNN_ERR_INVALID_ARG, "layer %zu: weights missing", net->layers.size()); return c.err; }
+    L.w = static_cast<const int8_t *>(upload(net, d.weights, wbytes));
+    if (!L.w) return c.err;
+    if (d.bias) {
+      L.bias = upload(net, d.bias, (size_t)d.ch_out * (d.type == PULPNN_LAYER_LINEAR_OUT_32 ? 4 : 1));
+      if (!L.bias) return c.err;
+    }
+    if (L.mode == EPI_BN32 || L.mode == EPI_BN64) {
+      if (!d.k || !d.lambda) { set_error(PULPNN_ERR_INVALID_ARG, "layer %zu: batch-norm parameters missing", net->layers.size()); return c.err; }
+      L.k = upload(net, d.k, bn_sz * d.ch_out);
+      L.lambda = upload(net, d.lambda, bn_sz * d.ch_out);
+      if (!L.k || !L.lambda) return c.err;
+    }
+  }
+  L.d.weights = nullptr; L.d.bias = nullptr; L.d.k = L.d.lambda = nullptr;
+  net->layers.push_back(L);
+  return PULPNN_OK;
+}
+
+int pulpnn_net_finalize(pulpnn_net_t *net, int micro_batch)
+{
+  Context &c = ctx();
+  if (!net || net->finalized || net->layers.empty()) { set_error(PULPNN_ERR_INVALID_ARG, "pulpnn_net_finalize: bad arguments"); return c.err; }
+  if (!ensure_device(c)) return c.err;
+  size_t biggest = 0;
+  for (size_t l = 0; l + 1 < net->layers.size(); l++) biggest = net->layers[l].out_bytes > biggest ? net->layers[l].out_bytes : biggest;
+  int micro = micro_batch > 0 ? micro_batch : net->max_batch;
+  if (micro > net->max_batch) micro = net->max_batch;
+  net->micro = micro;
+  net->act_bytes = biggest * micro;
+  for (int i = 0; i < 2; i++) {
+    if (net->act_bytes && !cuda_ok(cudaMalloc(&net->act[i], net->act_bytes), "cudaMalloc(activations)")) return c.err;
+    if (!cuda_ok(cudaEventCreateWithFlags(&net->ev_in[i], cudaEventDisableTiming), "cudaEventCreate")) return c.err;
+    if (!cuda_ok(cudaEventCreateWithFlags(&net->ev_done[i], cudaEventDisableTiming), "cudaEventCreate")) return c.err;
+  }
+  if (!cuda_ok(cudaStreamCreateWithFlags(&net->copy_stream, cudaStreamNonBlocking), "cudaStreamCreate")) return c.err;
+  net->finalized = true;
+  return PULPNN_OK;
+}
+
+int pulpnn_net_run(pulpnn_net_t *net, const uint8_t *input, void *output, int n_images)
+{
+  return run_impl(net, input, output, n_images, net ? (int)net->layers.size() : 0);
+}
+
+int pulpnn_net_run_prefix(pulpnn_net_t *net, const uint8_t *input, void *output, int n_images, int n_layers)
+{
+  return run_impl(net, input, output, n_images, n_layers);
+}
+
+int pulpnn_net_run_timed(pulpnn_net_t *net, const uint8_t *input, void *output, int n_images, float *layer_ms)
+{
+  Context &c = ctx();
+  if (!ensure_device(c)) return c.err;
+  if (!net || !net->finalized || !input || !output || !layer_ms || n_images < 1 || n_images > net->max_batch) {
+    set_error(PULPNN_ERR_INVALID_ARG, "pulpnn_net_run_timed: bad arguments");
+    return c.err;
+  }
+  if (!is_device_ptr(input) || !is_device_ptr(output)) {
+    set_error(PULPNN_ERR_INVALID_ARG, "pulpnn_net_run_timed: buffers must be device memory");
+    return c.err;
+  }
+  const int nl = (int)net->layers.size();
+  std::vector<cudaEvent_t> marks;
+  const bool ok = run_device(c, net, input, static_cast<uint8_t *>(output), n_images, nl, &marks);
+  if (ok && cuda_ok(cudaStreamSynchronize(c.stream), "cudaStreamSynchronize")) {
+    for (int l = 0; l < nl; l++) layer_ms[l] = 0.f;
+    // marks: one event before every layer call of every micro-batch, plus one at the very end
+    for (size_t i = 0; i + 1 < marks.size(); i++) {
+      float ms = 0.f;
+      cudaEventElapsedTime(&ms, marks[i], marks[i + 1]);
+      layer_ms[i % nl] += ms;
+    }
+  }
+  for (cudaEvent_t ev : marks) cudaEventDestroy(ev);
+  return c.err == PULPNN_OK && ok ? PULPNN_OK : (c.err ? c.err : PULPNN_ERR_CUDA);
+}
+
+int pulpnn_net_num_layers(const pulpnn_net_t *net) { return net ? (int)net->layers.size() : 0; }
+
+size_t pulpnn_net_layer_output_bytes(const pulpnn_net_t *net, int layer)
+{
+  if (!net || layer < 0 || layer >= (int)net->layers.size()) return 0;
+  return net->layers[layer].out_bytes;
+}
+
+unsigned long long pulpnn_net_launches_per_run(const pulpnn_net_t *net, int n_images)
+{
+  if (!net || !net->finalized) return 0;
+  const int micro = net->micro > 0 ? net->micro : n_images;
+  const unsigned long long chunks = (unsigned long long)((n_images + micro - 1) / micro);
+  return chunks * net->layers.size();
+}
+
+void pulpnn_net_destroy(pulpnn_net_t *net)
+{
+  if (!net) return;
+  cudaDeviceSynchronize();
+  for (void *p : net->owned) cudaFree(p);
+  for (int i = 0; i < 2; i++) {
+    if (net->act[i]) cudaFree(net->act[i]);
+    if (net->ev_in[i]) cudaEventDestroy(net->ev_in[i]);
+    if (net->ev_done[i]) cudaEventDestroy(net->ev_done[i]);
+  }
+  if (net->stage_in) cudaFree(net->stage_in);
+  if (net->stage_out) cudaFree(net->stage_out);
+  if (net->copy_stream) cudaStreamDestroy(net->copy_stream);
+  delete net;
+}
+
+}  // extern "C"

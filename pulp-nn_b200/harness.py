@@ -1,0 +1,154 @@
+"""Array-level front end to the C entry points, with the same method names and arguments as the
+CPU checkers' bindings, so a parity test runs one case through both and compares bytes.
+
+``GpuKernels(host_buffers=False)`` moves numpy inputs into torch CUDA tensors and passes device
+pointers (the fast path); ``host_buffers=True`` hands the numpy buffers straight to the C ABI and
+lets the library stage them. Torch is used for device memory only.
+"""
+import numpy as np
+
+from . import api
+
+
+class GpuKernels:
+    kind = "cuda"
+
+    def __init__(self, host_buffers=False, device=0):
+        import torch
+        if not torch.cuda.is_available():
+            raise RuntimeError("no CUDA device: the kernels of this package run on a GPU only")
+        self.torch = torch
+        self.host = host_buffers
+        self.dev = torch.device("cuda", device)
+        torch.cuda.set_device(self.dev)
+        api.set_device(device)
+        api.set_stream(None)
+
+    # -- buffers ---------------------------------------------------------------------------
+    def _in(self, a, dtype=None):
+        if a is None:
+            return None
+        a = np.ascontiguousarray(a if dtype is None else a.astype(dtype, copy=False))
+        if self.host:
+            return a
+        return self.torch.from_numpy(a).to(self.dev)
+
+    def _out(self, shape, dtype):
+        if self.host:
+            return np.zeros(shape, dtype)
+        tdt = {np.uint8: self.torch.uint8, np.int32: self.torch.int32}[dtype]
+        return self.torch.zeros(shape, dtype=tdt, device=self.dev)
+
+    def _np(self, t):
+        if self.host:
+            return t
+        api.synchronize()
+        return t.cpu().numpy()
+
+    @staticmethod
+    def _bn(bits, k, lam):
+        dt = np.int32 if bits == 32 else np.int64
+        return (None if k is None else np.ascontiguousarray(k, dt),
+                None if lam is None else np.ascontiguousarray(lam, dt))
+
+    # -- kernels ---------------------------------------------------------------------------
+    def conv(self, bits, x, w, k, lam, *, bias=None, out_mult=1, out_shift=0, out_hw, kernel, pads,
+             strides, relu=1, bn=1, variant="Ho"):
+        B, H, W, Cin = x.shape
+        Cout = w.shape[0]
+        Ho, Wo = out_hw
+        ky, kx = kernel
+        pt, pb, pl, pr = pads
+        sy, sx = strides
+        k, lam = self._bn(bits, k, lam)
+        out = self._out((B, Ho, Wo, Cout), np.uint8)
+        fn = {"Ho": api.pulp_nn_conv_Ho_parallel, "HoWo": api.pulp_nn_conv_HoWo_parallel}[variant]
+        api.set_batch(B)
+        fn(bits, self._in(x), None, self._in(bias), out, self._in(w), self._in(k), self._in(lam),
+           out_mult, out_shift, W, H, Cin, Wo, Ho, Cout, kx, ky, pt, pb, pl, pr, sx, sy, relu, bn)
+        return self._np(out)
+
+    def pointwise(self, bits, x, w, k, lam, *, bias=None, out_mult=1, out_shift=0, relu=1, bn=1):
+        B, H, W, Cin = x.shape
+        Cout = w.shape[0]
+        k, lam = self._bn(bits, k, lam)
+        out = self._out((B, H, W, Cout), np.uint8)
+        api.set_batch(B)
+        api.pulp_nn_pointwise_HoWo_parallel(bits, self._in(x), None, self._in(bias), out,
+                                            self._in(w), self._in(k), self._in(lam), out_mult,
+                                            out_shift, W, H, Cin, W, H, Cout, 1, 1, 0, 0, 0, 0, 1,
+                                            1, relu, bn)
+        return self._np(out)
+
+    def depthwise(self, bits, x, w, k, lam, *, bias=None, out_mult=1, out_shift=0, out_hw, kernel,
+                  pads, strides, relu=1, bn=1, in_is_hwc=False):
+        if in_is_hwc:
+            B, H, W, Cc = x.shape
+        else:
+            B, Cc, H, W = x.shape
+        Ho, Wo = out_hw
+        ky, kx = kernel
+        pt, pb, pl, pr = pads
+        sy, sx = strides
+        k, lam = self._bn(bits, k, lam)
+        out = self._out((B, Ho, Wo, Cc), np.uint8)
+        fn = api.pulpnn_depthwise_hwc if in_is_hwc else api.pulp_nn_depthwise_generic
+        api.set_batch(B)
+        fn(bits, self._in(x), None, self._in(bias), out, self._in(w), None, self._in(k),
+           self._in(lam), out_mult, out_shift, W, H, Cc, Wo, Ho, Cc, kx, ky, pt, pb, pl, pr, sx, sy,
+           relu, bn)
+        return self._np(out)
+
+    def linear(self, bits, x, w, k, lam, *, bias=None, out_mult=1, out_shift=0, relu=1, bn=1):
+        B, K = x.shape
+        N = w.shape[0]
+        k, lam = self._bn(bits, k, lam)
+        out = self._out((B, N), np.uint8)
+        api.set_batch(B)
+        api.pulp_nn_linear(bits, self._in(x), self._in(bias), out, self._in(w), self._in(k),
+                           self._in(lam), out_mult, out_shift, K, N, relu, bn)
+        return self._np(out)
+
+    def linear_out_32(self, x, w, *, bias32=None, bits=32):
+        B, K = x.shape
+        N = w.shape[0]
+        out = self._out((B, N), np.int32)
+        api.set_batch(B)
+        api.pulp_nn_linear_out_32(bits, self._in(x), self._in(bias32), out, self._in(w), K, N)
+        return self._np(out)
+
+    def maxpool(self, x, *, out_hw, kernel, pads, strides, want_input_after=False, bits=32):
+        B, H, W, Cc = x.shape
+        Ho, Wo = out_hw
+        ky, kx = kernel
+        pt, pb, pl, pr = pads
+        sy, sx = strides
+        xin = self._in(x.copy())
+        out = self._out((B, Ho, Wo, Cc), np.uint8)
+        api.set_batch(B)
+        api.set_option(api.OPT_MAXPOOL_CLOBBER, int(want_input_after))
+        try:
+            api.pulp_nn_maxpool(bits, xin, out, W, H, Cc, Wo, Ho, kx, ky, pt, pb, pl, pr, sx, sy)
+        finally:
+            api.set_option(api.OPT_MAXPOOL_CLOBBER, 0)
+        return (self._np(out), self._np(xin)) if want_input_after else self._np(out)
+
+    def avgpool(self, bits, x, *, lam=0, out_shift=0, out_add=0, out_hw, kernel, pads, strides,
+                requant=0):
+        B, H, W, Cc = x.shape
+        Ho, Wo = out_hw
+        ky, kx = kernel
+        pt, pb, pl, pr = pads
+        sy, sx = strides
+        out = self._out((B, Ho, Wo, Cc), np.uint8)
+        api.set_batch(B)
+        api.pulp_nn_avgpool(bits, self._in(x), out, lam, out_shift, out_add, W, H, Cc, Wo, Ho, kx,
+                            ky, pt, pb, pl, pr, sx, sy, requant)
+        return self._np(out)
+
+    def add(self, a, b, *, m1, m2, out_shift, bits=32):
+        B, H, W, Cc = a.shape
+        out = self._out(a.shape, np.uint8)
+        api.set_batch(B)
+        api.pulp_nn_add(bits, self._in(a), self._in(b), out, m1, m2, out_shift, H, W, Cc)
+        return self._np(out)

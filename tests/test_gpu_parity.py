@@ -1,0 +1,327 @@
+"""Bit-exact parity of the CUDA kernels with the CPU checker, through the C ABI.
+
+Integer arithmetic only, so the bar is byte equality (tolerance 0). Every case runs the seeded
+inputs through the C restatement (and, where oracle/_ref was built, spot-checks against the
+compiled reference itself) and through the library with device pointers; a subset repeats with
+host pointers (the staged path) and with the tensor-core kernel switched off, so both contraction
+kernels are held to the same checker.
+"""
+import numpy as np
+import pytest
+
+from conftest import pulpnn
+
+pytestmark = pytest.mark.gpu
+wl = pulpnn.workloads
+api = pulpnn.api
+
+MODES = [(1, 1), (1, 0), (0, 0), (0, 1), (2, 0)]
+
+
+@pytest.fixture(scope="module")
+def gpu():
+    return pulpnn.GpuKernels(host_buffers=False)
+
+
+@pytest.fixture(scope="module")
+def gpu_host():
+    return pulpnn.GpuKernels(host_buffers=True)
+
+
+@pytest.fixture(autouse=True)
+def _clean_status():
+    yield
+    assert api.device_status() == 0, "a bounded wait inside a tensor-core kernel ran out"
+    api.set_option(api.OPT_FORCE_GENERIC, 0)
+    api.set_option(api.OPT_SPLIT_K, 0)
+
+
+def conv_kw(c):
+    return dict(bias=c["bias"], out_mult=c["out_mult"], out_shift=c["out_shift"], out_hw=c["out_hw"],
+                kernel=c["kernel"], pads=c["pads"], strides=c["strides"], relu=c["relu"], bn=c["bn"])
+
+
+def pw_kw(c):
+    return dict(bias=c["bias"], out_mult=c["out_mult"], out_shift=c["out_shift"], relu=c["relu"],
+                bn=c["bn"])
+
+
+def same(a, b):
+    assert a.shape == b.shape and a.dtype == b.dtype
+    if not np.array_equal(a, b):
+        bad = np.argwhere(a != b)
+        raise AssertionError("%d of %d bytes differ; first at %s: got %d want %d"
+                             % (len(bad), a.size, tuple(bad[0]), a[tuple(bad[0])], b[tuple(bad[0])]))
+
+
+# ---- standard convolution ------------------------------------------------------------------
+@pytest.mark.parametrize("variant", ["Ho", "HoWo"])
+def test_conv_config1_literal(variant, gpu, restatement):
+    c = wl.config_c1()
+    want = restatement.conv(32, c["x"], c["w"], c["k"], c["lam"], **conv_kw(c))
+    same(gpu.conv(32, c["x"], c["w"], c["k"], c["lam"], variant=variant, **conv_kw(c)), want)
+
+
+@pytest.mark.parametrize("bits", [32, 64])
+def test_conv_config1_live_parameters(bits, gpu, gpu_host, restatement):
+    c = wl.conv_case(0, 32, 32, 32, 64, bits=bits, out_shift=12, batch=3, with_bias=True)
+    want = restatement.conv(bits, c["x"], c["w"], c["k"], c["lam"], **conv_kw(c))
+    assert np.count_nonzero(want) > want.size // 10
+    same(gpu.conv(bits, c["x"], c["w"], c["k"], c["lam"], **conv_kw(c)), want)
+    same(gpu_host.conv(bits, c["x"], c["w"], c["k"], c["lam"], **conv_kw(c)), want)
+
+
+@pytest.mark.parametrize("bits", [32, 64])
+@pytest.mark.parametrize("relu,bn", MODES)
+def test_conv_ragged_all_modes(bits, relu, bn, gpu, restatement):
+    c = wl.conv_case(11, 13, 11, 5, 7, kernel=(3, 5), strides=(2, 1), pads=(1, 0, 2, 1), batch=3,
+                     bits=bits, out_shift=9, with_bias=True, out_mult=5, relu=relu, bn=bn,
+                     k_range=(-64, 64), lam_range=(-2 ** 20, 2 ** 20))
+    want = restatement.conv(bits, c["x"], c["w"], c["k"], c["lam"], **conv_kw(c))
+    same(gpu.conv(bits, c["x"], c["w"], c["k"], c["lam"], **conv_kw(c)), want)
+
+
+def test_conv_bn_wraparound(gpu, restatement):
+    for bits in (32, 64):
+        c = wl.conv_case(12, 9, 9, 16, 8, bits=bits, out_shift=12, w_range=(-128, 127),
+                         k_range=(2 ** 20, 2 ** 24), lam_range=(-2 ** 30, 2 ** 30))
+        want = restatement.conv(bits, c["x"], c["w"], c["k"], c["lam"], **conv_kw(c))
+        same(gpu.conv(bits, c["x"], c["w"], c["k"], c["lam"], **conv_kw(c)), want)
+
+
+def test_conv_mobilenet_first_layer(gpu, restatement):
+    c = wl.conv_case(13, 224, 224, 3, 32, strides=(2, 2), batch=2, bits=32, out_shift=9)
+    want = restatement.conv(32, c["x"], c["w"], c["k"], c["lam"], **conv_kw(c))
+    same(gpu.conv(32, c["x"], c["w"], c["k"], c["lam"], **conv_kw(c)), want)
+
+
+def test_conv_against_compiled_reference(gpu, reference32):
+    c = wl.conv_case(14, 17, 19, 8, 12, batch=2, bits=32, out_shift=10, with_bias=True)
+    want = reference32.conv(32, c["x"], c["w"], c["k"], c["lam"], variant="HoWo", **conv_kw(c))
+    same(gpu.conv(32, c["x"], c["w"], c["k"], c["lam"], **conv_kw(c)), want)
+
+
+# ---- pointwise -----------------------------------------------------------------------------
+@pytest.mark.parametrize("force_generic", [0, 1])
+def test_pointwise_config2_literal_and_live(force_generic, gpu, restatement):
+    api.set_option(api.OPT_FORCE_GENERIC, force_generic)
+    for shift in (None, 10):
+        c = wl.pointwise_case(1, 56, 56, 128, 256, batch=4, bits=32, out_shift=shift)
+        want = restatement.pointwise(32, c["x"], c["w"], c["k"], c["lam"], **pw_kw(c))
+        same(gpu.pointwise(32, c["x"], c["w"], c["k"], c["lam"], **pw_kw(c)), want)
+
+
+@pytest.mark.parametrize("bits", [32, 64])
+@pytest.mark.parametrize("relu,bn", MODES)
+def test_pointwise_tensor_core_all_modes(bits, relu, bn, gpu, restatement):
+    # K = 80 (not a multiple of the 128-byte stage), N = 48 (< one tile), M = 3*9*7 = 189 (ragged)
+    c = wl.pointwise_case(22, 9, 7, 80, 48, batch=3, bits=bits, out_shift=8, with_bias=True,
+                          out_mult=3, relu=relu, bn=bn, w_range=(-128, 127))
+    want = restatement.pointwise(bits, c["x"], c["w"], c["k"], c["lam"], **pw_kw(c))
+    same(gpu.pointwise(bits, c["x"], c["w"], c["k"], c["lam"], **pw_kw(c)), want)
+
+
+@pytest.mark.parametrize("cin,cout", [(16, 16), (32, 64), (64, 128), (256, 512), (512, 520),
+                                      (1024, 1024), (48, 1000), (144, 24)])
+def test_pointwise_tensor_core_shapes(cin, cout, gpu, restatement):
+    c = wl.pointwise_case(23, 14, 14, cin, cout, batch=5, bits=32,
+                          out_shift=wl.ceil_log2(cin) + 3, w_range=(-128, 127))
+    want = restatement.pointwise(32, c["x"], c["w"], c["k"], c["lam"], **pw_kw(c))
+    assert np.count_nonzero(want) > want.size // 20
+    same(gpu.pointwise(32, c["x"], c["w"], c["k"], c["lam"], **pw_kw(c)), want)
+
+
+@pytest.mark.parametrize("relu,bn", MODES)
+def test_pointwise_ragged_generic_path(relu, bn, gpu, gpu_host, restatement):
+    c = wl.pointwise_case(21, 9, 7, 22, 13, batch=2, bits=32, out_shift=8, with_bias=True,
+                          out_mult=3, relu=relu, bn=bn)
+    want = restatement.pointwise(32, c["x"], c["w"], c["k"], c["lam"], **pw_kw(c))
+    same(gpu.pointwise(32, c["x"], c["w"], c["k"], c["lam"], **pw_kw(c)), want)
+    same(gpu_host.pointwise(32, c["x"], c["w"], c["k"], c["lam"], **pw_kw(c)), want)
+
+
+def test_pointwise_against_compiled_reference(gpu, reference64):
+    c = wl.pointwise_case(24, 12, 12, 64, 96, batch=2, bits=64, out_shift=9, with_bias=True)
+    want = reference64.pointwise(64, c["x"], c["w"], c["k"], c["lam"], **pw_kw(c))
+    same(gpu.pointwise(64, c["x"], c["w"], c["k"], c["lam"], **pw_kw(c)), want)
+
+
+def test_pointwise_many_tiles_property(gpu, restatement):
+    """Full config-2 batch: too large for the CPU checker in seconds, so check a size-independent
+    property instead: the batched result equals the per-image results (images are independent),
+    and the first and last images equal the checker."""
+    c = wl.config_c2(batch=64)
+    c["out_shift"] = 10
+    got = gpu.pointwise(32, c["x"], c["w"], c["k"], c["lam"], **pw_kw(c))
+    for i in (0, 63):
+        want = restatement.pointwise(32, c["x"][i:i + 1], c["w"], c["k"], c["lam"], **pw_kw(c))
+        same(got[i:i + 1], want)
+    one = gpu.pointwise(32, c["x"][17:18], c["w"], c["k"], c["lam"], **pw_kw(c))
+    same(got[17:18], one)
+
+
+# ---- depthwise -----------------------------------------------------------------------------
+def dw_kw(c):
+    return dict(bias=c["bias"], out_mult=c["out_mult"], out_shift=c["out_shift"], out_hw=c["out_hw"],
+                kernel=c["kernel"], pads=c["pads"], strides=c["strides"], relu=c["relu"], bn=c["bn"],
+                in_is_hwc=c["hwc"])
+
+
+@pytest.mark.parametrize("hwc", [False, True])
+def test_depthwise_config3(hwc, gpu, restatement):
+    c = wl.config_c3(batch=3)
+    if hwc:
+        c["x"] = np.ascontiguousarray(c["x"].transpose(0, 2, 3, 1))
+        c["hwc"] = True
+    want = restatement.depthwise(64, c["x"], c["w"], c["k"], c["lam"], **dw_kw(c))
+    assert np.count_nonzero(want) > want.size // 4
+    same(gpu.depthwise(64, c["x"], c["w"], c["k"], c["lam"], **dw_kw(c)), want)
+
+
+@pytest.mark.parametrize("bits", [32, 64])
+@pytest.mark.parametrize("relu,bn", MODES)
+@pytest.mark.parametrize("stride", [1, 2])
+@pytest.mark.parametrize("hwc", [False, True])
+def test_depthwise_modes(bits, relu, bn, stride, hwc, gpu, restatement):
+    c = wl.depthwise_case(31, 15, 14, 8, strides=(stride, stride), batch=2, bits=bits, out_shift=7,
+                          with_bias=True, out_mult=3, relu=relu, bn=bn, hwc=hwc)
+    want = restatement.depthwise(bits, c["x"], c["w"], c["k"], c["lam"], **dw_kw(c))
+    same(gpu.depthwise(bits, c["x"], c["w"], c["k"], c["lam"], **dw_kw(c)), want)
+
+
+@pytest.mark.parametrize("hwc", [False, True])
+@pytest.mark.parametrize("C", [6, 37, 64])
+def test_depthwise_ragged_and_5x5(hwc, C, gpu, gpu_host, restatement):
+    for kernel, pads in (((3, 3), (1, 1, 1, 1)), ((5, 5), (2, 2, 2, 2)), ((2, 3), (0, 1, 1, 1))):
+        c = wl.depthwise_case(32, 13, 12, C, kernel=kernel, pads=pads, batch=2, out_shift=8, hwc=hwc)
+        want = restatement.depthwise(32, c["x"], c["w"], c["k"], c["lam"], **dw_kw(c))
+        same(gpu.depthwise(32, c["x"], c["w"], c["k"], c["lam"], **dw_kw(c)), want)
+    same(gpu_host.depthwise(32, c["x"], c["w"], c["k"], c["lam"], **dw_kw(c)), want)
+
+
+def test_depthwise_mobilenet_shapes(gpu, restatement):
+    for (H, C, s) in ((112, 32, 1), (112, 64, 2), (14, 512, 1), (7, 1024, 1)):
+        c = wl.depthwise_case(33, H, H, C, strides=(s, s), batch=2, out_shift=9, hwc=True)
+        want = restatement.depthwise(32, c["x"], c["w"], c["k"], c["lam"], **dw_kw(c))
+        same(gpu.depthwise(32, c["x"], c["w"], c["k"], c["lam"], **dw_kw(c)), want)
+
+
+def test_depthwise_against_compiled_reference(gpu, reference64):
+    c = wl.config_c3(batch=1)
+    want = reference64.depthwise(64, c["x"], c["w"], c["k"], c["lam"], **dw_kw(c))
+    same(gpu.depthwise(64, c["x"], c["w"], c["k"], c["lam"], **dw_kw(c)), want)
+
+
+# ---- linear --------------------------------------------------------------------------------
+def lin_kw(c):
+    return dict(bias=c["bias"], out_mult=c["out_mult"], out_shift=c["out_shift"], relu=c["relu"],
+                bn=c["bn"])
+
+
+@pytest.mark.parametrize("bits", [32, 64])
+@pytest.mark.parametrize("relu,bn", MODES)
+def test_linear_modes_generic(bits, relu, bn, gpu, restatement):
+    c = wl.linear_case(41, 203, 37, batch=3, bits=bits, out_shift=6, out_mult=3, relu=relu, bn=bn,
+                       w_range=(-128, 127))
+    want = restatement.linear(bits, c["x"], c["w"], c["k"], c["lam"], **lin_kw(c))
+    same(gpu.linear(bits, c["x"], c["w"], c["k"], c["lam"], **lin_kw(c)), want)
+
+
+@pytest.mark.parametrize("split_k", [0, 1, 4])
+@pytest.mark.parametrize("relu,bn,shift", [(1, 0, None), (1, 1, 16), (0, 0, 14)])
+def test_linear_config4(split_k, relu, bn, shift, gpu, restatement):
+    api.set_option(api.OPT_SPLIT_K, split_k)
+    c = wl.config_c4(batch=32)
+    c.update(relu=relu, bn=bn)
+    if shift is not None:
+        c["out_shift"] = shift
+    want = restatement.linear(32, c["x"], c["w"], c["k"], c["lam"], **lin_kw(c))
+    same(gpu.linear(32, c["x"], c["w"], c["k"], c["lam"], **lin_kw(c)), want)
+
+
+@pytest.mark.parametrize("split_k", [0, 1, 3])
+def test_linear_out_32_config4_raw_accumulators(split_k, gpu, gpu_host, restatement):
+    api.set_option(api.OPT_SPLIT_K, split_k)
+    c = wl.config_c4(batch=32)
+    b32 = c["bias32"].view(np.int8)
+    want = restatement.linear_out_32(c["x"], c["w"], bias32=b32)
+    same(gpu.linear_out_32(c["x"], c["w"], bias32=b32), want)
+    same(gpu.linear_out_32(c["x"], c["w"]), restatement.linear_out_32(c["x"], c["w"]))
+    if split_k == 0:
+        same(gpu_host.linear_out_32(c["x"], c["w"], bias32=b32), want)
+
+
+def test_linear_single_vector_and_odd_sizes(gpu, restatement):
+    for (K, N, B) in ((4096, 4096, 1), (1024, 1000, 7), (77, 5, 1), (16, 16, 130)):
+        c = wl.linear_case(43, K, N, batch=B, out_shift=wl.ceil_log2(K) + 2, relu=1, bn=1)
+        want = restatement.linear(32, c["x"], c["w"], c["k"], c["lam"], **lin_kw(c))
+        same(gpu.linear(32, c["x"], c["w"], c["k"], c["lam"], **lin_kw(c)), want)
+        same(gpu.linear_out_32(c["x"], c["w"]), restatement.linear_out_32(c["x"], c["w"]))
+
+
+# ---- pooling and add -----------------------------------------------------------------------
+@pytest.mark.parametrize("geom", [
+    dict(kernel=(2, 2), strides=(2, 2), pads=(0, 0, 0, 0), out_hw=(7, 7)),
+    dict(kernel=(3, 3), strides=(2, 2), pads=(1, 1, 1, 1), out_hw=(7, 7)),
+    dict(kernel=(3, 2), strides=(3, 2), pads=(1, 0, 0, 0), out_hw=(5, 7)),
+])
+@pytest.mark.parametrize("C", [10, 64])
+def test_maxpool(geom, C, gpu, gpu_host, restatement):
+    rng = np.random.default_rng(51)
+    x = rng.integers(0, 256, size=(3, 14, 14, C), dtype=np.uint8)
+    want, want_after = restatement.maxpool(x, want_input_after=True, **geom)
+    same(gpu.maxpool(x, **geom), want)
+    same(gpu_host.maxpool(x, **geom), want)
+    got, got_after = gpu.maxpool(x, want_input_after=True, **geom)
+    same(got, want)
+    # only the columns the reference overwrites are compared: it leaves the rest untouched
+    same(got_after, want_after)
+
+
+@pytest.mark.parametrize("bits", [32, 64])
+@pytest.mark.parametrize("requant,lam,add,shift", [(0, 0, 0, 0), (1, 300, 128, 8), (1, -3, 5, 2),
+                                                   (1, 70000, -9, 11)])
+def test_avgpool(bits, requant, lam, add, shift, gpu, restatement):
+    rng = np.random.default_rng(52)
+    for C in (9, 32):
+        x = rng.integers(0, 256, size=(2, 14, 14, C), dtype=np.uint8)
+        for geom in (dict(kernel=(7, 7), strides=(7, 7), pads=(0, 0, 0, 0), out_hw=(2, 2)),
+                     dict(kernel=(3, 3), strides=(2, 2), pads=(1, 1, 1, 1), out_hw=(7, 7))):
+            kw = dict(lam=lam, out_shift=shift, out_add=add, requant=requant, **geom)
+            same(gpu.avgpool(bits, x, **kw), restatement.avgpool(bits, x, **kw))
+
+
+def test_avgpool_mobilenet_tail(gpu, restatement):
+    rng = np.random.default_rng(53)
+    x = rng.integers(0, 256, size=(5, 7, 7, 1024), dtype=np.uint8)
+    kw = dict(kernel=(7, 7), strides=(7, 7), pads=(0, 0, 0, 0), out_hw=(1, 1))
+    same(gpu.avgpool(32, x, **kw), restatement.avgpool(32, x, **kw))
+
+
+@pytest.mark.parametrize("m1,m2,shift", [(37, 91, 6), (1, 1, 0), (65535, 3, 4), (300, 500, 1)])
+def test_add(m1, m2, shift, gpu, gpu_host, restatement):
+    rng = np.random.default_rng(54)
+    for shape in ((2, 14, 13, 11), (4, 56, 56, 64)):
+        a = rng.integers(0, 256, size=shape, dtype=np.uint8)
+        b = rng.integers(0, 256, size=shape, dtype=np.uint8)
+        want = restatement.add(a, b, m1=m1, m2=m2, out_shift=shift)
+        same(gpu.add(a, b, m1=m1, m2=m2, out_shift=shift), want)
+    same(gpu_host.add(a, b, m1=m1, m2=m2, out_shift=shift), want)
+
+
+# ---- argument checking ---------------------------------------------------------------------
+def test_rejects_what_the_reference_leaves_undefined(gpu):
+    x = np.zeros((1, 8, 8, 16), np.uint8)
+    w = np.zeros((16, 16), np.int8)
+    k = np.ones(16, np.int32)
+    with pytest.raises(pulpnn.PulpNNError) as e:       # shift outside 0..31
+        gpu.pointwise(32, x, w, k, k, out_shift=40)
+    assert e.value.code == api.ERR_INVALID_ARG
+    wd = np.zeros((16, 3, 3), np.int8)
+    with pytest.raises(pulpnn.PulpNNError) as e:       # pad_left != kx/2
+        gpu.depthwise(32, x.transpose(0, 3, 1, 2).copy(), wd, k, k, out_hw=(8, 7), kernel=(3, 3),
+                      pads=(1, 1, 0, 1), strides=(1, 1))
+    assert e.value.code == api.ERR_UNSUPPORTED
+    with pytest.raises(pulpnn.PulpNNError) as e:       # in-place x pass would read pooled values
+        gpu.maxpool(x, out_hw=(8, 8), kernel=(3, 3), pads=(1, 1, 1, 1), strides=(1, 1))
+    assert e.value.code == api.ERR_UNSUPPORTED
