@@ -34,7 +34,7 @@ def test_mobilenet_every_layer(shift_bias, micro, restatement):
         got = _device_run(net, x, w.shape, w.dtype.type, n_layers=l + 1)
         assert np.array_equal(got, w), "layer %d (%s) differs" % (l, params[l]["name"])
     if shift_bias == 1:
-        assert np.count_nonzero(want[-3]) > want[-3].size // 4      # still alive at pw13
+        assert np.count_nonzero(want[-3]) > want[-3].size // 20     # still alive at pw13
         assert len(np.unique(want[-1])) > 100
     assert api.device_status() == 0
     # host buffers in and out give the same logits
