@@ -8,13 +8,13 @@
 // keeps weights as [ch_out][K], 32bit/src/pulp_nn_matmul.c:55-59, so both operands are K-major
 // exactly as they lie in memory).
 //
-// Structure of one CTA (192 threads, persistent over work units = (m-tile, n-tile, k-slice)):
+// Structure of one CTA (320 threads, persistent over work units = (m-tile, n-tile, k-slice)):
 //   warp 0, one lane   TMA producer: 128 x 128-byte tile of A and BN x 128-byte tile of W per
 //                      stage, 128-byte swizzle, completion on an mbarrier (no multicast)
 //   warp 1, one lane   issues tcgen05.mma.kind::i8 (M=128, N=BN, K=32 per instruction), operands
 //                      from shared-memory descriptors, accumulator in tensor memory; commits free
 //                      the stage and publish the accumulator
-//   warps 2..5         epilogue: tcgen05.ld the accumulator (lane = output row), add bias,
+//   warps 2..9         epilogue: tcgen05.ld the accumulator (lane = output row), add bias,
 //                      requantise with per-channel k/lambda held in shared memory, pack to bytes
 //                      and store 16 bytes at a time into the HWC output
 // Two accumulators live in tensor memory so that the epilogue of one tile overlaps the MMAs of
@@ -38,7 +38,8 @@ namespace {
 constexpr int BM = 128;            // rows per tile = TMEM lanes
 constexpr int BK = 128;            // bytes of K per stage = one 128-byte swizzle atom
 constexpr int UMMA_K = 32;         // K per tcgen05.mma for 8-bit operands
-constexpr int NUM_THREADS = 192;
+constexpr int EPI_WARPS = 8;      // two per TMEM lane quarter
+constexpr int NUM_THREADS = 64 + 32 * EPI_WARPS;
 constexpr unsigned long long WAIT_LIMIT_NS = 1000000000ull;
 
 // status codes (or-ed into the global status word)
@@ -168,10 +169,6 @@ __host__ __device__ constexpr uint32_t idesc_u8s8(int n)
   return (2u << 4) | (0u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 }
 
-__device__ __forceinline__ unsigned pack4_u8(int a, int b, int c, int d)
-{
-  return (unsigned)a | ((unsigned)b << 8) | ((unsigned)c << 16) | ((unsigned)d << 24);
-}
 
 // ---- kernel parameters ---------------------------------------------------------------------
 struct TcParams {
@@ -215,7 +212,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    for (int b = 0; b < 2; b++) { mbar_init(&tmem_full[b], 1); mbar_init(&tmem_empty[b], 4); }
+    for (int b = 0; b < 2; b++) { mbar_init(&tmem_full[b], 1); mbar_init(&tmem_empty[b], EPI_WARPS); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -297,29 +294,34 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       }
     }
   } else {
-    // ------------------------------ epilogue (warps 2..5) ------------------------------------
-    const int quad = warp & 3;                 // TMEM lanes 32*quad .. 32*quad+31
-    // each epilogue warp keeps its own copy of the per-channel parameters, so staging them needs
-    // no barrier between warps (a warp that gave up can never strand the others)
-    uint8_t *params = params_all + quad * L::PARAM_BYTES;
+    // ------------------------------ epilogue (warps 2..9) ------------------------------------
+    // A warp may only read the 32 TMEM lanes 32*(warp%4)..+31. Two warps share each lane quarter
+    // and split the accumulator's 32-column chunks between them (even chunks / odd chunks).
+    const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;
+    constexpr int HALF_COLS = BN_TILE / 2;     // columns this warp is responsible for
+    // each epilogue warp keeps its own copy of the per-channel parameters of ITS columns, so
+    // staging them needs no barrier between warps (a warp that gave up can never strand the others)
+    uint8_t *params = params_all + (warp - 2) * (L::PARAM_BYTES / 2);
     int acc = 0; uint32_t acc_phase = 0;
     const Epilogue &e = g.epi;
     int *p_bias = reinterpret_cast<int *>(params);                 // non-BN modes
     int *p_k32 = reinterpret_cast<int *>(params);                  // EPI_BN32: k, lambda'
-    int *p_l32 = p_k32 + BN_TILE;
+    int *p_l32 = p_k32 + HALF_COLS;
     long long *p_k64 = reinterpret_cast<long long *>(params);      // EPI_BN64
-    long long *p_l64 = p_k64 + BN_TILE;
+    long long *p_l64 = p_k64 + HALF_COLS;
     int staged_nt = -1;
     for (int u = blockIdx.x; u < units; u += gridDim.x) {
       const int nt = u % g.n_tiles, r = u / g.n_tiles;
       const int mt = r % g.m_tiles, ks = r / g.m_tiles;
       const int n0 = nt * BN_TILE;
       if (!PARTIAL && nt != staged_nt) {
-        // per-channel parameters of this n-tile -> shared memory. The bias is folded into
+        // per-channel parameters of this warp's columns -> shared memory. The bias is folded into
         // lambda: k*(acc+b)+lambda == k*acc + (k*b+lambda) in wrap-around arithmetic.
+        // Local slot i holds column (i/32)*64 + half*32 + i%32 of the tile.
         __syncwarp();
-        for (int i = lane; i < BN_TILE; i += 32) {
-          const int n = n0 + i;
+        for (int i = lane; i < HALF_COLS; i += 32) {
+          const int n = n0 + (i >> 5) * 64 + half * 32 + (i & 31);
           const bool v = n < g.N;
           if (MODE == EPI_BN32) {
             const int k = v ? __ldg(reinterpret_cast<const int *>(e.k) + n) : 0;
@@ -348,8 +350,9 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       const bool row_ok = m < g.M;
       const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN_TILE);
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN_TILE; c0 += 32) {
-        if (n0 + c0 >= g.N) break;             // uniform across the warp
+      for (int lc = 0; lc < HALF_COLS; lc += 32) {   // lc: offset inside this warp's parameter copy
+        const int c0 = (lc >> 5) * 64 + half * 32;   // column offset inside the tile
+        if (n0 + c0 >= g.N) break;                   // uniform across the warp
         uint32_t v[32];
         tmem_ld_32(t_row + (uint32_t)c0, v);
         tmem_wait_ld();
@@ -363,14 +366,17 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 if (n0 + c0 + i < g.N) {
                   int4 o;
                   o.x = (int)v[i]; o.y = (int)v[i + 1]; o.z = (int)v[i + 2]; o.w = (int)v[i + 3];
-                  if (!PARTIAL) { o.x += p_bias[c0 + i]; o.y += p_bias[c0 + i + 1]; o.z += p_bias[c0 + i + 2]; o.w += p_bias[c0 + i + 3]; }
+                  if (!PARTIAL) {
+                    const int4 bb = *reinterpret_cast<const int4 *>(p_bias + lc + i);
+                    o.x += bb.x; o.y += bb.y; o.z += bb.z; o.w += bb.w;
+                  }
                   *reinterpret_cast<int4 *>(orow + i) = o;
                 }
               }
             } else {
 #pragma unroll
               for (int i = 0; i < 32; i++)
-                if (n0 + c0 + i < g.N) orow[i] = (int)v[i] + (PARTIAL ? 0 : p_bias[c0 + i]);
+                if (n0 + c0 + i < g.N) orow[i] = (int)v[i] + (PARTIAL ? 0 : p_bias[lc + i]);
             }
           }
         } else {
@@ -378,20 +384,27 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 #pragma unroll
           for (int i = 0; i < 32; i += 4) {
             int q[4];
+            if (MODE == EPI_BN32) {
+              const int4 kk = *reinterpret_cast<const int4 *>(p_k32 + lc + i);
+              const int4 ll = *reinterpret_cast<const int4 *>(p_l32 + lc + i);
+              q[0] = (int)((unsigned)kk.x * v[i + 0] + (unsigned)ll.x) >> e.shift;
+              q[1] = (int)((unsigned)kk.y * v[i + 1] + (unsigned)ll.y) >> e.shift;
+              q[2] = (int)((unsigned)kk.z * v[i + 2] + (unsigned)ll.z) >> e.shift;
+              q[3] = (int)((unsigned)kk.w * v[i + 3] + (unsigned)ll.w) >> e.shift;
+            } else {
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-              const int a = (int)v[i + j];
-              if (MODE == EPI_BN32)
-                q[j] = clip_u8((int)((unsigned)p_k32[c0 + i + j] * (unsigned)a + (unsigned)p_l32[c0 + i + j]) >> e.shift);
-              else if (MODE == EPI_BN64)
-                q[j] = clip_u8((int)((long long)((unsigned long long)p_k64[c0 + i + j] * (unsigned long long)(long long)a +
-                                                 (unsigned long long)p_l64[c0 + i + j]) >> e.shift));
-              else if (MODE == EPI_MULT)
-                q[j] = clip_u8((int)(short)((int)((unsigned)e.out_mult * (unsigned)(a + p_bias[c0 + i + j])) >> e.shift));
-              else
-                q[j] = clip_u8((a + p_bias[c0 + i + j]) >> e.shift);
+              for (int j = 0; j < 4; j++) {
+                const int a = (int)v[i + j];
+                if (MODE == EPI_BN64)
+                  q[j] = (int)((long long)((unsigned long long)p_k64[lc + i + j] * (unsigned long long)(long long)a +
+                                           (unsigned long long)p_l64[lc + i + j]) >> e.shift);
+                else if (MODE == EPI_MULT)
+                  q[j] = (int)(short)((int)((unsigned)e.out_mult * (unsigned)(a + p_bias[lc + i + j])) >> e.shift);
+                else
+                  q[j] = (a + p_bias[lc + i + j]) >> e.shift;
+              }
             }
-            w[i >> 2] = pack4_u8(q[0], q[1], q[2], q[3]);
+            w[i >> 2] = pack4_sat_u8(q[0], q[1], q[2], q[3]);
           }
           if (row_ok) {
             uint8_t *orow = reinterpret_cast<uint8_t *>(g.out) + (size_t)m * g.N + n0 + c0;

@@ -74,6 +74,16 @@ __device__ __forceinline__ int requant_kl(int acc, long long k, long long l, int
   }
 }
 
+// Clamp four int32 values to [0,255] and pack them, a in the lowest byte. cvt.pack.sat converts
+// two values per instruction: d[7:0] = sat(second), d[15:8] = sat(first), d[31:16] = third[15:0].
+__device__ __forceinline__ unsigned pack4_sat_u8(int a, int b, int c, int d)
+{
+  unsigned hi, r;
+  asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(d), "r"(c), "r"(0));
+  asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(b), "r"(a), "r"(hi));
+  return r;
+}
+
 // u8 x s8 dot product of four byte lanes
 __device__ __forceinline__ int dp4a_us(unsigned a_u8x4, int b_s8x4, int c)
 {
@@ -163,9 +173,13 @@ class Stager {
 // ---------------------------------------------------------------------------------------------
 bool launch_conv(Context &c, const ConvProblem &p);             // picks tensor-core or generic
 bool launch_conv_generic(Context &c, const ConvProblem &p);
+bool conv_smallcin_supported(const ConvProblem &p);
+bool launch_conv_smallcin(Context &c, const ConvProblem &p);
 bool igemm_tc_supported(const Context &c, const ConvProblem &p);
 bool launch_igemm_tc(Context &c, const ConvProblem &p);
 bool launch_depthwise(Context &c, const DepthwiseProblem &p);
+bool depthwise_hwc3x3_supported(const DepthwiseProblem &p);
+bool launch_depthwise_hwc3x3(Context &c, const DepthwiseProblem &p);
 bool launch_maxpool(Context &c, const PoolProblem &p, uint8_t *clobber_in);
 bool launch_avgpool(Context &c, const PoolProblem &p);
 bool launch_add(Context &c, const uint8_t *a, const uint8_t *b, uint8_t *out, size_t n, int m1,
