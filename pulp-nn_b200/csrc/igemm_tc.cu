@@ -9,18 +9,22 @@
 // exactly as they lie in memory).
 //
 // Structure of one CTA (320 threads, persistent over work units = (m-tile, n-tile, k-slice)):
-//   warp 0, one lane   TMA producer: 128 x 128-byte tile of A and BN x 128-byte tile of W per
-//                      stage, 128-byte swizzle, completion on an mbarrier (no multicast)
+//   warp 0, one lane   TMA producer: a 128-row tile of A and a BN-row tile of W per pipeline stage,
+//                      BKB bytes of K wide (32, 64 or 128, matching swizzle), completion on an
+//                      mbarrier (no multicast). TMA fetches the whole box from L2 even where it
+//                      lies outside the tensor, so the box is never wider than K needs. When one
+//                      n-tile covers all of W and it is small, W is loaded ONCE per CTA and stays
+//                      in shared memory; the ring then carries A only.
 //   warp 1, one lane   issues tcgen05.mma.kind::i8 (M=128, N=BN, K=32 per instruction), operands
 //                      from shared-memory descriptors, accumulator in tensor memory; commits free
 //                      the stage and publish the accumulator
 //   warps 2..9         epilogue: tcgen05.ld the accumulator (lane = output row), add bias,
 //                      requantise with per-channel k/lambda held in shared memory, pack to bytes
-//                      and store 16 bytes at a time into the HWC output
-// Two accumulators live in tensor memory so that the epilogue of one tile overlaps the MMAs of
-// the next. Integer accumulation is associative, so splitting K over several CTAs (used when a
-// problem has too few tiles to fill the GPU) gives bit-identical sums; partial sums then go to a
-// scratch buffer and a second kernel adds them and requantises.
+//                      and store 32 bytes at a time into the HWC output
+// All 512 columns of tensor memory are used as a ring of 512/BN accumulators, so the MMA issuer runs
+// several tiles ahead of the epilogue. Integer accumulation is associative, so splitting K over
+// several CTAs (used when a problem has too few tiles to fill the GPU) gives bit-identical sums;
+// partial sums then go to a scratch buffer and a second kernel adds them and requantises.
 //
 // Every wait on an mbarrier is bounded: after about a second the waiting thread raises a flag in
 // shared memory, records a code in a global status word and all roles fall through to the common
@@ -36,14 +40,16 @@ namespace pulpnn {
 namespace {
 
 constexpr int BM = 128;            // rows per tile = TMEM lanes
-constexpr int BK = 128;            // bytes of K per stage = one 128-byte swizzle atom
 constexpr int UMMA_K = 32;         // K per tcgen05.mma for 8-bit operands
-constexpr int EPI_WARPS = 8;      // two per TMEM lane quarter
+constexpr int EPI_WARPS = 8;       // two per TMEM lane quarter
 constexpr int NUM_THREADS = 64 + 32 * EPI_WARPS;
+constexpr int MAX_STAGES = 12;
+constexpr int PIPE_BYTES = 192 * 1024;   // operand ring (+ resident W) per CTA
 constexpr unsigned long long WAIT_LIMIT_NS = 1000000000ull;
 
 // status codes (or-ed into the global status word)
-constexpr int ST_PRODUCER = 0x1, ST_MMA_FULL = 0x2, ST_MMA_TMEM = 0x4, ST_EPILOGUE = 0x8, ST_DRAIN = 0x10;
+constexpr int ST_PRODUCER = 0x1, ST_MMA_FULL = 0x2, ST_MMA_TMEM = 0x4, ST_EPILOGUE = 0x8, ST_DRAIN = 0x10,
+              ST_MMA_WRES = 0x20;
 
 // ---- PTX wrappers --------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void *p)
@@ -149,17 +155,20 @@ __device__ __forceinline__ void tmem_ld_32(uint32_t taddr, uint32_t (&r)[32])
 }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// Shared-memory matrix descriptor of a K-major tile stored with the 128-byte swizzle: rows are
-// 128 bytes apart, groups of 8 rows 1024 bytes apart (stride byte offset), descriptor version 1,
-// layout type 2 = SWIZZLE_128B. Addresses and offsets are encoded in 16-byte units.
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr)
+// Shared-memory matrix descriptor of a K-major tile whose rows are BKB bytes long and stored with
+// the BKB-byte swizzle (32, 64 or 128): groups of 8 rows are 8*BKB bytes apart (stride byte
+// offset), descriptor version 1, layout type 6 / 4 / 2 = SWIZZLE_32B / 64B / 128B. Addresses and
+// offsets are encoded in 16-byte units.
+template <int BKB>
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr)
 {
+  constexpr uint64_t layout = BKB == 128 ? 2 : (BKB == 64 ? 4 : 6);
   uint64_t d = 0;
   d |= (uint64_t)((saddr & 0x3ffffu) >> 4);          // start address
   d |= (uint64_t)1 << 16;                            // leading byte offset (unused with swizzle)
-  d |= (uint64_t)(1024 >> 4) << 32;                  // stride byte offset
+  d |= (uint64_t)((8 * BKB) >> 4) << 32;             // stride byte offset
   d |= (uint64_t)1 << 46;                            // version
-  d |= (uint64_t)2 << 61;                            // SWIZZLE_128B
+  d |= layout << 61;
   return d;
 }
 // Instruction descriptor: D = s32 (2 at bit 4), A = unsigned 8-bit (0 at bit 7), B = signed 8-bit
@@ -169,50 +178,61 @@ __host__ __device__ constexpr uint32_t idesc_u8s8(int n)
   return (2u << 4) | (0u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 }
 
-
 // ---- kernel parameters ---------------------------------------------------------------------
 struct TcParams {
   void *out;             // uint8 [M][N], int32 [M][N] (EPI_RAW32) or int32 partials [S][M][N]
   Epilogue epi;
   int M, N, K;
   int m_tiles, n_tiles, k_slices, slabs_per_slice, total_slabs;
-  int vec_store;         // 1: rows of the output can be written with 16-byte stores
+  int vec_store;         // 2: 32-byte stores, 1: 16-byte stores, 0: scalar stores
+  int w_resident;        // 1: all of W sits in shared memory for the CTA's lifetime
+  int n_stages;          // depth of the operand ring
   int *status;
 };
 
-template <int BN_TILE, int STAGES>
+template <int BN_TILE>
 struct SmemLayout {
-  static constexpr int A_BYTES = BM * BK;
-  static constexpr int B_BYTES = BN_TILE * BK;
-  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int PARAM_BYTES = BN_TILE * 16;    // k and lambda, up to 8 bytes each; one copy per epilogue warp
-  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES + 4 * PARAM_BYTES;
-  static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;   // barriers + slack for 1024-byte alignment
+  static constexpr int PARAM_BYTES = BN_TILE * 16;    // k and lambda, up to 8 bytes each, split over 8 warps
+  static constexpr int PARAM_OFFSET = PIPE_BYTES;
+  static constexpr int BAR_OFFSET = PARAM_OFFSET + 4 * PARAM_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + 512 + 1024;   // barriers + slack for 1024-byte alignment
+  // accumulators in tensor memory: all 512 columns are used, so a narrow tile gets a deep ring
+  static constexpr int NUM_ACC = 512 / BN_TILE;
 };
 
 // MODE: the final epilogue; PARTIAL: store raw int32 partial sums instead (split-K)
-template <int MODE, int BN_TILE, int STAGES, bool PARTIAL>
+template <int MODE, int BN_TILE, int BKB, bool PARTIAL>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                 const TcParams g)
 {
-  using L = SmemLayout<BN_TILE, STAGES>;
+  using L = SmemLayout<BN_TILE>;
+  constexpr int A_BYTES = BM * BKB, B_BYTES = BN_TILE * BKB;
+  constexpr int NUM_ACC = L::NUM_ACC;
+  constexpr uint32_t TMEM_COLS = 512;
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint8_t *params_all = smem + STAGES * L::STAGE_BYTES;
+  uint8_t *params_all = smem + L::PARAM_OFFSET;
   uint64_t *full_bar = reinterpret_cast<uint64_t *>(smem + L::BAR_OFFSET);
-  uint64_t *empty_bar = full_bar + STAGES;
-  uint64_t *tmem_full = empty_bar + STAGES;
-  uint64_t *tmem_empty = tmem_full + 2;
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tmem_empty + 2);
+  uint64_t *empty_bar = full_bar + MAX_STAGES;
+  uint64_t *tmem_full = empty_bar + MAX_STAGES;
+  uint64_t *tmem_empty = tmem_full + NUM_ACC;
+  uint64_t *wres_bar = tmem_empty + NUM_ACC;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(wres_bar + 1);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
+  // operand ring: [resident W: total_slabs * B_BYTES][stage 0][stage 1]...
+  const int wres_bytes = g.w_resident ? g.total_slabs * B_BYTES : 0;
+  const int stage_bytes = g.w_resident ? A_BYTES : A_BYTES + B_BYTES;
+  uint8_t *ring = smem + wres_bytes;
+  const int n_stages = g.n_stages;
+
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  constexpr uint32_t TMEM_COLS = 2 * BN_TILE < 32 ? 32 : 2 * BN_TILE;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    for (int b = 0; b < 2; b++) { mbar_init(&tmem_full[b], 1); mbar_init(&tmem_empty[b], EPI_WARPS); }
+    for (int s = 0; s < MAX_STAGES; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int b = 0; b < NUM_ACC; b++) { mbar_init(&tmem_full[b], 1); mbar_init(&tmem_empty[b], EPI_WARPS); }
+    mbar_init(wres_bar, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -230,6 +250,10 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0; int issued = 0;
       bool ok = true;
+      if (g.w_resident) {
+        mbar_arrive_expect_tx(wres_bar, (uint32_t)wres_bytes);
+        for (int s = 0; s < g.total_slabs; s++) tma_load_2d(smem + s * B_BYTES, &map_b, wres_bar, s * BKB, 0);
+      }
       for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
         const int nt = u % g.n_tiles, r = u / g.n_tiles;
         const int mt = r % g.m_tiles, ks = r / g.m_tiles;
@@ -237,22 +261,28 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         const int slab1 = min(slab0 + g.slabs_per_slice, g.total_slabs);
         for (int s = slab0; s < slab1; s++) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, g.status, ST_PRODUCER)) { ok = false; break; }
-          uint8_t *a_dst = smem + stage * L::STAGE_BYTES;
-          mbar_arrive_expect_tx(&full_bar[stage], L::STAGE_BYTES);
-          tma_load_2d(a_dst, &map_a, &full_bar[stage], s * BK, mt * BM);
-          tma_load_2d(a_dst + L::A_BYTES, &map_b, &full_bar[stage], s * BK, nt * BN_TILE);
+          uint8_t *a_dst = ring + stage * stage_bytes;
+          mbar_arrive_expect_tx(&full_bar[stage], (uint32_t)stage_bytes);
+          tma_load_2d(a_dst, &map_a, &full_bar[stage], s * BKB, mt * BM);
+          if (!g.w_resident) tma_load_2d(a_dst + A_BYTES, &map_b, &full_bar[stage], s * BKB, nt * BN_TILE);
           issued++;
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          if (++stage == n_stages) { stage = 0; phase ^= 1; }
         }
       }
       if (*abort_flag) {
         // something gave up: make sure no TMA write is still in flight into this CTA's memory
-        const int pending = issued < STAGES ? issued : STAGES;
+        const int pending = issued < n_stages ? issued : n_stages;
         for (int i = 0; i < pending; i++) {
           int st = stage - 1 - i; uint32_t ph = phase;
-          if (st < 0) { st += STAGES; ph ^= 1; }
+          if (st < 0) { st += n_stages; ph ^= 1; }
           const unsigned long long t0 = global_ns();
           while (!mbar_try_wait(&full_bar[st], ph)) {
+            if (global_ns() - t0 > WAIT_LIMIT_NS) { if (g.status) atomicOr(g.status, ST_DRAIN); break; }
+          }
+        }
+        if (g.w_resident) {
+          const unsigned long long t0 = global_ns();
+          while (!mbar_try_wait(wres_bar, 0)) {
             if (global_ns() - t0 > WAIT_LIMIT_NS) { if (g.status) atomicOr(g.status, ST_DRAIN); break; }
           }
         }
@@ -264,6 +294,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       constexpr uint32_t idesc = idesc_u8s8(BN_TILE);
       int stage = 0; uint32_t phase = 0; int acc = 0; uint32_t acc_phase = 0;
       bool ok = true;
+      if (g.w_resident) ok = mbar_wait(wres_bar, 0, abort_flag, g.status, ST_MMA_WRES);
       for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
         const int r = u / g.n_tiles;
         const int ks = r / g.m_tiles;
@@ -275,10 +306,11 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         for (int s = slab0; s < slab1; s++) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag, g.status, ST_MMA_FULL)) { ok = false; break; }
           tcgen05_fence_after();
-          const uint32_t a_addr = smem_u32(smem + stage * L::STAGE_BYTES);
-          const uint64_t da = smem_desc_sw128(a_addr), db = smem_desc_sw128(a_addr + L::A_BYTES);
+          const uint32_t a_addr = smem_u32(ring + stage * stage_bytes);
+          const uint32_t b_addr = g.w_resident ? smem_u32(smem + s * B_BYTES) : a_addr + A_BYTES;
+          const uint64_t da = smem_desc<BKB>(a_addr), db = smem_desc<BKB>(b_addr);
           // bytes of this slab that lie inside K; the rest of the tile is zero-filled by TMA
-          const int kbytes = min(BK, g.K - s * BK);
+          const int kbytes = min(BKB, g.K - s * BKB);
           const int n_mma = (kbytes + UMMA_K - 1) / UMMA_K;
           for (int j = 0; j < n_mma; j++) {
             // advancing K inside the swizzle atom = advancing the start address (16-byte units)
@@ -286,11 +318,11 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             umma_i8(d_tmem, da + adv, db + adv, idesc, (s > slab0 || j > 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);      // stage reusable once these MMAs have read it
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          if (++stage == n_stages) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
         umma_commit(&tmem_full[acc]);          // accumulator complete
-        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        if (++acc == NUM_ACC) { acc = 0; acc_phase ^= 1; }
       }
     }
   } else {
@@ -408,7 +440,13 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           }
           if (row_ok) {
             uint8_t *orow = reinterpret_cast<uint8_t *>(g.out) + (size_t)m * g.N + n0 + c0;
-            if (g.vec_store) {
+            if (g.vec_store == 2) {
+              // one full 32-byte sector per lane and instruction
+              asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                           ::"l"(orow), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]),
+                             "r"(w[6]), "r"(w[7])
+                           : "memory");
+            } else if (g.vec_store == 1) {
               if (n0 + c0 < g.N) *reinterpret_cast<uint4 *>(orow) = make_uint4(w[0], w[1], w[2], w[3]);
               if (n0 + c0 + 16 < g.N) *reinterpret_cast<uint4 *>(orow + 16) = make_uint4(w[4], w[5], w[6], w[7]);
             } else {
@@ -422,7 +460,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty[acc]);
-      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      if (++acc == NUM_ACC) { acc = 0; acc_phase ^= 1; }
     }
   }
 
@@ -475,28 +513,30 @@ EncodeTiledFn encode_fn()
   return fn;
 }
 
-// [rows][K] byte matrix, K contiguous; box = 128 bytes of K x box_rows rows, 128-byte swizzle.
+// [rows][K] byte matrix, K contiguous; box = bkb bytes of K x box_rows rows, bkb-byte swizzle.
 // Elements outside the matrix read as zero.
-bool make_map(CUtensorMap *map, const void *base, int rows, int K, int box_rows)
+bool make_map(CUtensorMap *map, const void *base, int rows, int K, int box_rows, int bkb)
 {
   EncodeTiledFn enc = encode_fn();
   if (!enc) { set_error(PULPNN_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver"); return false; }
   cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)K};
-  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t box[2] = {(cuuint32_t)bkb, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapSwizzle sw = bkb == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                              : (bkb == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) { set_error(PULPNN_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r); return false; }
   return true;
 }
 
-template <int MODE, int BN_TILE, int STAGES, bool PARTIAL>
+template <int MODE, int BN_TILE, int BKB, bool PARTIAL>
 bool launch_cfg(Context &c, const CUtensorMap &ma, const CUtensorMap &mb, const TcParams &g, int grid)
 {
-  using L = SmemLayout<BN_TILE, STAGES>;
-  auto kern = igemm_tc_kernel<MODE, BN_TILE, STAGES, PARTIAL>;
+  using L = SmemLayout<BN_TILE>;
+  auto kern = igemm_tc_kernel<MODE, BN_TILE, BKB, PARTIAL>;
   static bool attr_set = false;     // per instantiation
   if (!attr_set) {
     if (!cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL),
@@ -504,29 +544,37 @@ bool launch_cfg(Context &c, const CUtensorMap &ma, const CUtensorMap &mb, const 
       return false;
     attr_set = true;
   }
+  // every configuration asks for more than half of an SM's shared memory, so exactly one CTA (and
+  // its 512 tensor-memory columns) lives on an SM
   kern<<<grid, NUM_THREADS, L::TOTAL, c.stream>>>(ma, mb, g);
   count_launch();
   return cuda_ok(cudaGetLastError(), "igemm_tc launch");
 }
 
-template <int MODE, bool PARTIAL>
-bool launch_bn(Context &c, const CUtensorMap &ma, const CUtensorMap &mb, const TcParams &g, int bn, int grid)
+template <int MODE, int BN_TILE, bool PARTIAL>
+bool launch_bk(Context &c, const CUtensorMap &ma, const CUtensorMap &mb, const TcParams &g, int bkb, int grid)
 {
-  // stage counts keep every configuration above half of an SM's shared memory, so exactly one
-  // CTA (and its 2*BN tensor-memory columns) lives on an SM
-  if (bn == 64)  return launch_cfg<MODE, 64, 6, PARTIAL>(c, ma, mb, g, grid);
-  if (bn == 128) return launch_cfg<MODE, 128, 5, PARTIAL>(c, ma, mb, g, grid);
-  return launch_cfg<MODE, 256, 4, PARTIAL>(c, ma, mb, g, grid);
+  if (bkb == 32) return launch_cfg<MODE, BN_TILE, 32, PARTIAL>(c, ma, mb, g, grid);
+  if (bkb == 64) return launch_cfg<MODE, BN_TILE, 64, PARTIAL>(c, ma, mb, g, grid);
+  return launch_cfg<MODE, BN_TILE, 128, PARTIAL>(c, ma, mb, g, grid);
 }
 
-bool launch_final(Context &c, const CUtensorMap &ma, const CUtensorMap &mb, const TcParams &g, int bn, int grid)
+template <int MODE, bool PARTIAL>
+bool launch_bn(Context &c, const CUtensorMap &ma, const CUtensorMap &mb, const TcParams &g, int bn, int bkb, int grid)
+{
+  if (bn == 64)  return launch_bk<MODE, 64, PARTIAL>(c, ma, mb, g, bkb, grid);
+  if (bn == 128) return launch_bk<MODE, 128, PARTIAL>(c, ma, mb, g, bkb, grid);
+  return launch_bk<MODE, 256, PARTIAL>(c, ma, mb, g, bkb, grid);
+}
+
+bool launch_final(Context &c, const CUtensorMap &ma, const CUtensorMap &mb, const TcParams &g, int bn, int bkb, int grid)
 {
   switch (g.epi.mode) {
-    case EPI_NONE: return launch_bn<EPI_NONE, false>(c, ma, mb, g, bn, grid);
-    case EPI_MULT: return launch_bn<EPI_MULT, false>(c, ma, mb, g, bn, grid);
-    case EPI_BN32: return launch_bn<EPI_BN32, false>(c, ma, mb, g, bn, grid);
-    case EPI_BN64: return launch_bn<EPI_BN64, false>(c, ma, mb, g, bn, grid);
-    default:       return launch_bn<EPI_RAW32, false>(c, ma, mb, g, bn, grid);
+    case EPI_NONE: return launch_bn<EPI_NONE, false>(c, ma, mb, g, bn, bkb, grid);
+    case EPI_MULT: return launch_bn<EPI_MULT, false>(c, ma, mb, g, bn, bkb, grid);
+    case EPI_BN32: return launch_bn<EPI_BN32, false>(c, ma, mb, g, bn, bkb, grid);
+    case EPI_BN64: return launch_bn<EPI_BN64, false>(c, ma, mb, g, bn, bkb, grid);
+    default:       return launch_bn<EPI_RAW32, false>(c, ma, mb, g, bn, bkb, grid);
   }
 }
 
@@ -550,9 +598,14 @@ bool launch_igemm_tc(Context &c, const ConvProblem &p)
   g.M = p.B * p.Ho * p.Wo; g.N = p.Cout; g.K = p.Cin;
   g.epi = p.epi;
   const int bn = g.N <= 64 ? 64 : (g.N <= 128 ? 128 : 256);
+  // K-slab width: the narrowest box that does not fetch bytes beyond K; wider boxes for long K
+  int bkb = 128;
+  if (g.K <= 32) bkb = 32;
+  else if (g.K <= 64) bkb = 64;
+  else if (g.K < 128 && g.K % 64 != 0) bkb = 32;       // 80, 96, 112: no padded fetch with 32-byte slabs
   g.m_tiles = (g.M + BM - 1) / BM;
   g.n_tiles = (g.N + bn - 1) / bn;
-  g.total_slabs = (g.K + BK - 1) / BK;
+  g.total_slabs = (g.K + bkb - 1) / bkb;
   const int sms = c.sm_count > 0 ? c.sm_count : 148;
 
   // split K only when the tiles alone cannot occupy the GPU and there is enough K to share
@@ -569,6 +622,16 @@ bool launch_igemm_tc(Context &c, const ConvProblem &p)
   g.slabs_per_slice = (g.total_slabs + slices - 1) / slices;
   g.k_slices = (g.total_slabs + g.slabs_per_slice - 1) / g.slabs_per_slice;
 
+  // W stays in shared memory when one n-tile covers it, K is not split and it leaves room for at
+  // least four stages of A
+  const int a_bytes = BM * bkb, b_bytes = bn * bkb;
+  const long long wres = (long long)g.total_slabs * b_bytes;
+  g.w_resident = (g.n_tiles == 1 && g.k_slices == 1 && wres + 4LL * a_bytes <= PIPE_BYTES) ? 1 : 0;
+  const int stage_bytes = g.w_resident ? a_bytes : a_bytes + b_bytes;
+  int n_stages = (int)((PIPE_BYTES - (g.w_resident ? wres : 0)) / stage_bytes);
+  if (n_stages > MAX_STAGES) n_stages = MAX_STAGES;
+  g.n_stages = n_stages;
+
   if (!c.status_word) {
     if (!cuda_ok(cudaMalloc(&c.status_word, sizeof(int)), "cudaMalloc(status)")) return false;
     if (!cuda_ok(cudaMemsetAsync(c.status_word, 0, sizeof(int), c.stream), "cudaMemset(status)")) return false;
@@ -576,8 +639,8 @@ bool launch_igemm_tc(Context &c, const ConvProblem &p)
   g.status = c.status_word;
 
   CUtensorMap ma, mb;
-  if (!make_map(&ma, p.in, g.M, g.K, BM)) return false;
-  if (!make_map(&mb, p.w, g.N, g.K, bn)) return false;
+  if (!make_map(&ma, p.in, g.M, g.K, BM, bkb)) return false;
+  if (!make_map(&mb, p.w, g.N, g.K, bn, bkb)) return false;
 
   const int units = tiles * g.k_slices;
   const int grid = units < sms ? units : sms;
@@ -587,7 +650,8 @@ bool launch_igemm_tc(Context &c, const ConvProblem &p)
     g.out = p.out;
     const int align = raw ? 4 : 16;
     g.vec_store = (g.N % align == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
-    return launch_final(c, ma, mb, g, bn, grid);
+    if (!raw && g.vec_store && g.N % 32 == 0 && (reinterpret_cast<uintptr_t>(p.out) & 31) == 0) g.vec_store = 2;
+    return launch_final(c, ma, mb, g, bn, bkb, grid);
   }
   const size_t part_bytes = (size_t)g.k_slices * g.M * g.N * sizeof(int);
   int *partials = static_cast<int *>(ctx_scratch(c, part_bytes));
@@ -595,7 +659,7 @@ bool launch_igemm_tc(Context &c, const ConvProblem &p)
   g.out = partials;
   g.vec_store = (g.N % 4 == 0);
   // partial sums need no epilogue mode: one instantiation serves them all
-  if (!launch_bn<EPI_NONE, true>(c, ma, mb, g, bn, grid)) return false;
+  if (!launch_bn<EPI_NONE, true>(c, ma, mb, g, bn, bkb, grid)) return false;
   const size_t total = (size_t)g.M * g.N;
   const unsigned blocks = (unsigned)((total + 255) / 256 < (size_t)sms * 8 ? (total + 255) / 256 : (size_t)sms * 8);
   switch (p.epi.mode) {
