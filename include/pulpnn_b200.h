@@ -147,6 +147,33 @@ int  pulpnn_get_option(int option);
 PULPNN_DECLARE_TREE(_bn32, int32_t)
 PULPNN_DECLARE_TREE(_bn64, int64_t)
 
+/*
+ * pulpnn_linear_out_32_static_scratch -- no counterpart in the reference.
+ *
+ * The arithmetic of pulp_nn_linear_out_32 (int32 accumulators, bias read as int32 words, no
+ * requantisation) for n_vectors input vectors, computed with K split over k_slices groups of
+ * CTAs, for callers that must not allocate: a service that has given all free device memory to
+ * its own pool, or a deployment with a fixed, audited memory budget, cannot have a library call
+ * cudaMalloc behind its back (the ordinary split-K path does, the first time and whenever a
+ * larger problem arrives). Here the partial sums live in a 4 MiB array that is part of the
+ * library image (every GPU that loads the library holds it until the process exits), and the
+ * call uses no cudaMalloc, cudaFree or any other allocating routine.
+ *
+ *  - All four buffers must be DEVICE memory, 16-byte aligned (host buffers would need staging
+ *    memory); bias may be NULL; dim_vec must be a multiple of 16.
+ *  - Limit: k_slices * n_vectors * num_o_neurons <= 1048576 partial sums (k_slices >= 2, and
+ *    dim_vec long enough to split); anything larger is refused with PULPNN_ERR_UNSUPPORTED.
+ *  - The first call on a device looks up the array's device address; make that first call
+ *    before any stream capture is begun.
+ *  - Every call shares the one array, which keeps the previous call's contents. Nothing in it
+ *    has to start at zero (each call writes every partial sum it later reads), but two calls
+ *    whose kernels overlap on the GPU -- different streams, different host threads -- race.
+ *  - Enqueues on the calling thread's stream and returns a status (PULPNN_OK or an error code).
+ */
+int pulpnn_linear_out_32_static_scratch(const uint8_t *pInBuffer, const int32_t *bias,
+                                        int32_t *pOutBuffer, const int8_t *pWeights, int dim_vec,
+                                        int num_o_neurons, int n_vectors, int k_slices);
+
 /* ---- sequential network runner --------------------------------------------
  * The reference is a kernel library; its user chains the calls. This runner is
  * that chain for one GPU: layers are appended in order, parameters are copied

@@ -206,6 +206,22 @@ def pulp_nn_add(bits, Im_in_1, Im_in_2, Im_out, out_mult1, out_mult2, out_shift,
     _check()
 
 
+def pulpnn_linear_out_32_static_scratch(pInBuffer, bias, pOutBuffer, pWeights, dim_vec,
+                                        num_o_neurons, n_vectors, k_slices):
+    """pulp_nn_linear_out_32 arithmetic with split K for callers that may not allocate device
+    memory: the partial sums go to a 4 MiB array built into the library instead of a buffer
+    obtained with cudaMalloc. Device buffers only; k_slices * n_vectors * num_o_neurons must not
+    exceed 1048576. Calls that overlap on the GPU share that array and race."""
+    lib = _lib.load_library()
+    rc = lib.pulpnn_linear_out_32_static_scratch(_ptr(pInBuffer), _ptr(bias), _ptr(pOutBuffer),
+                                                 _ptr(pWeights), C.c_int(dim_vec),
+                                                 C.c_int(num_o_neurons), C.c_int(n_vectors),
+                                                 C.c_int(k_slices))
+    if rc != OK:
+        _check()
+        raise PulpNNError(rc, "pulpnn_linear_out_32_static_scratch failed")
+
+
 # ---- network runner --------------------------------------------------------------------------
 class LayerDesc(C.Structure):
     _fields_ = [(n, C.c_int) for n in (

@@ -673,4 +673,124 @@ bool launch_igemm_tc(Context &c, const ConvProblem &p)
   return cuda_ok(cudaGetLastError(), "splitk_reduce launch");
 }
 
+// ---- fully connected layer with split K, for callers that must not allocate -------------------
+// The split-K path above parks its per-slice partial sums in device memory that the context
+// obtains with cudaMalloc on first use (and again when a larger problem comes along). Some callers
+// cannot tolerate that: a serving loop that has handed every free byte of the device to its own
+// pool (a cudaMalloc there fails, or succeeds only by synchronising the whole device in the
+// middle of a request), or a deployment whose memory budget is fixed and audited up front. For
+// them the partial sums live in the array below: it is part of the library image, so every GPU
+// that loads the library carries these 4 MiB until the process exits, and the entry point that
+// uses it touches no allocator at all.
+constexpr size_t STATIC_SCRATCH_INTS = 1u << 20;                      // 4 MiB of int32 partial sums
+static __device__ __align__(256) int g_static_partials[STATIC_SCRATCH_INTS];
+
+namespace {
+constexpr int MAX_DEVICES = 64;
+int *g_static_partials_dev[MAX_DEVICES] = {};     // device address of the array, per device
+
+// In host code the name g_static_partials is only a handle for the runtime; the address a kernel
+// can use has to be asked for, once per device, with that device current.
+int *static_partials_for_current_device(Context &c)
+{
+  if (c.device < 0 || c.device >= MAX_DEVICES) {
+    set_error(PULPNN_ERR_INVALID_ARG, "device index %d outside 0..%d", c.device, MAX_DEVICES - 1);
+    return nullptr;
+  }
+  if (!g_static_partials_dev[c.device]) {
+    void *p = nullptr;
+    if (!cuda_ok(cudaGetSymbolAddress(&p, g_static_partials), "cudaGetSymbolAddress(static scratch)")) return nullptr;
+    g_static_partials_dev[c.device] = static_cast<int *>(p);
+  }
+  return g_static_partials_dev[c.device];
+}
+}  // namespace
+
 }  // namespace pulpnn
+
+using namespace pulpnn;
+
+extern "C" int pulpnn_linear_out_32_static_scratch(const uint8_t *pInBuffer, const int32_t *bias,
+                                                   int32_t *pOutBuffer, const int8_t *pWeights,
+                                                   int dim_vec, int num_o_neurons, int n_vectors,
+                                                   int k_slices)
+{
+  const char *who = "pulpnn_linear_out_32_static_scratch";
+  Context &c = ctx();
+  if (!ensure_device(c)) return c.err;
+  if (!pInBuffer || !pOutBuffer || !pWeights || dim_vec < 1 || num_o_neurons < 1 || n_vectors < 1 || k_slices < 2) {
+    set_error(PULPNN_ERR_INVALID_ARG, "%s: NULL pointer, empty dimension or fewer than 2 K slices", who);
+    return c.err;
+  }
+  // host buffers would have to be staged through allocated device memory: refuse them
+  const void *ptrs[4] = {pInBuffer, pWeights, pOutBuffer, bias};
+  for (const void *q : ptrs) {
+    if (!q) continue;
+    cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, q) != cudaSuccess ||
+        (a.type != cudaMemoryTypeDevice && a.type != cudaMemoryTypeManaged)) {
+      cudaGetLastError();
+      set_error(PULPNN_ERR_INVALID_ARG, "%s: every buffer must be device memory", who);
+      return c.err;
+    }
+  }
+  ConvProblem p;
+  p.in = pInBuffer; p.w = pWeights; p.out = pOutBuffer;
+  p.B = n_vectors; p.H = p.W = p.Ho = p.Wo = 1; p.Cin = dim_vec; p.Cout = num_o_neurons;
+  p.ky = p.kx = 1; p.pt = p.pl = 0; p.sy = p.sx = 1;
+  p.epi.k = p.epi.lambda = nullptr; p.epi.bias = bias; p.epi.mode = EPI_RAW32; p.epi.out_mult = 0; p.epi.shift = 0;
+  if (!igemm_tc_supported(c, p) || (reinterpret_cast<uintptr_t>(pOutBuffer) & 3) || (reinterpret_cast<uintptr_t>(bias) & 3)) {
+    set_error(PULPNN_ERR_UNSUPPORTED, "%s: needs dim_vec a multiple of 16 and 16-byte aligned device pointers", who);
+    return c.err;
+  }
+
+  TcParams g;
+  g.M = n_vectors; g.N = num_o_neurons; g.K = dim_vec;
+  g.epi = p.epi;
+  const int bn = g.N <= 64 ? 64 : (g.N <= 128 ? 128 : 256);
+  int bkb = 128;
+  if (g.K <= 32) bkb = 32;
+  else if (g.K <= 64) bkb = 64;
+  else if (g.K < 128 && g.K % 64 != 0) bkb = 32;
+  g.m_tiles = (g.M + BM - 1) / BM;
+  g.n_tiles = (g.N + bn - 1) / bn;
+  g.total_slabs = (g.K + bkb - 1) / bkb;
+  const int slices = k_slices < g.total_slabs ? k_slices : g.total_slabs;
+  g.slabs_per_slice = (g.total_slabs + slices - 1) / slices;
+  g.k_slices = (g.total_slabs + g.slabs_per_slice - 1) / g.slabs_per_slice;
+  if (g.k_slices < 2) {
+    set_error(PULPNN_ERR_UNSUPPORTED, "%s: dim_vec %d is too short to split", who, dim_vec);
+    return c.err;
+  }
+  const size_t need = (size_t)g.k_slices * g.M * g.N;
+  if (need > STATIC_SCRATCH_INTS) {
+    set_error(PULPNN_ERR_UNSUPPORTED,
+              "%s: %d slices x %d vectors x %d neurons = %zu partial sums exceed the built-in scratch of %zu "
+              "(4 MiB); use fewer slices or vectors, or pulp_nn_linear_out_32",
+              who, g.k_slices, g.M, g.N, need, (size_t)STATIC_SCRATCH_INTS);
+    return c.err;
+  }
+  int *partials = static_partials_for_current_device(c);
+  if (!partials) return c.err;
+
+  g.w_resident = 0;
+  g.n_stages = PIPE_BYTES / (BM * bkb + bn * bkb);
+  if (g.n_stages > MAX_STAGES) g.n_stages = MAX_STAGES;
+  g.status = nullptr;                      // the status word of the ordinary path is allocated; do without
+  g.out = partials;
+  g.vec_store = (g.N % 4 == 0);
+  CUtensorMap ma, mb;
+  if (!make_map(&ma, p.in, g.M, g.K, BM, bkb)) return c.err;
+  if (!make_map(&mb, p.w, g.N, g.K, bn, bkb)) return c.err;
+  const int sms = c.sm_count > 0 ? c.sm_count : 148;
+  const int units = g.m_tiles * g.n_tiles * g.k_slices;
+  // Nothing in the scratch has to start at zero: the GEMM below writes every partial sum the
+  // reduction reads (each slice owns at least one K slab, every tile of every slice is a unit).
+  if (!launch_bn<EPI_NONE, true>(c, ma, mb, g, bn, bkb, units < sms ? units : sms)) return c.err;
+  const size_t total = (size_t)g.M * g.N;
+  const unsigned blocks = (unsigned)((total + 255) / 256 < (size_t)sms * 8 ? (total + 255) / 256 : (size_t)sms * 8);
+  splitk_reduce_kernel<EPI_RAW32><<<blocks, 256, 0, c.stream>>>(partials, pOutBuffer, p.epi, g.M, g.N, g.k_slices);
+  count_launch();
+  if (!cuda_ok(cudaGetLastError(), "splitk_reduce launch")) return c.err;
+  return PULPNN_OK;
+}
