@@ -50,7 +50,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
@@ -140,7 +140,7 @@ def cpu_baseline(params, wl, budget_s=12.0, max_images=1024):
     from oracle import bindings
     cores = os.cpu_count() or 1
     if bindings.have_reference(32):
-        ref = bindings.CompiledReference(32, arena_mb=1024, threads=cores)
+        ref = bindings.CompiledReference(32, arena_mb=256, threads=cores)
         kind, build = "reference", ref.build_info()
         x = wl.mobilenet_input(7, min(cores, max_images))
         t, glue, _ = cpu_chain_seconds(ref, params, x)
@@ -172,7 +172,9 @@ def run_reference_arm(args):
     n_img, secs = 0, 0.0
     base = None
     for i in range(args.warmup + args.steps):
-        base, (n, t) = cpu_baseline(params, wl, budget_s=4.0, max_images=256)
+        # every step is a bounded sample; the whole run stays within a few minutes
+        budget = args.budget or max(0.5, min(4.0, 150.0 / (args.warmup + args.steps)))
+        base, (n, t) = cpu_baseline(params, wl, budget_s=budget, max_images=args.max_images)
         if i >= args.warmup:
             n_img += n
             secs += t
@@ -207,31 +209,44 @@ def run_gpu_arm(args):
     api.set_device(local)
     api.set_stream(None)
 
-    B = args.batch
+    sharding = __import__("importlib").import_module("pulpnn_b200.sharding")
+    if args.scaling == "strong":      # one batch of --batch images cut into per-rank slices
+        first, last = sharding.shard_bounds(args.batch, rank, world)
+        B, global_batch = last - first, args.batch
+    else:                             # weak: every GPU keeps --batch images
+        B, global_batch = args.batch, args.batch * world
     params = wl.mobilenet_params(seed=4, bits=32, shift_bias=11)
     net = api.build_mobilenet_v1(params, bits=32, max_batch=B, micro_batch=args.micro)
     x_host = torch.from_numpy(wl.mobilenet_input(100 + rank, B)).pin_memory()
     x_dev = x_host.cuda()
     logits = torch.zeros((B, 1000), dtype=torch.int32, device="cuda")
     logits_host = torch.zeros((B, 1000), dtype=torch.int32).pin_memory()
-    gathered = torch.zeros((world * B, 1000), dtype=torch.int32, device="cuda") if world > 1 else None
 
     def step():
         net.run(x_dev, logits, B)
         if world > 1:   # the only exchange of the whole path: the final logits gather
-            dist.all_gather_into_tensor(gathered, logits)
+            sharding.gather_rows(logits, global_batch)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(args.warmup, 3)):
-        step()
-    barrier()
+    # the clock sampler needs a moment to come up: start it before the warm-up and keep the GPU
+    # busy until its first samples are in, so that the timed region is covered
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
+    for _ in range(max(args.warmup, 3)):
+        step()
+    if world == 1:
+        t_wait = time.time()
+        while len(sampler.lines) < 2 and time.time() - t_wait < 3.0:
+            step()
+    else:
+        for _ in range(200):        # same count on every rank: the step contains a collective
+            step()
+    barrier()
     launches0 = api.launch_count()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
@@ -282,7 +297,7 @@ def run_gpu_arm(args):
         per_layer.append({"layer": L["name"], "ms": round(float(t_ms), 4),
                           "GOPs": round(gop / (t_ms / 1e3), 1), "GBs": round(gb / (t_ms / 1e3), 1),
                           "hbm_frac": round(gb / (t_ms / 1e3) / hbm_peak, 3)})
-        kname = {"conv": "conv_generic_kernel", "depthwise": "depthwise_hwc4_kernel",
+        kname = {"conv": "conv_smallcin_kernel", "depthwise": "depthwise_hwc3x3_kernel",
                  "pointwise": "igemm_tc_kernel", "avgpool": "avgpool_kernel",
                  "linear32": "igemm_tc_kernel"}[L["op"]]
         k = by_kernel.setdefault(kname, {"ms": 0.0, "bytes": 0.0, "launches": 0})
@@ -301,13 +316,13 @@ def run_gpu_arm(args):
                 "algorithmic_bytes_per_launch": int(tk["bytes"] / tk["launches"]),
                 "share_of_step": round(tk["ms"] / float(layer_ms.sum()), 3)}
 
-    images = B * world * args.steps
+    images = global_batch * args.steps
     value = images / (ms / 1e3)
     line = {"metric": "MobileNetV1-int8 images/s", "value": round(value, 1), "unit": "images/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-            "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True, "scaling": "weak",
+            "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True, "scaling": args.scaling,
             "vs_baseline": None, "dtype": "u8*s8->s32", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "per_gpu_batch": B, "global_batch": B * world,
+            "config": {"workload": WORKLOAD, "per_gpu_batch": B, "global_batch": global_batch,
                        "micro_batch": args.micro, "parallelism": "batch-sharded x%d, logits all-gather" % world,
                        "l2": "inputs larger than L2 (154 MB of images per step)"},
             "clocks": clocks,
@@ -317,7 +332,16 @@ def run_gpu_arm(args):
             "roofline": roofline,
             "per_layer": per_layer}
     if world == 1 and not args.no_cpu:
-        line["cpu_baseline"], _ = cpu_baseline(params, wl)
+        # in a process of its own: the reference harness wants a low-address arena, and a process
+        # that has CUDA loaded may already have that address range mapped
+        r = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "reference", "--steps", "1",
+                            "--warmup", "0", "--budget", "12", "--max-images", "1024"],
+                           capture_output=True, text=True, timeout=600)
+        try:
+            line["cpu_baseline"] = json.loads(r.stdout.strip().splitlines()[-1])["cpu_baseline"]
+        except Exception:
+            line["cpu_baseline"] = {"value": None, "unit": "images/s", "cores": os.cpu_count(), "kind": "reference",
+                                    "sample": "CPU baseline run failed: " + (r.stderr.strip().splitlines() or ["?"])[-1][:200]}
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -326,12 +350,16 @@ def run_gpu_arm(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=1024, help="images per GPU")
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                    help="weak: --batch images per GPU; strong: --batch images in total, sliced over the GPUs")
     ap.add_argument("--micro", type=int, default=0, help="images per pass through the stack (0 = all)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--budget", type=float, default=0.0, help="reference arm: seconds of CPU work per step")
+    ap.add_argument("--max-images", type=int, default=256, help="reference arm: largest sample per step")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

@@ -164,7 +164,7 @@ class CompiledReference:
     kind = "reference"
     _CONV = {"Ho": 0, "HoWo": 1, "pw_HoWo": 2, "pw_Ho": 3, "Co": 4, "pw_Co": 5}
 
-    def __init__(self, bits, arena_mb=384, threads=1):
+    def __init__(self, bits, arena_mb=192, threads=1):
         if not have_reference(bits):
             raise FileNotFoundError(_REF_SO[bits] + " was not built (needs the reference tree)")
         self.bits = bits

@@ -55,13 +55,12 @@ int refdrv_init(size_t bytes)
 {
   if (g_arena && g_arena_size >= bytes) return 0;
   if (g_arena) { munmap(g_arena, g_arena_size); g_arena = NULL; g_arena_size = 0; }
-  const uintptr_t bases[] = { 0x10000000u, 0x20000000u, 0x30000000u, 0x40000000u, 0x50000000u };
-  for (size_t i = 0; i < sizeof(bases) / sizeof(bases[0]); i++) {
-    if (bases[i] + bytes >= 0x7ff00000u) break;
-    void *p = mmap((void *)bases[i], bytes, PROT_READ | PROT_WRITE,
+  /* try every 64 MiB step below 2 GiB until a free range is found */
+  for (uintptr_t base = 0x10000000u; base + bytes < 0x7ff00000u; base += 0x04000000u) {
+    void *p = mmap((void *)base, bytes, PROT_READ | PROT_WRITE,
                    MAP_PRIVATE | MAP_ANONYMOUS | MAP_FIXED_NOREPLACE, -1, 0);
     if (p == MAP_FAILED) continue;
-    if ((uintptr_t)p != bases[i]) { munmap(p, bytes); continue; }
+    if ((uintptr_t)p != base) { munmap(p, bytes); continue; }
     g_arena = (uint8_t *)p;
     g_arena_size = bytes;
     return 0;

@@ -1,0 +1,140 @@
+#!/usr/bin/env python
+"""Single-kernel measurements: the four single-layer benchmark configurations and the layer shapes
+of MobileNetV1, one C-ABI call each, timed with CUDA events on device-resident buffers.
+
+    python pulp-nn_b200/layer_bench.py --case c2            # pointwise 56x56x128 -> 256, batch 64
+    python pulp-nn_b200/layer_bench.py --case pw1 --batch 128 --reps 3
+    python pulp-nn_b200/layer_bench.py --all
+
+Prints one JSON line per case: milliseconds per call, GOP/s, algorithmic GB/s and the fraction of
+the measured HBM bandwidth (MEASURED_PEAKS.json beside the repository root, if present). Also the
+command used for the ncu captures summarised under profiles/ (small batch, few repetitions).
+"""
+import argparse
+import json
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+import __graft_entry__ as entry  # noqa: E402
+
+POINTWISE = {"pw1": (112, 32, 64), "pw2": (56, 64, 128), "pw3": (56, 128, 128), "pw4": (28, 128, 256),
+             "pw5": (28, 256, 256), "pw6": (14, 256, 512), "pw7": (14, 512, 512), "pw12": (7, 512, 1024),
+             "pw13": (7, 1024, 1024), "c2": (56, 128, 256)}
+DEPTHWISE = {"dw1": (112, 32, 1), "dw2": (112, 64, 2), "dw3": (56, 128, 1), "dw4": (56, 128, 2),
+             "dw5": (28, 256, 1), "dw7": (14, 512, 1), "dw13": (7, 1024, 1)}
+DEFAULT_BATCH = {"c1": 1, "c2": 64, "c3": 64, "c4": 256}
+
+
+def hbm_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    return float(json.load(open(p))["hbm_gbs"]) if os.path.exists(p) else 6650.0
+
+
+def build_case(name, B, pkg):
+    """Returns (callable, ops, algorithmic bytes) for one case."""
+    import torch
+    api, wl = pkg.api, pkg.workloads
+
+    def dev(a):
+        return None if a is None else torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+    def out(shape, dt=torch.uint8):
+        return torch.zeros(shape, dtype=dt, device="cuda")
+
+    if name in POINTWISE:
+        H, cin, cout = POINTWISE[name]
+        c = wl.pointwise_case(1, H, H, cin, cout, batch=B, bits=32)
+        x, w, k, lam, o = dev(c["x"]), dev(c["w"]), dev(c["k"]), dev(c["lam"]), out((B, H, H, cout))
+        fn = lambda: api.pulp_nn_pointwise_HoWo_parallel(32, x, None, None, o, w, k, lam, 1, c["out_shift"], H, H,  # noqa: E731
+                                                         cin, H, H, cout, 1, 1, 0, 0, 0, 0, 1, 1, 1, 1)
+        return fn, 2.0 * B * H * H * cin * cout, B * H * H * (cin + cout) + cin * cout, (x, w, k, lam, o)
+    if name in DEPTHWISE or name == "c3":
+        if name == "c3":
+            c = wl.config_c3(batch=B)
+            H, C, s, bits, hwc = 112, 64, 2, 64, False
+        else:
+            H, C, s = DEPTHWISE[name]
+            bits, hwc = 32, True
+            c = wl.depthwise_case(2, H, H, C, strides=(s, s), batch=B, bits=32, hwc=True)
+        Ho = c["out_hw"][0]
+        x, w, k, lam, o = dev(c["x"]), dev(c["w"]), dev(c["k"]), dev(c["lam"]), out((B, Ho, Ho, C))
+        call = api.pulpnn_depthwise_hwc if hwc else api.pulp_nn_depthwise_generic
+        fn = lambda: call(bits, x, None, None, o, w, None, k, lam, 1, c["out_shift"], H, H, C, Ho, Ho, C,  # noqa: E731
+                          3, 3, 1, 1, 1, 1, s, s, 1, 1)
+        return fn, 2.0 * B * Ho * Ho * C * 9, B * C * (H * H + Ho * Ho), (x, w, k, lam, o)
+    if name in ("c1", "conv1"):
+        if name == "c1":
+            c = wl.config_c1(batch=B)
+            H, cin, cout, s = 32, 32, 64, 1
+        else:
+            c = wl.conv_case(3, 224, 224, 3, 32, strides=(2, 2), batch=B, bits=32)
+            H, cin, cout, s = 224, 3, 32, 2
+        Ho = c["out_hw"][0]
+        x, w, k, lam, o = dev(c["x"]), dev(c["w"]), dev(c["k"]), dev(c["lam"]), out((B, Ho, Ho, cout))
+        fn = lambda: api.pulp_nn_conv_Ho_parallel(32, x, None, None, o, w, k, lam, 1, c["out_shift"], H, H, cin,  # noqa: E731
+                                                  Ho, Ho, cout, 3, 3, 1, 1, 1, 1, s, s, 1, 1)
+        return (fn, 2.0 * B * Ho * Ho * cout * 9 * cin, B * (H * H * cin + Ho * Ho * cout) + cout * 9 * cin,
+                (x, w, k, lam, o))
+    if name in ("c4", "c4_out32"):
+        c = wl.config_c4(batch=B)
+        x, w, bias = dev(c["x"]), dev(c["w"]), dev(c["bias"])
+        if name == "c4":
+            o = out((B, 4096))
+            fn = lambda: api.pulp_nn_linear(32, x, bias, o, w, None, None, 1, c["out_shift"], 4096, 4096, 1, 0)  # noqa: E731
+            nbytes = B * 4096 * 2 + 4096 * 4096
+        else:
+            o = out((B, 4096), torch.int32)
+            fn = lambda: api.pulp_nn_linear_out_32(32, x, None, o, w, 4096, 4096)  # noqa: E731
+            nbytes = B * 4096 * 5 + 4096 * 4096
+        return fn, 2.0 * B * 4096 * 4096, nbytes, (x, w, bias, o)
+    raise SystemExit("unknown case %r" % name)
+
+
+def run_case(name, B, reps, pkg):
+    import torch
+    api = pkg.api
+    api.set_batch(B)
+    fn, ops, nbytes, keep = build_case(name, B, pkg)
+    for _ in range(max(3, reps)):
+        fn()
+    api.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(reps):
+        fn()
+    ev1.record()
+    torch.cuda.synchronize()
+    ms = ev0.elapsed_time(ev1) / reps
+    assert api.device_status() == 0
+    peak = hbm_peak()
+    return {"case": name, "batch": B, "ms_per_call": round(ms, 5), "GOPs": round(ops / ms / 1e6, 1),
+            "GBs": round(nbytes / ms / 1e6, 1), "hbm_frac": round(nbytes / ms / 1e6 / peak, 3),
+            "algorithmic_bytes": int(nbytes), "working_set_larger_than_L2": bool(nbytes > 126e6)}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--case", default="c2")
+    ap.add_argument("--batch", type=int, default=0, help="0 = the configuration's own batch (1024 for MobileNet layers)")
+    ap.add_argument("--reps", type=int, default=20)
+    ap.add_argument("--all", action="store_true")
+    args = ap.parse_args()
+    import torch
+    if not torch.cuda.is_available():
+        raise SystemExit("needs a CUDA device")
+    pkg = entry.load_package()
+    pkg.api.set_device(0)
+    names = [args.case]
+    if args.all:
+        names = list(dict.fromkeys(["c1", "c2", "c3", "c4", "c4_out32", "conv1"] + sorted(POINTWISE) + sorted(DEPTHWISE)))
+    for n in names:
+        B = args.batch or DEFAULT_BATCH.get(n, 1024)
+        print(json.dumps(run_case(n, B, args.reps, pkg)), flush=True)
+
+
+if __name__ == "__main__":
+    main()
