@@ -361,10 +361,24 @@ def main():
     ap.add_argument("--budget", type=float, default=0.0, help="reference arm: seconds of CPU work per step")
     ap.add_argument("--max-images", type=int, default=256, help="reference arm: largest sample per step")
     args = ap.parse_args()
-    if args.impl == "reference":
-        run_reference_arm(args)
-    else:
-        run_gpu_arm(args)
+    # stdout carries exactly one JSON line: whatever libraries print meanwhile (NCCL's version
+    # banner, for one) is sent to stderr by pointing file descriptor 1 there for the run
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+    global print
+    _print = print
+
+    def print(*a, **kw):          # noqa: A001 -- the two JSON lines below go to the real stdout
+        os.write(real_stdout, (" ".join(str(x) for x in a) + "\n").encode())
+    try:
+        if args.impl == "reference":
+            run_reference_arm(args)
+        else:
+            run_gpu_arm(args)
+    finally:
+        print = _print            # noqa: A001
+        os.dup2(real_stdout, 1)
 
 
 if __name__ == "__main__":
