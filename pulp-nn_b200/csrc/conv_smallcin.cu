@@ -50,7 +50,12 @@ __device__ __forceinline__ void epilogue_px(const int (&acc)[CO], const long lon
     }
     w[c >> 2] = pack4_sat_u8(q[0], q[1], q[2], q[3]);
   }
-  if (vec_store) {
+  if (vec_store == 2) {
+    // all 32 channels of the pixel: one full 32-byte sector
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 ::"l"(optr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+                 : "memory");
+  } else if (vec_store) {
 #pragma unroll
     for (int c = 0; c < CO; c += 16)
       if (c < Cout) *reinterpret_cast<uint4 *>(optr + c) = make_uint4(w[c >> 2], w[(c >> 2) + 1], w[(c >> 2) + 2], w[(c >> 2) + 3]);
@@ -199,6 +204,7 @@ bool launch_conv_smallcin(Context &c, const ConvProblem &p)
   g.pitch = (g.lead + (p.W + p.kx) * p.Cin + 16 + 3) & ~3;
   g.vec_rows = (g.row_bytes % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.in) & 3) == 0);
   g.vec_store = (p.Cout % 16 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
+  if (p.Cout == CO && (reinterpret_cast<uintptr_t>(p.out) & 31) == 0) g.vec_store = 2;
   const size_t fixed = (size_t)p.ky * RW * CO * 4 + CO * (8 + 8 + 4);
   // strip height: shared memory under 48 KB, and a pixel-pair count close to a multiple of 256
   int best = 1; double best_waste = 1e9;

@@ -91,13 +91,14 @@ __device__ __forceinline__ unsigned long long global_ns()
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
                                           int *status, int code)
 {
-  if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = global_ns();
+  // the clock is first read once a wait has lasted 256 polls: short waits never pay for it
+  unsigned long long t0 = 0;
   for (unsigned spin = 1;; spin++) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((spin & 255u) == 0) {
       if (*abort_flag) return false;
-      if (global_ns() - t0 > WAIT_LIMIT_NS) {
+      if (t0 == 0) t0 = global_ns();
+      else if (global_ns() - t0 > WAIT_LIMIT_NS) {
         *abort_flag = 1;
         if (status) atomicOr(status, code);
         return false;
@@ -200,6 +201,17 @@ struct SmemLayout {
   static constexpr int NUM_ACC = 512 / BN_TILE;
 };
 
+// unit index -> (n-tile, m-tile, k-slice), n fastest. The common shapes (one n-tile, K not split)
+// need no division at all, which matters in the epilogue where this runs once per tile.
+__device__ __forceinline__ void decode_unit(const TcParams &g, int u, int &nt, int &mt, int &ks)
+{
+  int r = u;
+  nt = 0;
+  if (g.n_tiles != 1) { r = u / g.n_tiles; nt = u - r * g.n_tiles; }
+  mt = r; ks = 0;
+  if (g.k_slices != 1) { ks = r / g.m_tiles; mt = r - ks * g.m_tiles; }
+}
+
 // MODE: the final epilogue; PARTIAL: store raw int32 partial sums instead (split-K)
 template <int MODE, int BN_TILE, int BKB, bool PARTIAL>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
@@ -255,8 +267,8 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         for (int s = 0; s < g.total_slabs; s++) tma_load_2d(smem + s * B_BYTES, &map_b, wres_bar, s * BKB, 0);
       }
       for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
-        const int nt = u % g.n_tiles, r = u / g.n_tiles;
-        const int mt = r % g.m_tiles, ks = r / g.m_tiles;
+        int nt, mt, ks;
+        decode_unit(g, u, nt, mt, ks);
         const int slab0 = ks * g.slabs_per_slice;
         const int slab1 = min(slab0 + g.slabs_per_slice, g.total_slabs);
         for (int s = slab0; s < slab1; s++) {
@@ -296,8 +308,9 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       bool ok = true;
       if (g.w_resident) ok = mbar_wait(wres_bar, 0, abort_flag, g.status, ST_MMA_WRES);
       for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
-        const int r = u / g.n_tiles;
-        const int ks = r / g.m_tiles;
+        int nt, mt, ks;
+        decode_unit(g, u, nt, mt, ks);
+        (void)nt; (void)mt;
         const int slab0 = ks * g.slabs_per_slice;
         const int slab1 = min(slab0 + g.slabs_per_slice, g.total_slabs);
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, g.status, ST_MMA_TMEM)) break;
@@ -344,8 +357,8 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     long long *p_l64 = p_k64 + HALF_COLS;
     int staged_nt = -1;
     for (int u = blockIdx.x; u < units; u += gridDim.x) {
-      const int nt = u % g.n_tiles, r = u / g.n_tiles;
-      const int mt = r % g.m_tiles, ks = r / g.m_tiles;
+      int nt, mt, ks;
+      decode_unit(g, u, nt, mt, ks);
       const int n0 = nt * BN_TILE;
       if (!PARTIAL && nt != staged_nt) {
         // per-channel parameters of this warp's columns -> shared memory. The bias is folded into

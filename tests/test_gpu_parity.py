@@ -199,6 +199,24 @@ def test_depthwise_ragged_and_5x5(hwc, C, gpu, gpu_host, restatement):
     same(gpu_host.depthwise(32, c["x"], c["w"], c["k"], c["lam"], **dw_kw(c)), want)
 
 
+@pytest.mark.parametrize("bits", [32, 64])
+@pytest.mark.parametrize("relu,bn", MODES)
+@pytest.mark.parametrize("stride", [1, 2])
+def test_depthwise_chw_row_kernel(bits, relu, bn, stride, gpu, restatement):
+    """CHW input with a width that is a multiple of 4 (8 for stride 2) takes the row-wise kernel:
+    ragged channel counts, several channel tiles, widths that leave the last column group partly
+    empty, large k that does not fit 32 bits in the 64-bit tree."""
+    for (H, W, C) in ((13, 16, 12), (9, 24, 4), (20, 40, 72), (7, 128, 8)):
+        c = wl.depthwise_case(35, H, W, C, strides=(stride, stride), batch=2, bits=bits, out_shift=9,
+                              with_bias=True, out_mult=3, relu=relu, bn=bn,
+                              k_range=(1, 2 ** 33) if bits == 64 else (1, 64),
+                              lam_range=(-2 ** 34, 2 ** 34) if bits == 64 else (-32768, 32767))
+        if bits == 64:
+            c["out_shift"] = 30
+        want = restatement.depthwise(bits, c["x"], c["w"], c["k"], c["lam"], **dw_kw(c))
+        same(gpu.depthwise(bits, c["x"], c["w"], c["k"], c["lam"], **dw_kw(c)), want)
+
+
 def test_depthwise_mobilenet_shapes(gpu, restatement):
     for (H, C, s) in ((112, 32, 1), (112, 64, 2), (14, 512, 1), (7, 1024, 1)):
         c = wl.depthwise_case(33, H, H, C, strides=(s, s), batch=2, out_shift=9, hwc=True)
