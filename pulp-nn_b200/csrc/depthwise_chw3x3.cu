@@ -103,26 +103,52 @@ __global__ void __launch_bounds__(256) depthwise_chw3x3_kernel(const Chw3Params 
     const unsigned *chan0 = reinterpret_cast<const unsigned *>(p.in + ((size_t)b * p.C + (q_on ? c0 : 0)) * p.H * p.W);
     const size_t chan_words = (size_t)p.H * wrow;
 
+    // Words of the three input rows of the current output row, per channel: x0 (and x1 at stride 2)
+    // are the lane's own words, xr (stride 1 only) is the word right of the last column group.
+    // Consecutive output rows share 3-S input rows, so only S rows are fetched per output row, and
+    // they are fetched one output row ahead.
+    unsigned x0[4][3], x1[4][3], xr[4][3];
+    unsigned n0[4][S], n1[4][S], nr[4][S];
+    auto fetch = [&](int iy, int j, unsigned &a, unsigned &bb, unsigned &rr) {
+      a = 0u; bb = 0u; rr = 0u;
+      if (q_on && c0 + j < p.C && (unsigned)iy < (unsigned)p.H) {
+        const unsigned *rowp = chan0 + (size_t)j * chan_words + (size_t)iy * wrow;
+        if (S == 1) {
+          if (w0 < wrow) a = __ldg(rowp + w0);
+          if (gidx == g.groups - 1 && w0 + 1 < wrow) rr = __ldg(rowp + w0 + 1);
+        } else if (w0 + 1 < wrow) {
+          const uint2 v = __ldg(reinterpret_cast<const uint2 *>(rowp + w0));
+          a = v.x; bb = v.y;
+        } else if (w0 < wrow) {
+          a = __ldg(rowp + w0);
+        }
+      }
+    };
+#pragma unroll
+    for (int j = 0; j < 4; j++)
+#pragma unroll
+      for (int fy = 0; fy < 3; fy++) fetch(oy0 * S - 1 + fy, j, x0[j][fy], x1[j][fy], xr[j][fy]);
+
     for (int r = 0; r < rows; r++) {
-      const int oy = oy0 + r;
+      if (r + 1 < rows) {
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+#pragma unroll
+          for (int t = 0; t < S; t++) fetch((oy0 + r + 1) * S - 1 + (3 - S) + t, j, n0[j][t], n1[j][t], nr[j][t]);
+      }
       unsigned res[4];                                     // per channel: 4 packed output pixels
 #pragma unroll
       for (int j = 0; j < 4; j++) {
-        const bool c_on = q_on && c0 + j < p.C;
         int a0 = 0, a1 = 0, a2 = 0, a3 = 0;
 #pragma unroll
         for (int fy = 0; fy < 3; fy++) {
-          const int iy = oy * S - 1 + fy;
-          const bool row_on = (unsigned)iy < (unsigned)p.H;          // warp-uniform
-          const unsigned *rowp = chan0 + (size_t)j * chan_words + (size_t)(row_on ? iy : 0) * wrow;
           if (S == 1) {
             // outputs ox0..ox0+3 read pixels ox0-1..ox0+4: the lane's word and one byte each of its neighbours'
-            const unsigned m = (c_on && row_on && w0 < wrow) ? __ldg(rowp + w0) : 0u;
+            const unsigned m = x0[j][fy];
             unsigned hm = __shfl_up_sync(0xffffffffu, m, 1);
             unsigned hp = __shfl_down_sync(0xffffffffu, m, 1);
             if (gidx == 0) hm = 0u;
-            // the last group's right neighbour is no lane's word: fetch it, or zero past the row end
-            if (gidx == g.groups - 1) hp = (c_on && row_on && w0 + 1 < wrow) ? __ldg(rowp + w0 + 1) : 0u;
+            if (gidx == g.groups - 1) hp = xr[j][fy];              // no lane holds that word
             const unsigned A = __funnelshift_r(hm, m, 24);           // [p-1, p0, p1, p2]
             const unsigned Bw = __funnelshift_r(m, hp, 16);          // [p2, p3, p4, p5]
             a0 = dp4a_us(A, wa[j][fy], a0);
@@ -131,15 +157,7 @@ __global__ void __launch_bounds__(256) depthwise_chw3x3_kernel(const Chw3Params 
             a3 = dp4a_us(Bw, wa[j][fy], a3);
           } else {
             // outputs ox0..ox0+3 read pixels 2*ox0-1..2*ox0+7: two words of the lane, one byte of the left neighbour
-            unsigned m0 = 0u, m1 = 0u;
-            if (c_on && row_on) {
-              if (w0 + 1 < wrow) {
-                const uint2 v = __ldg(reinterpret_cast<const uint2 *>(rowp + w0));
-                m0 = v.x; m1 = v.y;
-              } else if (w0 < wrow) {
-                m0 = __ldg(rowp + w0);
-              }
-            }
+            const unsigned m0 = x0[j][fy], m1 = x1[j][fy];
             unsigned hm = __shfl_up_sync(0xffffffffu, m1, 1);
             if (gidx == 0) hm = 0u;
             const unsigned A = __funnelshift_r(hm, m0, 24);          // [p-1, p0, p1, p2]
@@ -150,6 +168,11 @@ __global__ void __launch_bounds__(256) depthwise_chw3x3_kernel(const Chw3Params 
             a3 = dp4a_us(m1, wb[j][fy], a3);
           }
         }
+        // slide the window down by S input rows
+#pragma unroll
+        for (int fy = 0; fy < 3 - S; fy++) { x0[j][fy] = x0[j][fy + S]; x1[j][fy] = x1[j][fy + S]; xr[j][fy] = xr[j][fy + S]; }
+#pragma unroll
+        for (int t = 0; t < S; t++) { x0[j][3 - S + t] = n0[j][t]; x1[j][3 - S + t] = n1[j][t]; xr[j][3 - S + t] = nr[j][t]; }
         res[j] = pack4_sat_u8(requant_one<MODE>(a0, kk[j], ll[j], bias[j], e), requant_one<MODE>(a1, kk[j], ll[j], bias[j], e),
                               requant_one<MODE>(a2, kk[j], ll[j], bias[j], e), requant_one<MODE>(a3, kk[j], ll[j], bias[j], e));
       }
