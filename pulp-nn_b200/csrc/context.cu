@@ -83,6 +83,16 @@ void *ctx_scratch(Context &c, size_t bytes)
   return c.scratch;
 }
 
+// device word that kernels with bounded waits report into (read by pulpnn_device_status)
+int *ctx_status_word(Context &c)
+{
+  if (!c.status_word) {
+    if (!cuda_ok(cudaMalloc(&c.status_word, sizeof(int)), "cudaMalloc(status)")) return nullptr;
+    if (!cuda_ok(cudaMemsetAsync(c.status_word, 0, sizeof(int), c.stream), "cudaMemset(status)")) return nullptr;
+  }
+  return c.status_word;
+}
+
 // ---- staging ------------------------------------------------------------------------------
 static bool is_device_pointer(const void *p)
 {

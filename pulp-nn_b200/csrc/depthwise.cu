@@ -263,6 +263,7 @@ bool launch_dw_mode(Context &c, const DepthwiseProblem &p)
 
 bool launch_depthwise(Context &c, const DepthwiseProblem &p)
 {
+  if (!c.opt_force_generic && depthwise_hwc3x3_tma_supported(p)) return launch_depthwise_hwc3x3_tma(c, p);
   if (!c.opt_force_generic && depthwise_hwc3x3_supported(p)) return launch_depthwise_hwc3x3(c, p);
   if (!c.opt_force_generic && depthwise_chw3x3_supported(p)) return launch_depthwise_chw3x3(c, p);
   switch (p.epi.mode) {

@@ -1,0 +1,498 @@
+// depthwise_hwc3x3_tma.cu -- 3x3 depthwise convolution on HWC input (padding 1, stride 1 or 2) for
+// channel counts that are a multiple of 128, with input and output staged through shared memory by
+// TMA. Arithmetic is that of depthwise.cu (32bit/src/pulp_nn_depthwise_generic.c:133-180) and the
+// register scheme is that of depthwise_hwc3x3.cu: a thread owns four channels and four adjacent
+// output columns, transposes four pixel words into four channel words with byte permutes, and
+// pays one dp4a per output and filter row.
+//
+// What this file changes is everything around that arithmetic. A CTA owns a tile of 128 channels x
+// 4*NGX output columns and slides down the image. A ring of three groups of input rows is kept full
+// by 4-D TMA loads (tensor [B][H][W][C]); rows and columns outside the image arrive as zeros from
+// the TMA unit, which IS the zero padding, so the inner loop has no boundary test at all. Results
+// go to a double-buffered tile in shared memory and leave with one TMA store per group of rows,
+// which also clips columns and rows past the output's edge. One warp = the 32 channel words of one
+// pixel, so every shared-memory access is a conflict-free 128-byte row, and with the tile width a
+// template parameter every address in the row loop is "one register + constant".
+//
+// Synchronisation per group of rows: one mbarrier wait (data landed), one __syncthreads (all
+// threads finished reading the group and writing the output tile), after which thread 0 issues the
+// store of the tile and the load that refills the group. Every wait is bounded.
+#include <type_traits>
+
+#include "internal.cuh"
+#include "sm100_primitives.cuh"
+
+namespace pulpnn {
+
+namespace {
+
+using namespace sm100;
+
+constexpr int CI = 128;                       // channel bytes per tile = one warp of 32-bit words
+constexpr int RING = 3;                       // groups of input rows in flight
+constexpr int ST_HWC_TMA = 0x400;
+
+__device__ __forceinline__ unsigned prmt(unsigned a, unsigned b, unsigned sel)
+{
+  unsigned d;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+  return d;
+}
+__device__ __forceinline__ unsigned lds32(uint32_t addr)
+{
+  unsigned v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void sts32(uint32_t addr, unsigned v)
+{
+  asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+
+// four pixel words (byte j = channel j) -> four channel words (byte i = pixel i)
+__device__ __forceinline__ void transpose4(const unsigned m0, const unsigned m1, const unsigned m2,
+                                           const unsigned m3, unsigned (&t)[4])
+{
+  const unsigned a = prmt(m0, m1, 0x5140), b = prmt(m0, m1, 0x7362);
+  const unsigned c = prmt(m2, m3, 0x5140), d = prmt(m2, m3, 0x7362);
+  t[0] = prmt(a, c, 0x5410); t[1] = prmt(a, c, 0x7632);
+  t[2] = prmt(b, d, 0x5410); t[3] = prmt(b, d, 0x7632);
+}
+
+// geometry of a tile, all compile-time
+template <int S, int NGX> struct Geo {
+  static constexpr int WT = 4 * NGX;                          // output columns per tile
+  static constexpr int WBOX = S == 1 ? WT + 2 : 2 * WT + 1;   // input columns per tile (with halo)
+  static constexpr int ROWS_IN = S == 1 ? 3 : 4;              // input rows per group
+  static constexpr int ROWS_OUT = S == 1 ? 3 : 2;             // output rows a group completes
+  static constexpr int IN_PITCH = WBOX * CI;                  // bytes per staged input row
+  static constexpr int OUT_PITCH = WT * CI;                   // bytes per staged output row
+  static constexpr int GROUP_BYTES = ROWS_IN * IN_PITCH;
+  static constexpr int TILE_BYTES = ROWS_OUT * OUT_PITCH;
+  static constexpr int THREADS = 32 * NGX;
+  static constexpr int SMEM = 128 + RING * GROUP_BYTES + 2 * TILE_BYTES + 64;
+};
+
+struct HwcTmaParams {
+  DepthwiseProblem p;
+  int col_tiles, chunks, strips;   // tiles across the width, 128-channel chunks, strips down the height
+  int rows_per_strip;              // output rows per strip (a multiple of the rows a group completes)
+  int *status;
+};
+
+template <int MODE> struct QuantT {
+  typename std::conditional<MODE == EPI_BN64, long long, int>::type k[4], l[4];
+  int bias[4];     // accumulators start from it in the modes without batch normalisation
+};
+
+// requantise a completed 4 columns x 4 channels block and put the four pixel words in the tile
+template <int MODE, bool K32>
+__device__ __forceinline__ void finalize_k(const int (&acc)[4][4], const QuantT<MODE> &q, const Epilogue &e, uint32_t oaddr)
+{
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    int v[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      if (MODE == EPI_BN32)
+        v[j] = (int)((unsigned)q.k[j] * (unsigned)acc[i][j] + (unsigned)q.l[j]) >> e.shift;
+      else if (MODE == EPI_BN64 && K32)      // every k fits in 32 bits: one wide multiply-add
+        v[j] = (int)(((long long)(int)q.k[j] * acc[i][j] + (long long)q.l[j]) >> e.shift);
+      else if (MODE == EPI_BN64)
+        v[j] = (int)((long long)((unsigned long long)q.k[j] * (unsigned long long)(long long)acc[i][j] +
+                                 (unsigned long long)q.l[j]) >> e.shift);
+      else if (MODE == EPI_MULT)
+        v[j] = (int)(short)((int)((unsigned)e.out_mult * (unsigned)acc[i][j]) >> e.shift);
+      else
+        v[j] = acc[i][j] >> e.shift;
+    }
+    sts32(oaddr + i * CI, pack4_sat_u8(v[0], v[1], v[2], v[3]));
+  }
+}
+template <int MODE>
+__device__ __forceinline__ void finalize_row(const int (&acc)[4][4], const QuantT<MODE> &q, const Epilogue &e,
+                                             bool k32, uint32_t oaddr)
+{
+  if (MODE == EPI_BN64 && k32) finalize_k<MODE, true>(acc, q, e, oaddr);
+  else finalize_k<MODE, false>(acc, q, e, oaddr);
+}
+
+// ---- stride 1: six pixels per staged row feed four outputs ---------------------------------------
+struct Win1 { unsigned T[4], A[4], B[4]; };
+
+__device__ __forceinline__ void load_row1(uint32_t addr, unsigned (&cur)[6])
+{
+#pragma unroll
+  for (int i = 0; i < 6; i++) cur[i] = lds32(addr + i * CI);
+}
+__device__ __forceinline__ void windows1(const unsigned (&cur)[6], Win1 &w)
+{
+  transpose4(cur[1], cur[2], cur[3], cur[4], w.T);
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    w.A[j] = prmt(w.T[j], cur[0], 0x2104u + j);                   // [left, p0, p1, p2]
+    w.B[j] = prmt(w.T[j], cur[5], 0x0321u | ((4u + j) << 12));     // [p1, p2, p3, right]
+  }
+}
+// one staged row: filter row 2 of X (which it completes), row 1 of Y, row 0 of Z (which it opens)
+template <bool DOX, bool DOY>
+__device__ __forceinline__ void mac1(const Win1 &w, const int (&wa)[3][4], const int (&wb)[3][4], const int (&init)[4],
+                                     int (&X)[4][4], int (&Y)[4][4], int (&Z)[4][4])
+{
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    if (DOX) {
+      X[0][j] = dp4a_us(w.A[j], wa[2][j], X[0][j]);  X[1][j] = dp4a_us(w.T[j], wa[2][j], X[1][j]);
+      X[2][j] = dp4a_us(w.T[j], wb[2][j], X[2][j]);  X[3][j] = dp4a_us(w.B[j], wb[2][j], X[3][j]);
+    }
+    if (DOY) {
+      Y[0][j] = dp4a_us(w.A[j], wa[1][j], Y[0][j]);  Y[1][j] = dp4a_us(w.T[j], wa[1][j], Y[1][j]);
+      Y[2][j] = dp4a_us(w.T[j], wb[1][j], Y[2][j]);  Y[3][j] = dp4a_us(w.B[j], wb[1][j], Y[3][j]);
+    }
+    Z[0][j] = dp4a_us(w.A[j], wa[0][j], init[j]);    Z[1][j] = dp4a_us(w.T[j], wa[0][j], init[j]);
+    Z[2][j] = dp4a_us(w.T[j], wb[0][j], init[j]);    Z[3][j] = dp4a_us(w.B[j], wb[0][j], init[j]);
+  }
+}
+
+// ---- stride 2: nine pixels per staged row feed four outputs --------------------------------------
+struct Win2 { unsigned T[4], U[4], A[4], C[4]; };
+
+__device__ __forceinline__ void load_row2(uint32_t addr, unsigned (&cur)[9])
+{
+#pragma unroll
+  for (int i = 0; i < 9; i++) cur[i] = lds32(addr + i * CI);
+}
+__device__ __forceinline__ void windows2(const unsigned (&cur)[9], Win2 &w)
+{
+  transpose4(cur[1], cur[2], cur[3], cur[4], w.T);
+  transpose4(cur[5], cur[6], cur[7], cur[8], w.U);
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    w.A[j] = prmt(w.T[j], cur[0], 0x2104u + j);     // [left, p0, p1, p2]
+    w.C[j] = prmt(w.T[j], w.U[j], 0x6543u);         // [p3, p4, p5, p6]
+  }
+}
+template <bool OPEN>
+__device__ __forceinline__ void mac2(const Win2 &w, const int (&wa)[4], const int (&wb)[4], const int (&init)[4],
+                                     int (&acc)[4][4])
+{
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    acc[0][j] = dp4a_us(w.A[j], wa[j], OPEN ? init[j] : acc[0][j]);
+    acc[1][j] = dp4a_us(w.T[j], wb[j], OPEN ? init[j] : acc[1][j]);
+    acc[2][j] = dp4a_us(w.C[j], wa[j], OPEN ? init[j] : acc[2][j]);
+    acc[3][j] = dp4a_us(w.U[j], wb[j], OPEN ? init[j] : acc[3][j]);
+  }
+}
+
+// three bytes of a packed weight array starting at byte n, as [b0, b1, b2, 0]
+__device__ __forceinline__ int taps3(const unsigned (&W)[9], int n)
+{
+  const int wi = n >> 2, off = n & 3;
+  const unsigned lo = W[wi], hi = wi + 1 < 9 ? W[wi + 1] : 0u;
+  return (int)(__funnelshift_r(lo, hi, 8 * off) & 0x00ffffffu);
+}
+
+template <int MODE, int S, int NGX>
+__global__ void __launch_bounds__(32 * NGX, 16 / NGX)
+depthwise_hwc3x3_tma_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_constant__ CUtensorMap map_out,
+                            const HwcTmaParams g)
+{
+  using G = Geo<S, NGX>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t pad = (128u - (smem_u32(smem_raw) & 127u)) & 127u;
+  uint8_t *sm = smem_raw + pad;
+  const uint32_t ring = smem_u32(sm), tiles = ring + RING * G::GROUP_BYTES;
+  uint64_t *full = reinterpret_cast<uint64_t *>(sm + RING * G::GROUP_BYTES + 2 * G::TILE_BYTES);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(full + RING);
+
+  const DepthwiseProblem &p = g.p;
+  const Epilogue &e = p.epi;
+  const int tid = threadIdx.x, lane = tid & 31, gx = tid >> 5;
+
+  // which tile: column tile fastest, then strip, then channel chunk, then image
+  int t = blockIdx.x;
+  const int col_tile = t % g.col_tiles; t /= g.col_tiles;
+  const int strip = t % g.strips; t /= g.strips;
+  const int chunk = t % g.chunks;
+  const int b = t / g.chunks;
+  const int c_base = chunk * CI, ox_base = col_tile * G::WT;
+  const int oyA = strip * g.rows_per_strip, oyB = min(oyA + g.rows_per_strip, p.Ho);
+  const int ngroups = 1 + (oyB - oyA + G::ROWS_OUT - 1) / G::ROWS_OUT;    // group 0 only opens accumulators
+  const int in_x = S * ox_base - 1;                                      // first staged input column
+  const int in_y0 = S == 1 ? oyA - 2 : 2 * oyA - 4;                      // first staged row of group 0
+
+  if (tid == 0) {
+    for (int s = 0; s < RING; s++) mbar_init(&full[s], 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    const int first = ngroups < RING ? ngroups : RING;
+    for (int j = 0; j < first; j++) {
+      mbar_arrive_expect_tx(&full[j], (uint32_t)G::GROUP_BYTES);
+      tma_load_4d(sm + j * G::GROUP_BYTES, &map_in, &full[j], c_base, in_x, in_y0 + j * G::ROWS_IN, b);
+    }
+  }
+
+  // the thread's four channels: weights as [w0,w1,w2,0] and [0,w0,w1,w2] per filter row, and the
+  // requantisation parameters (fetched while the first loads are in flight)
+  const int c = c_base + 4 * lane;
+  int wa[3][4], wb[3][4];
+  {
+    unsigned W[9];
+    const unsigned *wp = reinterpret_cast<const unsigned *>(p.w + (size_t)c * 9);
+#pragma unroll
+    for (int i = 0; i < 9; i++) W[i] = __ldg(wp + i);
+#pragma unroll
+    for (int j = 0; j < 4; j++)
+#pragma unroll
+      for (int fy = 0; fy < 3; fy++) {
+        wa[fy][j] = taps3(W, j * 9 + fy * 3);
+        wb[fy][j] = (int)((unsigned)wa[fy][j] << 8);
+      }
+  }
+  QuantT<MODE> q;
+  int init[4];
+  bool k32 = true;
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    q.bias[j] = e.bias ? (int)__ldg(reinterpret_cast<const int8_t *>(e.bias) + c + j) : 0;
+    q.k[j] = 0; q.l[j] = 0;
+    init[j] = (MODE == EPI_BN32 || MODE == EPI_BN64) ? 0 : q.bias[j];
+    if (MODE == EPI_BN32) {
+      const int k = __ldg(reinterpret_cast<const int *>(e.k) + c + j);
+      q.k[j] = k;   // the bias moves into lambda: k*(acc+bias)+l == k*acc + (k*bias+l) in wrap-around arithmetic
+      q.l[j] = (int)((unsigned)k * (unsigned)q.bias[j] + (unsigned)__ldg(reinterpret_cast<const int *>(e.lambda) + c + j));
+    } else if (MODE == EPI_BN64) {
+      const long long k = __ldg(reinterpret_cast<const long long *>(e.k) + c + j);
+      q.k[j] = k;
+      q.l[j] = (long long)((unsigned long long)k * (unsigned long long)(long long)q.bias[j] +
+                           (unsigned long long)__ldg(reinterpret_cast<const long long *>(e.lambda) + c + j));
+      k32 = k32 && (k == (long long)(int)k);
+    }
+  }
+  __syncthreads();                                   // the barriers are initialised
+
+  const uint32_t in_thr = ring + (uint32_t)(4 * S * gx) * CI + 4u * lane;     // thread's first staged pixel
+  const uint32_t out_thr = tiles + (uint32_t)(4 * gx) * CI + 4u * lane;
+  bool dead = false;              // a wait ran out: keep pace at the barriers, do no more work
+  int issued = ngroups < RING ? ngroups : RING;      // thread 0: groups whose load has been issued
+  int consumed = 0;                                  // groups whose data this thread has seen land
+  auto refill = [&](int j_next, int grp_) {          // thread 0 only
+    mbar_arrive_expect_tx(&full[grp_], (uint32_t)G::GROUP_BYTES);
+    tma_load_4d(sm + grp_ * G::GROUP_BYTES, &map_in, &full[grp_], c_base, in_x, in_y0 + j_next * G::ROWS_IN, b);
+    issued = j_next + 1;
+  };
+
+  // Accumulators. Stride 1: three sets, one per output row in flight (an input row is filter row 2
+  // of one, row 1 of the next and row 0 of the one after). Stride 2: one set.
+  int acc[S == 1 ? 3 : 1][4][4];
+#pragma unroll
+  for (int a = 0; a < (S == 1 ? 3 : 1); a++)
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+      for (int j = 0; j < 4; j++) acc[a][i][j] = 0;
+
+  // ---- group 0: the rows above the strip's first output row only open accumulators ---------------
+  if (!mbar_wait(&full[0], 0, abort_flag, g.status, ST_HWC_TMA)) dead = true;
+  if (!dead) {
+    consumed = 1;
+    if constexpr (S == 1) {
+      unsigned cur[6]; Win1 w;
+      load_row1(in_thr + 1 * G::IN_PITCH, cur);                 // input row oyA-1
+      windows1(cur, w);
+      load_row1(in_thr + 2 * G::IN_PITCH, cur);                 // input row oyA
+      mac1<false, false>(w, wa, wb, init, acc[0], acc[0], acc[0]);
+      windows1(cur, w);
+      mac1<false, true>(w, wa, wb, init, acc[0], acc[0], acc[S == 1 ? 1 : 0]);
+    } else {
+      unsigned cur[9]; Win2 w;
+      load_row2(in_thr + 3 * G::IN_PITCH, cur);                 // input row 2*oyA-1
+      windows2(cur, w);
+      mac2<true>(w, wa[0], wb[0], init, acc[0]);
+    }
+  }
+  __syncthreads();                                              // group 0 has been read by everyone
+  if (tid == 0 && !dead && RING < ngroups) refill(RING, 0);
+
+  int grp = 0, half = 0;
+  uint32_t parity = 0;
+  for (int j = 1; j < ngroups; j++) {
+    if (++grp == RING) { grp = 0; parity ^= 1; }
+    if (!dead && !mbar_wait(&full[grp], parity, abort_flag, g.status, ST_HWC_TMA)) dead = true;
+    if (!dead) {
+      consumed = j + 1;
+      const uint32_t ia = in_thr + grp * G::GROUP_BYTES, oa = out_thr + half * G::TILE_BYTES;
+      if constexpr (S == 1) {
+        constexpr int A1 = S == 1 ? 1 : 0, A2 = S == 1 ? 2 : 0;
+        unsigned cur[6]; Win1 w;
+        load_row1(ia, cur);
+        windows1(cur, w);
+        load_row1(ia + G::IN_PITCH, cur);
+        mac1<true, true>(w, wa, wb, init, acc[0], acc[A1], acc[A2]);
+        finalize_row<MODE>(acc[0], q, e, k32, oa);
+        windows1(cur, w);
+        load_row1(ia + 2 * G::IN_PITCH, cur);
+        mac1<true, true>(w, wa, wb, init, acc[A1], acc[A2], acc[0]);
+        finalize_row<MODE>(acc[A1], q, e, k32, oa + G::OUT_PITCH);
+        windows1(cur, w);
+        mac1<true, true>(w, wa, wb, init, acc[A2], acc[0], acc[A1]);
+        finalize_row<MODE>(acc[A2], q, e, k32, oa + 2 * G::OUT_PITCH);
+      } else {
+        unsigned cur[9]; Win2 w;
+        load_row2(ia, cur);                                     // input row 2m
+        windows2(cur, w);
+        load_row2(ia + G::IN_PITCH, cur);                       // 2m+1: closes row m, opens m+1
+        mac2<false>(w, wa[1], wb[1], init, acc[0]);
+        windows2(cur, w);
+        load_row2(ia + 2 * G::IN_PITCH, cur);
+        mac2<false>(w, wa[2], wb[2], init, acc[0]);
+        finalize_row<MODE>(acc[0], q, e, k32, oa);
+        mac2<true>(w, wa[0], wb[0], init, acc[0]);
+        windows2(cur, w);
+        load_row2(ia + 3 * G::IN_PITCH, cur);
+        mac2<false>(w, wa[1], wb[1], init, acc[0]);
+        windows2(cur, w);
+        mac2<false>(w, wa[2], wb[2], init, acc[0]);
+        finalize_row<MODE>(acc[0], q, e, k32, oa + G::OUT_PITCH);
+        mac2<true>(w, wa[0], wb[0], init, acc[0]);
+      }
+      fence_proxy_async();            // the tile words written above, before the TMA store reads them
+    }
+    // the store issued two groups ago read the half that the NEXT group will write
+    if (tid == 0) bulk_wait_read_all();
+    __syncthreads();
+    if (tid == 0 && !dead) {
+      tma_store_4d(&map_out, sm + RING * G::GROUP_BYTES + half * G::TILE_BYTES, c_base, ox_base,
+                   oyA + (j - 1) * G::ROWS_OUT, b);
+      bulk_commit();
+      if (j + RING < ngroups) refill(j + RING, grp);
+    }
+    half ^= 1;
+  }
+  if (tid == 0) {
+    bulk_wait_all();
+    if (*abort_flag) {
+      // no TMA write may still be in flight when the CTA's shared memory is released
+      for (int qn = consumed; qn < issued; qn++) {
+        const unsigned long long t0 = global_ns();
+        while (!mbar_try_wait(&full[qn % RING], (uint32_t)(qn / RING) & 1u))
+          if (global_ns() - t0 > WAIT_LIMIT_NS) break;
+      }
+    }
+  }
+}
+
+// ---- host side ----------------------------------------------------------------------------------
+bool encode_4d(CUtensorMap *map, const void *base, int C, int Wd, int Hd, int B, int box_w, int box_h)
+{
+  cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)Wd, (cuuint64_t)Hd, (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)C, (cuuint64_t)Wd * C, (cuuint64_t)Hd * Wd * C};
+  cuuint32_t box[4] = {(cuuint32_t)CI, (cuuint32_t)box_w, (cuuint32_t)box_h, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUresult r = encode_tiled_fn()(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void *>(base), dims, strides, box,
+                                       estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                       CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error(PULPNN_ERR_CUDA, "cuTensorMapEncodeTiled (depthwise, %dx%dx%dx%d) failed with code %d", B, Hd, Wd, C, (int)r);
+    return false;
+  }
+  return true;
+}
+
+// column groups per tile: the candidate that wastes the fewest columns past the right edge (the
+// wider one on a tie)
+int pick_ngx(int Wo)
+{
+  const int cand[3] = {7, 4, 2};
+  int best = 7;
+  long long best_cost = -1;
+  for (int i = 0; i < 3; i++) {
+    const int wt = 4 * cand[i];
+    const long long cost = (long long)((Wo + wt - 1) / wt) * wt;
+    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = cand[i]; }
+  }
+  return best;
+}
+
+template <int MODE, int S, int NGX>
+bool launch_geo(Context &c, const DepthwiseProblem &p)
+{
+  using G = Geo<S, NGX>;
+  HwcTmaParams g;
+  g.p = p;
+  g.col_tiles = (p.Wo + G::WT - 1) / G::WT;
+  g.chunks = p.C / CI;
+  g.status = ctx_status_word(c);
+  if (!g.status) return false;
+  auto kern = depthwise_hwc3x3_tma_kernel<MODE, S, NGX>;
+  static thread_local int resident = 0;     // CTAs of this instantiation that fit on one SM
+  if (resident == 0) {
+    if (!cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM),
+                 "cudaFuncSetAttribute(depthwise_hwc3x3_tma)"))
+      return false;
+    int n = 0;
+    if (!cuda_ok(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, G::THREADS, G::SMEM), "occupancy query")) return false;
+    resident = n > 0 ? n : 1;
+  }
+  // Strips down the height only when whole columns leave the GPU short of CTAs (small batches): a
+  // strip boundary costs one extra group of input rows.
+  const long long columns = (long long)p.B * g.chunks * g.col_tiles;
+  const long long want = 4LL * (c.sm_count > 0 ? c.sm_count : 148) * resident;
+  int strips = 1;
+  while (columns * strips < want && p.Ho / (strips * 2) >= 4 * G::ROWS_OUT) strips *= 2;
+  int rows = (p.Ho + strips - 1) / strips;
+  rows = (rows + G::ROWS_OUT - 1) / G::ROWS_OUT * G::ROWS_OUT;
+  g.rows_per_strip = rows;
+  g.strips = (p.Ho + rows - 1) / rows;
+  const long long total = columns * g.strips;
+  if (total > 0x7fffffffLL) { set_error(PULPNN_ERR_UNSUPPORTED, "depthwise: too many tiles"); return false; }
+  CUtensorMap map_in, map_out;
+  if (!encode_4d(&map_in, p.in, p.C, p.W, p.H, p.B, G::WBOX, G::ROWS_IN)) return false;
+  if (!encode_4d(&map_out, p.out, p.C, p.Wo, p.Ho, p.B, G::WT, G::ROWS_OUT)) return false;
+  kern<<<(unsigned)total, G::THREADS, G::SMEM, c.stream>>>(map_in, map_out, g);
+  count_launch();
+  return cuda_ok(cudaGetLastError(), "depthwise_hwc3x3_tma launch");
+}
+
+template <int MODE, int S>
+bool launch_ngx(Context &c, const DepthwiseProblem &p)
+{
+  switch (pick_ngx(p.Wo)) {
+    case 7:  return launch_geo<MODE, S, 7>(c, p);
+    case 4:  return launch_geo<MODE, S, 4>(c, p);
+    default: return launch_geo<MODE, S, 2>(c, p);
+  }
+}
+
+template <int MODE>
+bool launch_stride(Context &c, const DepthwiseProblem &p)
+{
+  return p.sx == 1 ? launch_ngx<MODE, 1>(c, p) : launch_ngx<MODE, 2>(c, p);
+}
+
+}  // namespace
+
+bool depthwise_hwc3x3_tma_supported(const DepthwiseProblem &p)
+{
+  if (!p.in_is_hwc || p.ky != 3 || p.kx != 3 || p.pt != 1 || p.pl != 1) return false;
+  if (p.sx != p.sy || (p.sx != 1 && p.sx != 2)) return false;
+  if (p.C % CI != 0) return false;
+  // TMA wants 16-byte aligned tensors; the weights are read as 32-bit words
+  if ((reinterpret_cast<uintptr_t>(p.in) & 15) || (reinterpret_cast<uintptr_t>(p.out) & 15)) return false;
+  if (reinterpret_cast<uintptr_t>(p.w) & 3) return false;
+  if ((long long)p.H * p.W * p.C > 0x7fffffffffLL) return false;
+  return encode_tiled_fn() != nullptr;
+}
+
+bool launch_depthwise_hwc3x3_tma(Context &c, const DepthwiseProblem &p)
+{
+  switch (p.epi.mode) {
+    case EPI_NONE: return launch_stride<EPI_NONE>(c, p);
+    case EPI_MULT: return launch_stride<EPI_MULT>(c, p);
+    case EPI_BN32: return launch_stride<EPI_BN32>(c, p);
+    default:       return launch_stride<EPI_BN64>(c, p);
+  }
+}
+
+}  // namespace pulpnn

@@ -180,8 +180,11 @@ bool launch_igemm_tc(Context &c, const ConvProblem &p);
 bool launch_depthwise(Context &c, const DepthwiseProblem &p);
 bool depthwise_hwc3x3_supported(const DepthwiseProblem &p);
 bool launch_depthwise_hwc3x3(Context &c, const DepthwiseProblem &p);
+bool depthwise_hwc3x3_tma_supported(const DepthwiseProblem &p);
+bool launch_depthwise_hwc3x3_tma(Context &c, const DepthwiseProblem &p);
 bool depthwise_chw3x3_supported(const DepthwiseProblem &p);
 bool launch_depthwise_chw3x3(Context &c, const DepthwiseProblem &p);
+int *ctx_status_word(Context &c);               // allocated on first use; nullptr on failure
 bool launch_maxpool(Context &c, const PoolProblem &p, uint8_t *clobber_in);
 bool launch_avgpool(Context &c, const PoolProblem &p);
 bool launch_add(Context &c, const uint8_t *a, const uint8_t *b, uint8_t *out, size_t n, int m1,

@@ -25,7 +25,8 @@ POINTWISE = {"pw1": (112, 32, 64), "pw2": (56, 64, 128), "pw3": (56, 128, 128), 
              "pw5": (28, 256, 256), "pw6": (14, 256, 512), "pw7": (14, 512, 512), "pw12": (7, 512, 1024),
              "pw13": (7, 1024, 1024), "c2": (56, 128, 256)}
 DEPTHWISE = {"dw1": (112, 32, 1), "dw2": (112, 64, 2), "dw3": (56, 128, 1), "dw4": (56, 128, 2),
-             "dw5": (28, 256, 1), "dw7": (14, 512, 1), "dw13": (7, 1024, 1)}
+             "dw5": (28, 256, 1), "dw6": (28, 256, 2), "dw7": (14, 512, 1), "dw12": (14, 512, 2),
+             "dw13": (7, 1024, 1)}
 DEFAULT_BATCH = {"c1": 1, "c2": 64, "c3": 64, "c4": 256}
 
 

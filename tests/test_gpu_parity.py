@@ -217,6 +217,35 @@ def test_depthwise_chw_row_kernel(bits, relu, bn, stride, gpu, restatement):
         same(gpu.depthwise(bits, c["x"], c["w"], c["k"], c["lam"], **dw_kw(c)), want)
 
 
+@pytest.mark.parametrize("bits", [32, 64])
+@pytest.mark.parametrize("relu,bn", MODES)
+@pytest.mark.parametrize("stride", [1, 2])
+def test_depthwise_hwc_tma_kernel(bits, relu, bn, stride, gpu, restatement):
+    """HWC input with a multiple of 128 channels takes the TMA-staged kernel: every tile width,
+    images narrower and shorter than a tile, several column tiles with a ragged last one, heights
+    that are not a multiple of the rows a group completes, two channel chunks, and (64-bit tree)
+    k that does not fit 32 bits."""
+    for (H, W, C) in ((14, 14, 128), (7, 7, 256), (5, 4, 128), (33, 61, 128), (28, 28, 128), (16, 30, 128)):
+        c = wl.depthwise_case(36, H, W, C, strides=(stride, stride), batch=3, bits=bits, out_shift=9,
+                              with_bias=True, out_mult=3, relu=relu, bn=bn, hwc=True,
+                              k_range=(1, 2 ** 33) if (bits == 64 and H == 7) else (1, 64),
+                              lam_range=(-2 ** 34, 2 ** 34) if (bits == 64 and H == 7) else (-32768, 32767))
+        if bits == 64 and H == 7:
+            c["out_shift"] = 30
+        want = restatement.depthwise(bits, c["x"], c["w"], c["k"], c["lam"], **dw_kw(c))
+        same(gpu.depthwise(bits, c["x"], c["w"], c["k"], c["lam"], **dw_kw(c)), want)
+    assert api.device_status() == 0
+
+
+def test_depthwise_hwc_tma_small_batch_strips(gpu, restatement):
+    """Batch 1 splits the height into strips (each with its own opening group of rows)."""
+    for (H, W, C, s) in ((56, 56, 128, 1), (56, 56, 128, 2), (112, 20, 128, 1)):
+        c = wl.depthwise_case(37, H, W, C, strides=(s, s), batch=1, out_shift=9, hwc=True)
+        want = restatement.depthwise(32, c["x"], c["w"], c["k"], c["lam"], **dw_kw(c))
+        same(gpu.depthwise(32, c["x"], c["w"], c["k"], c["lam"], **dw_kw(c)), want)
+    assert api.device_status() == 0
+
+
 def test_depthwise_mobilenet_shapes(gpu, restatement):
     for (H, C, s) in ((112, 32, 1), (112, 64, 2), (14, 512, 1), (7, 1024, 1)):
         c = wl.depthwise_case(33, H, H, C, strides=(s, s), batch=2, out_shift=9, hwc=True)
