@@ -28,8 +28,9 @@ namespace {
 
 using namespace sm100;
 
-constexpr int CI = 128;                       // channel bytes per tile = one warp of 32-bit words
-constexpr int RING = 3;                       // groups of input rows in flight
+// CI (template parameter below) = channel bytes per tile: 128, 64 or 32. A warp covers 128/CI
+// column groups of CI/4 channel words each.
+constexpr int RING = 3;                      // groups of input rows in flight
 constexpr int ST_HWC_TMA = 0x400;
 
 __device__ __forceinline__ unsigned prmt(unsigned a, unsigned b, unsigned sel)
@@ -49,28 +50,53 @@ __device__ __forceinline__ void sts32(uint32_t addr, unsigned v)
   asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
 }
 
-// four pixel words (byte j = channel j) -> four channel words (byte i = pixel i)
+// Four pixel words (byte j = channel j) -> four channel words (byte i = pixel i). The registers hold
+// the pixels rotated by the lane's rotation r (register i = pixel (i + r) & 3, see the kernel); the
+// second level of permutes undoes the rotation through its selectors, so it costs nothing.
+struct Rot { unsigned off[4]; unsigned sel_lo, sel_hi; };
+
+template <int CI>
+__device__ __forceinline__ Rot make_rot(int r)
+{
+  Rot rot;
+  unsigned sel = 0;
+#pragma unroll
+  for (int m = 0; m < 4; m++) {
+    const unsigned i = (unsigned)(m - r) & 3u;     // the register that holds pixel m
+    sel |= ((i & 1u) | ((i & 2u) << 1)) << (4 * m);   // its channel-0 byte after level one: 0, 1, 4, 5
+  }
+  rot.sel_lo = sel;
+  rot.sel_hi = sel + 0x2222u;
+#pragma unroll
+  for (int i = 0; i < 4; i++) rot.off[i] = (unsigned)(((i + r) & 3) * CI);
+  return rot;
+}
 __device__ __forceinline__ void transpose4(const unsigned m0, const unsigned m1, const unsigned m2,
-                                           const unsigned m3, unsigned (&t)[4])
+                                           const unsigned m3, const Rot &rot, unsigned (&t)[4])
 {
   const unsigned a = prmt(m0, m1, 0x5140), b = prmt(m0, m1, 0x7362);
   const unsigned c = prmt(m2, m3, 0x5140), d = prmt(m2, m3, 0x7362);
-  t[0] = prmt(a, c, 0x5410); t[1] = prmt(a, c, 0x7632);
-  t[2] = prmt(b, d, 0x5410); t[3] = prmt(b, d, 0x7632);
+  t[0] = prmt(a, c, rot.sel_lo); t[1] = prmt(a, c, rot.sel_hi);
+  t[2] = prmt(b, d, rot.sel_lo); t[3] = prmt(b, d, rot.sel_hi);
 }
 
 // geometry of a tile, all compile-time
-template <int S, int NGX> struct Geo {
-  static constexpr int WT = 4 * NGX;                          // output columns per tile
+template <int S, int NGX, int CI> struct Geo {
+  static constexpr int LPC = CI / 4;                          // lanes (channel words) per pixel
+  static constexpr int NSUB = 32 / LPC;                       // column groups per warp
+  static constexpr int WT = 4 * NGX;                         // output columns per tile
   static constexpr int WBOX = S == 1 ? WT + 2 : 2 * WT + 1;   // input columns per tile (with halo)
   static constexpr int ROWS_IN = S == 1 ? 3 : 4;              // input rows per group
   static constexpr int ROWS_OUT = S == 1 ? 3 : 2;             // output rows a group completes
   static constexpr int IN_PITCH = WBOX * CI;                  // bytes per staged input row
   static constexpr int OUT_PITCH = WT * CI;                   // bytes per staged output row
-  static constexpr int GROUP_BYTES = ROWS_IN * IN_PITCH;
+  static constexpr int GROUP_BYTES = ROWS_IN * IN_PITCH;      // bytes one TMA load brings
   static constexpr int TILE_BYTES = ROWS_OUT * OUT_PITCH;
-  static constexpr int THREADS = 32 * NGX;
-  static constexpr int SMEM = 128 + RING * GROUP_BYTES + 2 * TILE_BYTES + 64;
+  static constexpr int GROUP_STRIDE = (GROUP_BYTES + 127) / 128 * 128;   // TMA wants 128-byte aligned boxes
+  static constexpr int TILE_STRIDE = (TILE_BYTES + 127) / 128 * 128;
+  static constexpr int THREADS = 32 * NGX / NSUB;
+  static constexpr int SMEM = 128 + RING * GROUP_STRIDE + 2 * TILE_STRIDE + 64;
+  static_assert(NGX % NSUB == 0, "a warp's column groups must all belong to the tile");
 };
 
 struct HwcTmaParams {
@@ -86,7 +112,7 @@ template <int MODE> struct QuantT {
 };
 
 // requantise a completed 4 columns x 4 channels block and put the four pixel words in the tile
-template <int MODE, bool K32>
+template <int MODE, bool K32, int CI>
 __device__ __forceinline__ void finalize_k(const int (&acc)[4][4], const QuantT<MODE> &q, const Epilogue &e, uint32_t oaddr)
 {
 #pragma unroll
@@ -109,25 +135,30 @@ __device__ __forceinline__ void finalize_k(const int (&acc)[4][4], const QuantT<
     sts32(oaddr + i * CI, pack4_sat_u8(v[0], v[1], v[2], v[3]));
   }
 }
-template <int MODE>
+template <int MODE, int CI>
 __device__ __forceinline__ void finalize_row(const int (&acc)[4][4], const QuantT<MODE> &q, const Epilogue &e,
                                              bool k32, uint32_t oaddr)
 {
-  if (MODE == EPI_BN64 && k32) finalize_k<MODE, true>(acc, q, e, oaddr);
-  else finalize_k<MODE, false>(acc, q, e, oaddr);
+  if (MODE == EPI_BN64 && k32) finalize_k<MODE, true, CI>(acc, q, e, oaddr);
+  else finalize_k<MODE, false, CI>(acc, q, e, oaddr);
 }
 
 // ---- stride 1: six pixels per staged row feed four outputs ---------------------------------------
 struct Win1 { unsigned T[4], A[4], B[4]; };
 
-__device__ __forceinline__ void load_row1(uint32_t addr, unsigned (&cur)[6])
+// addr = the thread's first staged pixel of the row (the left neighbour of its four columns);
+// ra[i] = address of the i-th of the four middle pixels in the lane's rotated order
+template <int CI>
+__device__ __forceinline__ void load_row1(uint32_t addr, const uint32_t (&ra)[4], int row_off, unsigned (&cur)[6])
 {
+  cur[0] = lds32(addr + row_off);
 #pragma unroll
-  for (int i = 0; i < 6; i++) cur[i] = lds32(addr + i * CI);
+  for (int i = 0; i < 4; i++) cur[1 + i] = lds32(ra[i] + row_off);
+  cur[5] = lds32(addr + row_off + 5 * CI);
 }
-__device__ __forceinline__ void windows1(const unsigned (&cur)[6], Win1 &w)
+__device__ __forceinline__ void windows1(const unsigned (&cur)[6], const Rot &rot, Win1 &w)
 {
-  transpose4(cur[1], cur[2], cur[3], cur[4], w.T);
+  transpose4(cur[1], cur[2], cur[3], cur[4], rot, w.T);
 #pragma unroll
   for (int j = 0; j < 4; j++) {
     w.A[j] = prmt(w.T[j], cur[0], 0x2104u + j);                   // [left, p0, p1, p2]
@@ -157,15 +188,19 @@ __device__ __forceinline__ void mac1(const Win1 &w, const int (&wa)[3][4], const
 // ---- stride 2: nine pixels per staged row feed four outputs --------------------------------------
 struct Win2 { unsigned T[4], U[4], A[4], C[4]; };
 
-__device__ __forceinline__ void load_row2(uint32_t addr, unsigned (&cur)[9])
+template <int CI>
+__device__ __forceinline__ void load_row2(uint32_t addr, const uint32_t (&ra)[4], int row_off, unsigned (&cur)[9])
 {
+  cur[0] = lds32(addr + row_off);
 #pragma unroll
-  for (int i = 0; i < 9; i++) cur[i] = lds32(addr + i * CI);
+  for (int i = 0; i < 4; i++) cur[1 + i] = lds32(ra[i] + row_off);
+#pragma unroll
+  for (int i = 0; i < 4; i++) cur[5 + i] = lds32(ra[i] + row_off + 4 * CI);
 }
-__device__ __forceinline__ void windows2(const unsigned (&cur)[9], Win2 &w)
+__device__ __forceinline__ void windows2(const unsigned (&cur)[9], const Rot &rot, Win2 &w)
 {
-  transpose4(cur[1], cur[2], cur[3], cur[4], w.T);
-  transpose4(cur[5], cur[6], cur[7], cur[8], w.U);
+  transpose4(cur[1], cur[2], cur[3], cur[4], rot, w.T);
+  transpose4(cur[5], cur[6], cur[7], cur[8], rot, w.U);
 #pragma unroll
   for (int j = 0; j < 4; j++) {
     w.A[j] = prmt(w.T[j], cur[0], 0x2104u + j);     // [left, p0, p1, p2]
@@ -193,22 +228,24 @@ __device__ __forceinline__ int taps3(const unsigned (&W)[9], int n)
   return (int)(__funnelshift_r(lo, hi, 8 * off) & 0x00ffffffu);
 }
 
-template <int MODE, int S, int NGX>
-__global__ void __launch_bounds__(32 * NGX, 16 / NGX)
+template <int MODE, int S, int NGX, int CI>
+__global__ void __launch_bounds__(Geo<S, NGX, CI>::THREADS, 512 / Geo<S, NGX, CI>::THREADS)
 depthwise_hwc3x3_tma_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_constant__ CUtensorMap map_out,
                             const HwcTmaParams g)
 {
-  using G = Geo<S, NGX>;
+  using G = Geo<S, NGX, CI>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t pad = (128u - (smem_u32(smem_raw) & 127u)) & 127u;
   uint8_t *sm = smem_raw + pad;
-  const uint32_t ring = smem_u32(sm), tiles = ring + RING * G::GROUP_BYTES;
-  uint64_t *full = reinterpret_cast<uint64_t *>(sm + RING * G::GROUP_BYTES + 2 * G::TILE_BYTES);
+  const uint32_t ring = smem_u32(sm), tiles = ring + RING * G::GROUP_STRIDE;
+  uint64_t *full = reinterpret_cast<uint64_t *>(sm + RING * G::GROUP_STRIDE + 2 * G::TILE_STRIDE);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(full + RING);
 
   const DepthwiseProblem &p = g.p;
   const Epilogue &e = p.epi;
-  const int tid = threadIdx.x, lane = tid & 31, gx = tid >> 5;
+  // a warp = NSUB column groups x LPC channel words; with CI = 128 that is one column group
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int c4 = lane % G::LPC, sub = lane / G::LPC, gx = (tid >> 5) * G::NSUB + sub;
 
   // which tile: column tile fastest, then strip, then channel chunk, then image
   int t = blockIdx.x;
@@ -229,13 +266,13 @@ depthwise_hwc3x3_tma_kernel(const __grid_constant__ CUtensorMap map_in, const __
     const int first = ngroups < RING ? ngroups : RING;
     for (int j = 0; j < first; j++) {
       mbar_arrive_expect_tx(&full[j], (uint32_t)G::GROUP_BYTES);
-      tma_load_4d(sm + j * G::GROUP_BYTES, &map_in, &full[j], c_base, in_x, in_y0 + j * G::ROWS_IN, b);
+      tma_load_4d(sm + j * G::GROUP_STRIDE, &map_in, &full[j], c_base, in_x, in_y0 + j * G::ROWS_IN, b);
     }
   }
 
   // the thread's four channels: weights as [w0,w1,w2,0] and [0,w0,w1,w2] per filter row, and the
   // requantisation parameters (fetched while the first loads are in flight)
-  const int c = c_base + 4 * lane;
+  const int c = c_base + 4 * c4;
   int wa[3][4], wb[3][4];
   {
     unsigned W[9];
@@ -272,14 +309,18 @@ depthwise_hwc3x3_tma_kernel(const __grid_constant__ CUtensorMap map_in, const __
   }
   __syncthreads();                                   // the barriers are initialised
 
-  const uint32_t in_thr = ring + (uint32_t)(4 * S * gx) * CI + 4u * lane;     // thread's first staged pixel
-  const uint32_t out_thr = tiles + (uint32_t)(4 * gx) * CI + 4u * lane;
-  bool dead = false;              // a wait ran out: keep pace at the barriers, do no more work
+  const uint32_t in_thr = ring + (uint32_t)(4 * S * gx) * CI + 4u * c4;       // thread's first staged pixel
+  const uint32_t out_thr = tiles + (uint32_t)(4 * gx) * CI + 4u * c4;
+  // Pixels are CI bytes apart, so the column groups of a warp (4 or 4*S pixels apart) would meet in
+  // the same shared-memory banks. Each reads its four middle pixels in an order rotated by its
+  // index inside the warp instead: one load instruction then touches NSUB different pixels mod 4.
+  const Rot rot = make_rot<CI>(sub);
+  bool dead = false;             // a wait ran out: keep pace at the barriers, do no more work
   int issued = ngroups < RING ? ngroups : RING;      // thread 0: groups whose load has been issued
   int consumed = 0;                                  // groups whose data this thread has seen land
   auto refill = [&](int j_next, int grp_) {          // thread 0 only
     mbar_arrive_expect_tx(&full[grp_], (uint32_t)G::GROUP_BYTES);
-    tma_load_4d(sm + grp_ * G::GROUP_BYTES, &map_in, &full[grp_], c_base, in_x, in_y0 + j_next * G::ROWS_IN, b);
+    tma_load_4d(sm + grp_ * G::GROUP_STRIDE, &map_in, &full[grp_], c_base, in_x, in_y0 + j_next * G::ROWS_IN, b);
     issued = j_next + 1;
   };
 
@@ -297,18 +338,21 @@ depthwise_hwc3x3_tma_kernel(const __grid_constant__ CUtensorMap map_in, const __
   if (!mbar_wait(&full[0], 0, abort_flag, g.status, ST_HWC_TMA)) dead = true;
   if (!dead) {
     consumed = 1;
+    uint32_t ra[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) ra[i] = in_thr + CI + rot.off[i];
     if constexpr (S == 1) {
       unsigned cur[6]; Win1 w;
-      load_row1(in_thr + 1 * G::IN_PITCH, cur);                 // input row oyA-1
-      windows1(cur, w);
-      load_row1(in_thr + 2 * G::IN_PITCH, cur);                 // input row oyA
+      load_row1<CI>(in_thr, ra, 1 * G::IN_PITCH, cur);          // input row oyA-1
+      windows1(cur, rot, w);
+      load_row1<CI>(in_thr, ra, 2 * G::IN_PITCH, cur);          // input row oyA
       mac1<false, false>(w, wa, wb, init, acc[0], acc[0], acc[0]);
-      windows1(cur, w);
+      windows1(cur, rot, w);
       mac1<false, true>(w, wa, wb, init, acc[0], acc[0], acc[S == 1 ? 1 : 0]);
     } else {
       unsigned cur[9]; Win2 w;
-      load_row2(in_thr + 3 * G::IN_PITCH, cur);                 // input row 2*oyA-1
-      windows2(cur, w);
+      load_row2<CI>(in_thr, ra, 3 * G::IN_PITCH, cur);          // input row 2*oyA-1
+      windows2(cur, rot, w);
       mac2<true>(w, wa[0], wb[0], init, acc[0]);
     }
   }
@@ -322,39 +366,42 @@ depthwise_hwc3x3_tma_kernel(const __grid_constant__ CUtensorMap map_in, const __
     if (!dead && !mbar_wait(&full[grp], parity, abort_flag, g.status, ST_HWC_TMA)) dead = true;
     if (!dead) {
       consumed = j + 1;
-      const uint32_t ia = in_thr + grp * G::GROUP_BYTES, oa = out_thr + half * G::TILE_BYTES;
+      const uint32_t ia = in_thr + grp * G::GROUP_STRIDE, oa = out_thr + half * G::TILE_STRIDE;
+      uint32_t ra[4];
+#pragma unroll
+      for (int i = 0; i < 4; i++) ra[i] = ia + CI + rot.off[i];
       if constexpr (S == 1) {
         constexpr int A1 = S == 1 ? 1 : 0, A2 = S == 1 ? 2 : 0;
         unsigned cur[6]; Win1 w;
-        load_row1(ia, cur);
-        windows1(cur, w);
-        load_row1(ia + G::IN_PITCH, cur);
+        load_row1<CI>(ia, ra, 0, cur);
+        windows1(cur, rot, w);
+        load_row1<CI>(ia, ra, G::IN_PITCH, cur);
         mac1<true, true>(w, wa, wb, init, acc[0], acc[A1], acc[A2]);
-        finalize_row<MODE>(acc[0], q, e, k32, oa);
-        windows1(cur, w);
-        load_row1(ia + 2 * G::IN_PITCH, cur);
+        finalize_row<MODE, CI>(acc[0], q, e, k32, oa);
+        windows1(cur, rot, w);
+        load_row1<CI>(ia, ra, 2 * G::IN_PITCH, cur);
         mac1<true, true>(w, wa, wb, init, acc[A1], acc[A2], acc[0]);
-        finalize_row<MODE>(acc[A1], q, e, k32, oa + G::OUT_PITCH);
-        windows1(cur, w);
+        finalize_row<MODE, CI>(acc[A1], q, e, k32, oa + G::OUT_PITCH);
+        windows1(cur, rot, w);
         mac1<true, true>(w, wa, wb, init, acc[A2], acc[0], acc[A1]);
-        finalize_row<MODE>(acc[A2], q, e, k32, oa + 2 * G::OUT_PITCH);
+        finalize_row<MODE, CI>(acc[A2], q, e, k32, oa + 2 * G::OUT_PITCH);
       } else {
         unsigned cur[9]; Win2 w;
-        load_row2(ia, cur);                                     // input row 2m
-        windows2(cur, w);
-        load_row2(ia + G::IN_PITCH, cur);                       // 2m+1: closes row m, opens m+1
+        load_row2<CI>(ia, ra, 0, cur);                          // input row 2m
+        windows2(cur, rot, w);
+        load_row2<CI>(ia, ra, G::IN_PITCH, cur);                // 2m+1: closes row m, opens m+1
         mac2<false>(w, wa[1], wb[1], init, acc[0]);
-        windows2(cur, w);
-        load_row2(ia + 2 * G::IN_PITCH, cur);
+        windows2(cur, rot, w);
+        load_row2<CI>(ia, ra, 2 * G::IN_PITCH, cur);
         mac2<false>(w, wa[2], wb[2], init, acc[0]);
-        finalize_row<MODE>(acc[0], q, e, k32, oa);
+        finalize_row<MODE, CI>(acc[0], q, e, k32, oa);
         mac2<true>(w, wa[0], wb[0], init, acc[0]);
-        windows2(cur, w);
-        load_row2(ia + 3 * G::IN_PITCH, cur);
+        windows2(cur, rot, w);
+        load_row2<CI>(ia, ra, 3 * G::IN_PITCH, cur);
         mac2<false>(w, wa[1], wb[1], init, acc[0]);
-        windows2(cur, w);
+        windows2(cur, rot, w);
         mac2<false>(w, wa[2], wb[2], init, acc[0]);
-        finalize_row<MODE>(acc[0], q, e, k32, oa + G::OUT_PITCH);
+        finalize_row<MODE, CI>(acc[0], q, e, k32, oa + G::OUT_PITCH);
         mac2<true>(w, wa[0], wb[0], init, acc[0]);
       }
       fence_proxy_async();            // the tile words written above, before the TMA store reads them
@@ -363,7 +410,7 @@ depthwise_hwc3x3_tma_kernel(const __grid_constant__ CUtensorMap map_in, const __
     if (tid == 0) bulk_wait_read_all();
     __syncthreads();
     if (tid == 0 && !dead) {
-      tma_store_4d(&map_out, sm + RING * G::GROUP_BYTES + half * G::TILE_BYTES, c_base, ox_base,
+      tma_store_4d(&map_out, sm + RING * G::GROUP_STRIDE + half * G::TILE_STRIDE, c_base, ox_base,
                    oyA + (j - 1) * G::ROWS_OUT, b);
       bulk_commit();
       if (j + RING < ngroups) refill(j + RING, grp);
@@ -384,11 +431,11 @@ depthwise_hwc3x3_tma_kernel(const __grid_constant__ CUtensorMap map_in, const __
 }
 
 // ---- host side ----------------------------------------------------------------------------------
-bool encode_4d(CUtensorMap *map, const void *base, int C, int Wd, int Hd, int B, int box_w, int box_h)
+bool encode_4d(CUtensorMap *map, const void *base, int C, int Wd, int Hd, int B, int ci, int box_w, int box_h)
 {
   cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)Wd, (cuuint64_t)Hd, (cuuint64_t)B};
   cuuint64_t strides[3] = {(cuuint64_t)C, (cuuint64_t)Wd * C, (cuuint64_t)Hd * Wd * C};
-  cuuint32_t box[4] = {(cuuint32_t)CI, (cuuint32_t)box_w, (cuuint32_t)box_h, 1};
+  cuuint32_t box[4] = {(cuuint32_t)ci, (cuuint32_t)box_w, (cuuint32_t)box_h, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   const CUresult r = encode_tiled_fn()(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void *>(base), dims, strides, box,
                                        estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
@@ -402,10 +449,9 @@ bool encode_4d(CUtensorMap *map, const void *base, int C, int Wd, int Hd, int B,
 
 // column groups per tile: the candidate that wastes the fewest columns past the right edge (the
 // wider one on a tie)
-int pick_ngx(int Wo)
+int pick_ngx(int Wo, const int (&cand)[3])
 {
-  const int cand[3] = {7, 4, 2};
-  int best = 7;
+  int best = cand[0];
   long long best_cost = -1;
   for (int i = 0; i < 3; i++) {
     const int wt = 4 * cand[i];
@@ -415,17 +461,17 @@ int pick_ngx(int Wo)
   return best;
 }
 
-template <int MODE, int S, int NGX>
+template <int MODE, int S, int NGX, int CI>
 bool launch_geo(Context &c, const DepthwiseProblem &p)
 {
-  using G = Geo<S, NGX>;
+  using G = Geo<S, NGX, CI>;
   HwcTmaParams g;
   g.p = p;
   g.col_tiles = (p.Wo + G::WT - 1) / G::WT;
   g.chunks = p.C / CI;
   g.status = ctx_status_word(c);
   if (!g.status) return false;
-  auto kern = depthwise_hwc3x3_tma_kernel<MODE, S, NGX>;
+  auto kern = depthwise_hwc3x3_tma_kernel<MODE, S, NGX, CI>;
   static thread_local int resident = 0;     // CTAs of this instantiation that fit on one SM
   if (resident == 0) {
     if (!cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM),
@@ -448,27 +494,39 @@ bool launch_geo(Context &c, const DepthwiseProblem &p)
   const long long total = columns * g.strips;
   if (total > 0x7fffffffLL) { set_error(PULPNN_ERR_UNSUPPORTED, "depthwise: too many tiles"); return false; }
   CUtensorMap map_in, map_out;
-  if (!encode_4d(&map_in, p.in, p.C, p.W, p.H, p.B, G::WBOX, G::ROWS_IN)) return false;
-  if (!encode_4d(&map_out, p.out, p.C, p.Wo, p.Ho, p.B, G::WT, G::ROWS_OUT)) return false;
+  if (!encode_4d(&map_in, p.in, p.C, p.W, p.H, p.B, CI, G::WBOX, G::ROWS_IN)) return false;
+  if (!encode_4d(&map_out, p.out, p.C, p.Wo, p.Ho, p.B, CI, G::WT, G::ROWS_OUT)) return false;
   kern<<<(unsigned)total, G::THREADS, G::SMEM, c.stream>>>(map_in, map_out, g);
   count_launch();
   return cuda_ok(cudaGetLastError(), "depthwise_hwc3x3_tma launch");
 }
 
-template <int MODE, int S>
+// tile widths on offer: 28, 16 or 8 columns per column group of a warp's first lane ... in column
+// groups: 7, 4 or 2 warps' worth when a warp is one group (CI = 128); wider when a warp holds more
+template <int MODE, int S, int CI>
 bool launch_ngx(Context &c, const DepthwiseProblem &p)
 {
-  switch (pick_ngx(p.Wo)) {
-    case 7:  return launch_geo<MODE, S, 7>(c, p);
-    case 4:  return launch_geo<MODE, S, 4>(c, p);
-    default: return launch_geo<MODE, S, 2>(c, p);
-  }
+  constexpr int NSUB = 128 / CI;
+  constexpr int N0 = 7 * NSUB, N1 = NSUB == 4 ? 8 : 4, N2 = NSUB == 4 ? 4 : 2;
+  const int cand[3] = {N0, N1, N2};
+  const int ngx = pick_ngx(p.Wo, cand);
+  if (ngx == N0) return launch_geo<MODE, S, N0, CI>(c, p);
+  if (ngx == N1) return launch_geo<MODE, S, N1, CI>(c, p);
+  return launch_geo<MODE, S, N2, CI>(c, p);
+}
+
+template <int MODE, int S>
+bool launch_ci(Context &c, const DepthwiseProblem &p)
+{
+  if (p.C % 128 == 0) return launch_ngx<MODE, S, 128>(c, p);
+  if (p.C % 64 == 0) return launch_ngx<MODE, S, 64>(c, p);
+  return launch_ngx<MODE, S, 32>(c, p);
 }
 
 template <int MODE>
 bool launch_stride(Context &c, const DepthwiseProblem &p)
 {
-  return p.sx == 1 ? launch_ngx<MODE, 1>(c, p) : launch_ngx<MODE, 2>(c, p);
+  return p.sx == 1 ? launch_ci<MODE, 1>(c, p) : launch_ci<MODE, 2>(c, p);
 }
 
 }  // namespace
@@ -477,7 +535,7 @@ bool depthwise_hwc3x3_tma_supported(const DepthwiseProblem &p)
 {
   if (!p.in_is_hwc || p.ky != 3 || p.kx != 3 || p.pt != 1 || p.pl != 1) return false;
   if (p.sx != p.sy || (p.sx != 1 && p.sx != 2)) return false;
-  if (p.C % CI != 0) return false;
+  if (p.C % 32 != 0) return false;
   // TMA wants 16-byte aligned tensors; the weights are read as 32-bit words
   if ((reinterpret_cast<uintptr_t>(p.in) & 15) || (reinterpret_cast<uintptr_t>(p.out) & 15)) return false;
   if (reinterpret_cast<uintptr_t>(p.w) & 3) return false;

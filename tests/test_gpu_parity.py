@@ -221,11 +221,13 @@ def test_depthwise_chw_row_kernel(bits, relu, bn, stride, gpu, restatement):
 @pytest.mark.parametrize("relu,bn", MODES)
 @pytest.mark.parametrize("stride", [1, 2])
 def test_depthwise_hwc_tma_kernel(bits, relu, bn, stride, gpu, restatement):
-    """HWC input with a multiple of 128 channels takes the TMA-staged kernel: every tile width,
-    images narrower and shorter than a tile, several column tiles with a ragged last one, heights
-    that are not a multiple of the rows a group completes, two channel chunks, and (64-bit tree)
-    k that does not fit 32 bits."""
-    for (H, W, C) in ((14, 14, 128), (7, 7, 256), (5, 4, 128), (33, 61, 128), (28, 28, 128), (16, 30, 128)):
+    """HWC input with a multiple of 32 channels takes the TMA-staged kernel: 128-, 64- and 32-byte
+    channel chunks, every tile width, images narrower and shorter than a tile, several column tiles
+    with a ragged last one, heights that are not a multiple of the rows a group completes, several
+    channel chunks, and (64-bit tree) k that does not fit 32 bits."""
+    for (H, W, C) in ((14, 14, 128), (7, 7, 256), (5, 4, 128), (33, 61, 128), (28, 28, 128), (16, 30, 128),
+                      (14, 14, 32), (9, 30, 64), (12, 20, 96), (8, 115, 32), (6, 112 * stride, 32),
+                      (10, 56 * stride, 64), (7, 40, 192)):
         c = wl.depthwise_case(36, H, W, C, strides=(stride, stride), batch=3, bits=bits, out_shift=9,
                               with_bias=True, out_mult=3, relu=relu, bn=bn, hwc=True,
                               k_range=(1, 2 ** 33) if (bits == 64 and H == 7) else (1, 64),
