@@ -326,6 +326,7 @@ void add_entry(uint8_t *a, uint8_t *b, uint8_t *out, int m1, int m2, int out_shi
 bool launch_conv(Context &c, const ConvProblem &p)
 {
   if (!c.opt_force_generic && igemm_tc_supported(c, p)) return launch_igemm_tc(c, p);
+  if (!c.opt_force_generic && conv_smallcin_tc_supported(p)) return launch_conv_smallcin_tc(c, p);
   if (!c.opt_force_generic && conv_smallcin_supported(p)) return launch_conv_smallcin(c, p);
   return launch_conv_generic(c, p);
 }

@@ -8,19 +8,22 @@
 // keeps weights as [ch_out][K], 32bit/src/pulp_nn_matmul.c:55-59, so both operands are K-major
 // exactly as they lie in memory).
 //
-// Structure of one CTA (320 threads, persistent over work units = (m-tile, n-tile, k-slice)):
-//   warp 0, one lane   TMA producer: a 128-row tile of A and a BN-row tile of W per pipeline stage,
-//                      BKB bytes of K wide (32, 64 or 128, matching swizzle), completion on an
-//                      mbarrier (no multicast). TMA fetches the whole box from L2 even where it
-//                      lies outside the tensor, so the box is never wider than K needs. When one
-//                      n-tile covers all of W and it is small, W is loaded ONCE per CTA and stays
-//                      in shared memory; the ring then carries A only.
-//   warp 1, one lane   issues tcgen05.mma.kind::i8 (M=128, N=BN, K=32 per instruction), operands
-//                      from shared-memory descriptors, accumulator in tensor memory; commits free
-//                      the stage and publish the accumulator
-//   warps 2..9         epilogue: tcgen05.ld the accumulator (lane = output row), add bias,
-//                      requantise with per-channel k/lambda held in shared memory, pack to bytes
-//                      and store 32 bytes at a time into the HWC output
+// Structure of one CTA (22 warps, persistent over work units = (m-tile, n-tile, k-slice)):
+//   warps 0..3, one lane each   TMA producers: a 128-row tile of A and a BN-row tile of W per
+//                      pipeline stage, BKB bytes of K wide (32, 64 or 128, matching swizzle),
+//                      completion on an mbarrier (no multicast). TMA fetches the whole box from L2
+//                      even where it lies outside the tensor, so the box is never wider than K
+//                      needs. When one n-tile covers all of W and it is small, W is loaded ONCE per
+//                      CTA and stays in shared memory; the ring then carries A only. The four
+//                      warps take turns slab by slab: getting one load on its way costs a thread
+//                      several hundred cycles, more than a short-K tile has to spare.
+//   warps 4..5, one lane each   issue tcgen05.mma.kind::i8 (M=128, N=BN, K=32 per instruction),
+//                      operands from shared-memory descriptors, accumulator in tensor memory;
+//                      commits free the stage and publish the accumulator. They alternate tiles.
+//   warps 6..21        epilogue, two groups of eight that alternate tiles: tcgen05.ld the
+//                      accumulator (lane = output row), add bias, requantise with per-channel
+//                      k/lambda held in shared memory, pack to bytes and store 32 bytes at a time
+//                      into the HWC output
 // All 512 columns of tensor memory are used as a ring of 512/BN accumulators, so the MMA issuer runs
 // several tiles ahead of the epilogue. Integer accumulation is associative, so splitting K over
 // several CTAs (used when a problem has too few tiles to fill the GPU) gives bit-identical sums;
@@ -41,8 +44,16 @@ namespace {
 
 constexpr int BM = 128;            // rows per tile = TMEM lanes
 constexpr int UMMA_K = 32;         // K per tcgen05.mma for 8-bit operands
-constexpr int EPI_WARPS = 8;       // two per TMEM lane quarter
-constexpr int NUM_THREADS = 64 + 32 * EPI_WARPS;
+constexpr int EPI_WARPS = 8;       // warps that drain one accumulator: two per TMEM lane quarter
+constexpr int EPI_GROUPS = 2;      // groups of EPI_WARPS; group g drains the CTA's tiles g, g+2, ...
+// One thread needs several hundred cycles to get a TMA load on its way, and a tcgen05.mma plus its
+// commits is not much cheaper; with the short K of a pointwise layer that, not the memory system,
+// bounded the whole kernel. So both jobs are shared out: producer warp w issues the loads of every
+// NPROD-th slab of the CTA's slab sequence, MMA warp m the MMAs of every NMMA-th tile.
+constexpr int NPROD = 4;
+constexpr int NMMA = 2;
+constexpr int FIRST_EPI = NPROD + NMMA;
+constexpr int NUM_THREADS = 32 * (FIRST_EPI + EPI_WARPS * EPI_GROUPS);
 constexpr int MAX_STAGES = 12;
 constexpr int PIPE_BYTES = 192 * 1024;   // operand ring (+ resident W) per CTA
 constexpr unsigned long long WAIT_LIMIT_NS = 1000000000ull;
@@ -195,7 +206,7 @@ template <int BN_TILE>
 struct SmemLayout {
   static constexpr int PARAM_BYTES = BN_TILE * 16;    // k and lambda, up to 8 bytes each, split over 8 warps
   static constexpr int PARAM_OFFSET = PIPE_BYTES;
-  static constexpr int BAR_OFFSET = PARAM_OFFSET + 4 * PARAM_BYTES;
+  static constexpr int BAR_OFFSET = PARAM_OFFSET + 4 * EPI_GROUPS * PARAM_BYTES;
   static constexpr int TOTAL = BAR_OFFSET + 512 + 1024;   // barriers + slack for 1024-byte alignment
   // accumulators in tensor memory: all 512 columns are used, so a narrow tile gets a deep ring
   static constexpr int NUM_ACC = 512 / BN_TILE;
@@ -232,6 +243,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   uint64_t *wres_bar = tmem_empty + NUM_ACC;
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(wres_bar + 1);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+  volatile int *tiles_landed = abort_flag + 1;      // tiles whose operands have all arrived (MMA warps)
 
   // operand ring: [resident W: total_slabs * B_BYTES][stage 0][stage 1]...
   const int wres_bytes = g.w_resident ? g.total_slabs * B_BYTES : 0;
@@ -246,10 +258,11 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     for (int b = 0; b < NUM_ACC; b++) { mbar_init(&tmem_full[b], 1); mbar_init(&tmem_empty[b], EPI_WARPS); }
     mbar_init(wres_bar, 1);
     *abort_flag = 0;
+    *tiles_landed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
-  if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+  if (warp == NPROD) tmem_alloc(tmem_slot, TMEM_COLS);
   tcgen05_fence_before();
   __syncthreads();
   tcgen05_fence_after();
@@ -257,12 +270,16 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
   const int units = g.m_tiles * g.n_tiles * g.k_slices;
 
-  if (warp == 0) {
-    // ------------------------------ TMA producer --------------------------------------------
+  if (warp < NPROD) {
+    // ------------------------------ TMA producers -------------------------------------------
+    // q numbers the CTA's slabs over all its units; slab q uses stage q % n_stages. This warp takes
+    // the slabs q = warp, warp + NPROD, ...
     if (lane == 0) {
-      int stage = 0; uint32_t phase = 0; int issued = 0;
+      int stage = warp % n_stages;
+      uint32_t phase = (uint32_t)(warp / n_stages) & 1u;
+      int skip = warp, issued = 0;
       bool ok = true;
-      if (g.w_resident) {
+      if (warp == 0 && g.w_resident) {
         mbar_arrive_expect_tx(wres_bar, (uint32_t)wres_bytes);
         for (int s = 0; s < g.total_slabs; s++) tma_load_2d(smem + s * B_BYTES, &map_b, wres_bar, s * BKB, 0);
       }
@@ -272,27 +289,32 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         const int slab0 = ks * g.slabs_per_slice;
         const int slab1 = min(slab0 + g.slabs_per_slice, g.total_slabs);
         for (int s = slab0; s < slab1; s++) {
+          if (skip > 0) { skip--; continue; }
+          skip = NPROD - 1;
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, g.status, ST_PRODUCER)) { ok = false; break; }
           uint8_t *a_dst = ring + stage * stage_bytes;
           mbar_arrive_expect_tx(&full_bar[stage], (uint32_t)stage_bytes);
           tma_load_2d(a_dst, &map_a, &full_bar[stage], s * BKB, mt * BM);
           if (!g.w_resident) tma_load_2d(a_dst + A_BYTES, &map_b, &full_bar[stage], s * BKB, nt * BN_TILE);
           issued++;
-          if (++stage == n_stages) { stage = 0; phase ^= 1; }
+          stage += NPROD;
+          while (stage >= n_stages) { stage -= n_stages; phase ^= 1; }
         }
       }
       if (*abort_flag) {
-        // something gave up: make sure no TMA write is still in flight into this CTA's memory
-        const int pending = issued < n_stages ? issued : n_stages;
+        // something gave up: make sure none of this warp's TMA writes is still in flight into the
+        // CTA's memory (walk back over the stages it filled last)
+        const int mine = (n_stages + NPROD - 1) / NPROD;
+        const int pending = issued < mine ? issued : mine;
         for (int i = 0; i < pending; i++) {
-          int st = stage - 1 - i; uint32_t ph = phase;
-          if (st < 0) { st += n_stages; ph ^= 1; }
+          stage -= NPROD;
+          while (stage < 0) { stage += n_stages; phase ^= 1; }
           const unsigned long long t0 = global_ns();
-          while (!mbar_try_wait(&full_bar[st], ph)) {
+          while (!mbar_try_wait(&full_bar[stage], phase)) {
             if (global_ns() - t0 > WAIT_LIMIT_NS) { if (g.status) atomicOr(g.status, ST_DRAIN); break; }
           }
         }
-        if (g.w_resident) {
+        if (warp == 0 && g.w_resident) {
           const unsigned long long t0 = global_ns();
           while (!mbar_try_wait(wres_bar, 0)) {
             if (global_ns() - t0 > WAIT_LIMIT_NS) { if (g.status) atomicOr(g.status, ST_DRAIN); break; }
@@ -300,24 +322,55 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         }
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------ MMA issuer ----------------------------------------------
+  } else if (warp < FIRST_EPI) {
+    // ------------------------------ MMA issuers ---------------------------------------------
+    // tile i of the CTA (accumulator i % NUM_ACC) belongs to MMA warp i % NMMA
     if (lane == 0) {
       constexpr uint32_t idesc = idesc_u8s8(BN_TILE);
-      int stage = 0; uint32_t phase = 0; int acc = 0; uint32_t acc_phase = 0;
+      static_assert(NUM_ACC % NMMA == 0, "an accumulator must always be filled by the same MMA warp");
+      const int me = warp - NPROD;
+      int q = 0;                                  // first slab of the current tile in the CTA's sequence
       bool ok = true;
       if (g.w_resident) ok = mbar_wait(wres_bar, 0, abort_flag, g.status, ST_MMA_WRES);
-      for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
+      int i = 0;
+      for (int u = blockIdx.x; u < units && ok; u += gridDim.x, i++) {
         int nt, mt, ks;
         decode_unit(g, u, nt, mt, ks);
         (void)nt; (void)mt;
         const int slab0 = ks * g.slabs_per_slice;
         const int slab1 = min(slab0 + g.slabs_per_slice, g.total_slabs);
+        const int q0 = q;
+        q += slab1 - slab0;
+        if (i % NMMA != me) continue;
+        // A parity wait is only meaningful while the waiter is less than one round of the ring
+        // ahead of the barrier. The other MMA warp owns the previous tile, so this one may not
+        // look at a stage's barrier before everything up to that tile has arrived.
+        if (NMMA > 1 && i > 0) {
+          unsigned long long t0 = 0;
+          for (unsigned spin = 1; *tiles_landed < i; spin++) {
+            if ((spin & 255u) == 0) {
+              if (*abort_flag) { ok = false; break; }
+              if (t0 == 0) t0 = global_ns();
+              else if (global_ns() - t0 > WAIT_LIMIT_NS) {
+                *abort_flag = 1;
+                if (g.status) atomicOr(g.status, ST_MMA_FULL);
+                ok = false;
+                break;
+              }
+            }
+          }
+          if (!ok) break;
+        }
+        const int acc = i % NUM_ACC;
+        const uint32_t acc_phase = (uint32_t)(i / NUM_ACC) & 1u;
+        int stage = q0 % n_stages;
+        uint32_t phase = (uint32_t)(q0 / n_stages) & 1u;
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, g.status, ST_MMA_TMEM)) break;
         tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN_TILE);
         for (int s = slab0; s < slab1; s++) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag, g.status, ST_MMA_FULL)) { ok = false; break; }
+          if (NMMA > 1 && s == slab1 - 1) *tiles_landed = i + 1;    // the next tile's warp may go ahead
           tcgen05_fence_after();
           const uint32_t a_addr = smem_u32(ring + stage * stage_bytes);
           const uint32_t b_addr = g.w_resident ? smem_u32(smem + s * B_BYTES) : a_addr + A_BYTES;
@@ -335,7 +388,6 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         }
         if (!ok) break;
         umma_commit(&tmem_full[acc]);          // accumulator complete
-        if (++acc == NUM_ACC) { acc = 0; acc_phase ^= 1; }
       }
     }
   } else {
@@ -343,12 +395,13 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     // A warp may only read the 32 TMEM lanes 32*(warp%4)..+31. Two warps share each lane quarter
     // and split the accumulator's 32-column chunks between them (even chunks / odd chunks).
     const int quad = warp & 3;
-    const int half = (warp - 2) >> 2;
+    const int half = ((warp - FIRST_EPI) >> 2) & 1;
+    const int grp = (warp - FIRST_EPI) >> 3;
     constexpr int HALF_COLS = BN_TILE / 2;     // columns this warp is responsible for
     // each epilogue warp keeps its own copy of the per-channel parameters of ITS columns, so
     // staging them needs no barrier between warps (a warp that gave up can never strand the others)
-    uint8_t *params = params_all + (warp - 2) * (L::PARAM_BYTES / 2);
-    int acc = 0; uint32_t acc_phase = 0;
+    uint8_t *params = params_all + (warp - FIRST_EPI) * (L::PARAM_BYTES / 2);
+    static_assert(NUM_ACC % EPI_GROUPS == 0, "a group must always meet the same accumulators");
     const Epilogue &e = g.epi;
     int *p_bias = reinterpret_cast<int *>(params);                 // non-BN modes
     int *p_k32 = reinterpret_cast<int *>(params);                  // EPI_BN32: k, lambda'
@@ -356,7 +409,10 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     long long *p_k64 = reinterpret_cast<long long *>(params);      // EPI_BN64
     long long *p_l64 = p_k64 + HALF_COLS;
     int staged_nt = -1;
-    for (int u = blockIdx.x; u < units; u += gridDim.x) {
+    // i counts the CTA's tiles; tile i lives in accumulator i % NUM_ACC
+    for (int i = grp, u = blockIdx.x + grp * gridDim.x; u < units; i += EPI_GROUPS, u += EPI_GROUPS * gridDim.x) {
+      const int acc = i % NUM_ACC;
+      const uint32_t acc_phase = (uint32_t)(i / NUM_ACC) & 1u;
       int nt, mt, ks;
       decode_unit(g, u, nt, mt, ks);
       const int n0 = nt * BN_TILE;
@@ -473,13 +529,12 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty[acc]);
-      if (++acc == NUM_ACC) { acc = 0; acc_phase ^= 1; }
     }
   }
 
   tcgen05_fence_before();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == NPROD) {
     tcgen05_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
@@ -643,6 +698,10 @@ bool launch_igemm_tc(Context &c, const ConvProblem &p)
   const int stage_bytes = g.w_resident ? a_bytes : a_bytes + b_bytes;
   int n_stages = (int)((PIPE_BYTES - (g.w_resident ? wres : 0)) / stage_bytes);
   if (n_stages > MAX_STAGES) n_stages = MAX_STAGES;
+  // a stage must always be refilled by the same producer warp (its parity waits assume it has seen
+  // every earlier round of that stage)
+  n_stages -= n_stages % NPROD;
+  if (n_stages < NPROD) { set_error(PULPNN_ERR_UNSUPPORTED, "igemm: operand ring too small"); return false; }
   g.n_stages = n_stages;
 
   if (!c.status_word) {

@@ -173,6 +173,8 @@ class Stager {
 // ---------------------------------------------------------------------------------------------
 bool launch_conv(Context &c, const ConvProblem &p);             // picks tensor-core or generic
 bool launch_conv_generic(Context &c, const ConvProblem &p);
+bool conv_smallcin_tc_supported(const ConvProblem &p);
+bool launch_conv_smallcin_tc(Context &c, const ConvProblem &p);
 bool conv_smallcin_supported(const ConvProblem &p);
 bool launch_conv_smallcin(Context &c, const ConvProblem &p);
 bool igemm_tc_supported(const Context &c, const ConvProblem &p);

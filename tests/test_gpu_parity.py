@@ -95,6 +95,31 @@ def test_conv_mobilenet_first_layer(gpu, restatement):
     same(gpu.conv(32, c["x"], c["w"], c["k"], c["lam"], **conv_kw(c)), want)
 
 
+@pytest.mark.parametrize("bits", [32, 64])
+@pytest.mark.parametrize("relu,bn", MODES)
+def test_conv_first_layer_tensor_core_kernel(bits, relu, bn, gpu, restatement):
+    """3x3 kernels on at most 3 input channels with 32 or 64 filters take the kernel that builds
+    the im2col tiles in shared memory: both strides, 1 to 3 input channels, left/top padding 0 to
+    2, widths up to the 128 columns of a tile, heights that are not a multiple of the four rows a
+    unit covers, more units than SMs."""
+    cases = [  # H, W, Cin, Cout, strides, pads (top, bottom, left, right), batch
+        (20, 32, 3, 32, (2, 2), (1, 1, 1, 1), 3),
+        (9, 16, 3, 64, (1, 1), (1, 1, 1, 1), 2),
+        (13, 64, 1, 32, (1, 1), (1, 1, 1, 1), 2),
+        (10, 48, 2, 32, (2, 1), (0, 1, 2, 1), 2),
+        (6, 256, 3, 32, (2, 2), (1, 1, 1, 1), 1),
+        (7, 128, 3, 64, (1, 1), (2, 1, 0, 2), 2),
+        (8, 16, 3, 32, (2, 2), (1, 1, 1, 1), 160),
+    ]
+    for (H, W, Cin, Cout, strides, pads, batch) in cases:
+        c = wl.conv_case(40, H, W, Cin, Cout, strides=strides, pads=pads, batch=batch, bits=bits,
+                         out_shift=9, with_bias=True, out_mult=5, relu=relu, bn=bn,
+                         k_range=(-64, 64), lam_range=(-2 ** 20, 2 ** 20))
+        want = restatement.conv(bits, c["x"], c["w"], c["k"], c["lam"], **conv_kw(c))
+        same(gpu.conv(bits, c["x"], c["w"], c["k"], c["lam"], **conv_kw(c)), want)
+    assert api.device_status() == 0
+
+
 def test_conv_against_compiled_reference(gpu, reference32):
     c = wl.conv_case(14, 17, 19, 8, 12, batch=2, bits=32, out_shift=10, with_bias=True)
     want = reference32.conv(32, c["x"], c["w"], c["k"], c["lam"], variant="HoWo", **conv_kw(c))
