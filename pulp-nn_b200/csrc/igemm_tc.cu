@@ -51,10 +51,10 @@ constexpr int EPI_GROUPS = 2;      // groups of EPI_WARPS; group g drains the CT
 // bounded the whole kernel. So both jobs are shared out: producer warp w issues the loads of every
 // NPROD-th slab of the CTA's slab sequence, MMA warp m the MMAs of every NMMA-th tile.
 constexpr int NPROD = 4;
-constexpr int NMMA = 2;
+constexpr int NMMA = 4;            // at most one per accumulator of the ring
 constexpr int FIRST_EPI = NPROD + NMMA;
 constexpr int NUM_THREADS = 32 * (FIRST_EPI + EPI_WARPS * EPI_GROUPS);
-constexpr int MAX_STAGES = 12;
+constexpr int MAX_STAGES = 44;     // short-K stages are small: what counts is the bytes in flight
 constexpr int PIPE_BYTES = 192 * 1024;   // operand ring (+ resident W) per CTA
 constexpr unsigned long long WAIT_LIMIT_NS = 1000000000ull;
 
@@ -197,20 +197,37 @@ struct TcParams {
   int M, N, K;
   int m_tiles, n_tiles, k_slices, slabs_per_slice, total_slabs;
   int vec_store;         // 2: 32-byte stores, 1: 16-byte stores, 0: scalar stores
-  int w_resident;        // 1: all of W sits in shared memory for the CTA's lifetime
+  int w_resident;        // 1: the CTA's n-tile of W sits in shared memory for the CTA's lifetime
+  int stationary;        // 1: a CTA keeps one n-tile (blockIdx % n_tiles) and walks down the m-tiles
   int n_stages;          // depth of the operand ring
   int *status;
 };
 
-template <int BN_TILE>
+// bytes of the operand ring (+ resident W). With TMA stores the epilogue stages one output tile
+// per group of warps in shared memory, which the ring has to make room for.
+__host__ __device__ constexpr int pipe_bytes(int bn, bool tma_out)
+{
+  return (tma_out && bn == 128) ? 176 * 1024 : PIPE_BYTES;
+}
+
+template <int BN_TILE, bool TMA_OUT>
 struct SmemLayout {
+  static constexpr int PIPE = pipe_bytes(BN_TILE, TMA_OUT);
   static constexpr int PARAM_BYTES = BN_TILE * 16;    // k and lambda, up to 8 bytes each, split over 8 warps
-  static constexpr int PARAM_OFFSET = PIPE_BYTES;
-  static constexpr int BAR_OFFSET = PARAM_OFFSET + 4 * EPI_GROUPS * PARAM_BYTES;
-  static constexpr int TOTAL = BAR_OFFSET + 512 + 1024;   // barriers + slack for 1024-byte alignment
+  static constexpr int PARAM_OFFSET = PIPE;
+  static constexpr int OUT_TILE_BYTES = TMA_OUT ? BM * BN_TILE : 0;        // per epilogue group
+  static constexpr int OUT_OFFSET = PARAM_OFFSET + 4 * EPI_GROUPS * PARAM_BYTES;
+  static constexpr int BAR_OFFSET = OUT_OFFSET + EPI_GROUPS * OUT_TILE_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + 1024 + 1024;  // barriers + slack for 1024-byte alignment
+  static_assert(TOTAL <= 232448, "shared memory of one CTA");
   // accumulators in tensor memory: all 512 columns are used, so a narrow tile gets a deep ring
   static constexpr int NUM_ACC = 512 / BN_TILE;
 };
+
+// The i-th work unit of this CTA. Stationary: n-tile fixed, m-tiles blockIdx/n_tiles, + gridDim/n_tiles, ...
+// (so a resident slice of W serves every unit of the CTA). Otherwise units are dealt round robin.
+__device__ __forceinline__ bool unit_at(const TcParams &g, int i, int units, int nt0, int m0, int m_step,
+                                        int &nt, int &mt, int &ks);
 
 // unit index -> (n-tile, m-tile, k-slice), n fastest. The common shapes (one n-tile, K not split)
 // need no division at all, which matters in the epilogue where this runs once per tile.
@@ -223,13 +240,40 @@ __device__ __forceinline__ void decode_unit(const TcParams &g, int u, int &nt, i
   if (g.k_slices != 1) { ks = r / g.m_tiles; mt = r - ks * g.m_tiles; }
 }
 
-// MODE: the final epilogue; PARTIAL: store raw int32 partial sums instead (split-K)
-template <int MODE, int BN_TILE, int BKB, bool PARTIAL>
+__device__ __forceinline__ bool unit_at(const TcParams &g, int i, int units, int nt0, int m0, int m_step,
+                                        int &nt, int &mt, int &ks)
+{
+  if (g.stationary) {
+    nt = nt0; ks = 0;
+    mt = m0 + i * m_step;
+    return mt < g.m_tiles;
+  }
+  const int u = blockIdx.x + i * gridDim.x;
+  if (u >= units) return false;
+  decode_unit(g, u, nt, mt, ks);
+  return true;
+}
+
+__device__ __forceinline__ void sts128(uint32_t addr, unsigned a, unsigned b, unsigned c, unsigned d)
+{
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, const void *src, int x, int y)
+{
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(smem_u32(src)), "r"(x), "r"(y)
+               : "memory");
+}
+
+// MODE: the final epilogue; PARTIAL: store raw int32 partial sums instead (split-K); TMA_OUT: the
+// uint8 output tile is staged in shared memory and leaves with one TMA store per tile
+template <int MODE, int BN_TILE, int BKB, bool PARTIAL, bool TMA_OUT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                const TcParams g)
+                const __grid_constant__ CUtensorMap map_out, const TcParams g)
 {
-  using L = SmemLayout<BN_TILE>;
+  using L = SmemLayout<BN_TILE, TMA_OUT>;
+  static_assert(!TMA_OUT || (!PARTIAL && MODE != EPI_RAW32 && BN_TILE <= 128), "TMA stores carry uint8 tiles of at most 128 columns");
   constexpr int A_BYTES = BM * BKB, B_BYTES = BN_TILE * BKB;
   constexpr int NUM_ACC = L::NUM_ACC;
   constexpr uint32_t TMEM_COLS = 512;
@@ -244,6 +288,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(wres_bar + 1);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
   volatile int *tiles_landed = abort_flag + 1;      // tiles whose operands have all arrived (MMA warps)
+  volatile uint8_t *issued_parity = reinterpret_cast<volatile uint8_t *>(tiles_landed + 1);   // per stage: 1 + parity of its last load
 
   // operand ring: [resident W: total_slabs * B_BYTES][stage 0][stage 1]...
   const int wres_bytes = g.w_resident ? g.total_slabs * B_BYTES : 0;
@@ -259,6 +304,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     mbar_init(wres_bar, 1);
     *abort_flag = 0;
     *tiles_landed = 0;
+    for (int s = 0; s < MAX_STAGES; s++) issued_parity[s] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -269,48 +315,48 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   const uint32_t tmem_base = *tmem_slot;
 
   const int units = g.m_tiles * g.n_tiles * g.k_slices;
+  // stationary CTAs: n-tile and first m-tile of this CTA, distance between its m-tiles
+  const int nt0 = g.stationary ? (int)(blockIdx.x % (unsigned)g.n_tiles) : 0;
+  const int m0 = g.stationary ? (int)(blockIdx.x / (unsigned)g.n_tiles) : 0;
+  const int m_step = g.stationary ? (int)(gridDim.x / (unsigned)g.n_tiles) : 0;
 
   if (warp < NPROD) {
     // ------------------------------ TMA producers -------------------------------------------
-    // q numbers the CTA's slabs over all its units; slab q uses stage q % n_stages. This warp takes
-    // the slabs q = warp, warp + NPROD, ...
+    // The CTA's slabs, over all its units, use the stages of the ring in turn. A stage is always
+    // refilled by the same warp (stage % NPROD): its parity wait on the stage's "empty" barrier is
+    // only meaningful because it has itself seen every earlier round of that stage.
     if (lane == 0) {
-      int stage = warp % n_stages;
-      uint32_t phase = (uint32_t)(warp / n_stages) & 1u;
-      int skip = warp, issued = 0;
+      int st = 0; uint32_t ph = 0;           // ring position of the current slab
       bool ok = true;
       if (warp == 0 && g.w_resident) {
         mbar_arrive_expect_tx(wres_bar, (uint32_t)wres_bytes);
-        for (int s = 0; s < g.total_slabs; s++) tma_load_2d(smem + s * B_BYTES, &map_b, wres_bar, s * BKB, 0);
+        for (int s = 0; s < g.total_slabs; s++) tma_load_2d(smem + s * B_BYTES, &map_b, wres_bar, s * BKB, nt0 * BN_TILE);
       }
-      for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
+      for (int i = 0; ok; i++) {
         int nt, mt, ks;
-        decode_unit(g, u, nt, mt, ks);
+        if (!unit_at(g, i, units, nt0, m0, m_step, nt, mt, ks)) break;
         const int slab0 = ks * g.slabs_per_slice;
         const int slab1 = min(slab0 + g.slabs_per_slice, g.total_slabs);
         for (int s = slab0; s < slab1; s++) {
-          if (skip > 0) { skip--; continue; }
-          skip = NPROD - 1;
-          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, g.status, ST_PRODUCER)) { ok = false; break; }
-          uint8_t *a_dst = ring + stage * stage_bytes;
-          mbar_arrive_expect_tx(&full_bar[stage], (uint32_t)stage_bytes);
-          tma_load_2d(a_dst, &map_a, &full_bar[stage], s * BKB, mt * BM);
-          if (!g.w_resident) tma_load_2d(a_dst + A_BYTES, &map_b, &full_bar[stage], s * BKB, nt * BN_TILE);
-          issued++;
-          stage += NPROD;
-          while (stage >= n_stages) { stage -= n_stages; phase ^= 1; }
+          if ((st & (NPROD - 1)) == warp) {
+            if (!mbar_wait(&empty_bar[st], ph ^ 1, abort_flag, g.status, ST_PRODUCER)) { ok = false; break; }
+            uint8_t *a_dst = ring + st * stage_bytes;
+            mbar_arrive_expect_tx(&full_bar[st], (uint32_t)stage_bytes);
+            tma_load_2d(a_dst, &map_a, &full_bar[st], s * BKB, mt * BM);
+            if (!g.w_resident) tma_load_2d(a_dst + A_BYTES, &map_b, &full_bar[st], s * BKB, nt * BN_TILE);
+            issued_parity[st] = (uint8_t)(1u + ph);
+          }
+          if (++st == n_stages) { st = 0; ph ^= 1; }
         }
       }
       if (*abort_flag) {
         // something gave up: make sure none of this warp's TMA writes is still in flight into the
-        // CTA's memory (walk back over the stages it filled last)
-        const int mine = (n_stages + NPROD - 1) / NPROD;
-        const int pending = issued < mine ? issued : mine;
-        for (int i = 0; i < pending; i++) {
-          stage -= NPROD;
-          while (stage < 0) { stage += n_stages; phase ^= 1; }
+        // CTA's memory (the last load into each of its stages)
+        for (int s2 = warp; s2 < n_stages; s2 += NPROD) {
+          if (issued_parity[s2] == 0) continue;
+          const uint32_t par = (uint32_t)issued_parity[s2] - 1u;
           const unsigned long long t0 = global_ns();
-          while (!mbar_try_wait(&full_bar[stage], phase)) {
+          while (!mbar_try_wait(&full_bar[s2], par)) {
             if (global_ns() - t0 > WAIT_LIMIT_NS) { if (g.status) atomicOr(g.status, ST_DRAIN); break; }
           }
         }
@@ -327,21 +373,24 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     // tile i of the CTA (accumulator i % NUM_ACC) belongs to MMA warp i % NMMA
     if (lane == 0) {
       constexpr uint32_t idesc = idesc_u8s8(BN_TILE);
-      static_assert(NUM_ACC % NMMA == 0, "an accumulator must always be filled by the same MMA warp");
+      // an accumulator must always be filled by the same MMA warp: no more warps than accumulators
+      constexpr int NM = NMMA < NUM_ACC ? NMMA : NUM_ACC;
+      static_assert(NUM_ACC % NM == 0, "an accumulator must always be filled by the same MMA warp");
       const int me = warp - NPROD;
-      int q = 0;                                  // first slab of the current tile in the CTA's sequence
-      bool ok = true;
-      if (g.w_resident) ok = mbar_wait(wres_bar, 0, abort_flag, g.status, ST_MMA_WRES);
-      int i = 0;
-      for (int u = blockIdx.x; u < units && ok; u += gridDim.x, i++) {
+      int st_next = 0; uint32_t ph_next = 0;      // ring position of the next tile's first slab
+      bool ok = me < NM;
+      if (ok && g.w_resident) ok = mbar_wait(wres_bar, 0, abort_flag, g.status, ST_MMA_WRES);
+      for (int i = 0; ok; i++) {
         int nt, mt, ks;
-        decode_unit(g, u, nt, mt, ks);
+        if (!unit_at(g, i, units, nt0, m0, m_step, nt, mt, ks)) break;
         (void)nt; (void)mt;
         const int slab0 = ks * g.slabs_per_slice;
         const int slab1 = min(slab0 + g.slabs_per_slice, g.total_slabs);
-        const int q0 = q;
-        q += slab1 - slab0;
-        if (i % NMMA != me) continue;
+        int stage = st_next;
+        uint32_t phase = ph_next;
+        st_next += slab1 - slab0;
+        while (st_next >= n_stages) { st_next -= n_stages; ph_next ^= 1; }
+        if ((i & (NM - 1)) != me) continue;
         // A parity wait is only meaningful while the waiter is less than one round of the ring
         // ahead of the barrier. The other MMA warp owns the previous tile, so this one may not
         // look at a stage's barrier before everything up to that tile has arrived.
@@ -363,8 +412,6 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         }
         const int acc = i % NUM_ACC;
         const uint32_t acc_phase = (uint32_t)(i / NUM_ACC) & 1u;
-        int stage = q0 % n_stages;
-        uint32_t phase = (uint32_t)(q0 / n_stages) & 1u;
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, g.status, ST_MMA_TMEM)) break;
         tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN_TILE);
@@ -409,12 +456,16 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     long long *p_k64 = reinterpret_cast<long long *>(params);      // EPI_BN64
     long long *p_l64 = p_k64 + HALF_COLS;
     int staged_nt = -1;
+    // TMA_OUT: the group's staging tile, and the one thread of the group that issues its stores
+    uint8_t *out_tile = smem + L::OUT_OFFSET + grp * L::OUT_TILE_BYTES;
+    const bool elected = ((warp - FIRST_EPI) & 7) == 0 && lane == 0;
+    bool dead = false;      // TMA_OUT: a wait ran out; keep meeting the group's barriers, do no work
     // i counts the CTA's tiles; tile i lives in accumulator i % NUM_ACC
-    for (int i = grp, u = blockIdx.x + grp * gridDim.x; u < units; i += EPI_GROUPS, u += EPI_GROUPS * gridDim.x) {
+    for (int i = grp;; i += EPI_GROUPS) {
+      int nt, mt, ks;
+      if (!unit_at(g, i, units, nt0, m0, m_step, nt, mt, ks)) break;
       const int acc = i % NUM_ACC;
       const uint32_t acc_phase = (uint32_t)(i / NUM_ACC) & 1u;
-      int nt, mt, ks;
-      decode_unit(g, u, nt, mt, ks);
       const int n0 = nt * BN_TILE;
       if (!PARTIAL && nt != staged_nt) {
         // per-channel parameters of this warp's columns -> shared memory. The bias is folded into
@@ -444,6 +495,76 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         }
         __syncwarp();
         staged_nt = nt;
+      }
+      if constexpr (TMA_OUT) {
+        // requantised bytes of this warp's columns, 8 words per 32-column chunk
+        constexpr int NCHUNK = HALF_COLS / 32;
+        unsigned w[NCHUNK][8];
+        if (!dead && !mbar_wait(&tmem_full[acc], acc_phase, abort_flag, g.status, ST_EPILOGUE)) dead = true;
+        if (!dead) {
+          tcgen05_fence_after();
+          const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN_TILE);
+#pragma unroll
+          for (int ch = 0; ch < NCHUNK; ch++) {
+            const int lc = ch * 32, c0 = ch * 64 + half * 32;
+            uint32_t v[32];
+            tmem_ld_32(t_row + (uint32_t)c0, v);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              int q[4];
+              if (MODE == EPI_BN32) {
+                const int4 kk = *reinterpret_cast<const int4 *>(p_k32 + lc + j);
+                const int4 ll = *reinterpret_cast<const int4 *>(p_l32 + lc + j);
+                q[0] = (int)((unsigned)kk.x * v[j + 0] + (unsigned)ll.x) >> e.shift;
+                q[1] = (int)((unsigned)kk.y * v[j + 1] + (unsigned)ll.y) >> e.shift;
+                q[2] = (int)((unsigned)kk.z * v[j + 2] + (unsigned)ll.z) >> e.shift;
+                q[3] = (int)((unsigned)kk.w * v[j + 3] + (unsigned)ll.w) >> e.shift;
+              } else {
+#pragma unroll
+                for (int t = 0; t < 4; t++) {
+                  const int a = (int)v[j + t];
+                  if (MODE == EPI_BN64)
+                    q[t] = (int)((long long)((unsigned long long)p_k64[lc + j + t] * (unsigned long long)(long long)a +
+                                             (unsigned long long)p_l64[lc + j + t]) >> e.shift);
+                  else if (MODE == EPI_MULT)
+                    q[t] = (int)(short)((int)((unsigned)e.out_mult * (unsigned)(a + p_bias[lc + j + t])) >> e.shift);
+                  else
+                    q[t] = (a + p_bias[lc + j + t]) >> e.shift;
+                }
+              }
+              w[ch][j >> 2] = pack4_sat_u8(q[0], q[1], q[2], q[3]);
+            }
+          }
+          // the accumulator is in registers: hand it back to the MMA warps before the stores
+          tcgen05_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+        }
+        // (A) the store of this group's previous tile has finished reading the staging tile
+        if (elected) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        asm volatile("bar.sync %0, 256;" ::"r"(1 + grp) : "memory");
+        if (!dead) {
+          // row r of the tile, 16-byte chunks cc, cc+1 of each 32-column chunk, swizzled the way the
+          // TMA store expects (BN_TILE-byte rows with the BN_TILE-byte swizzle): no bank conflicts
+          const int r = quad * 32 + lane;
+          const uint32_t rowaddr = smem_u32(out_tile) + (uint32_t)(r * BN_TILE);
+          const int x = BN_TILE == 128 ? (r & 7) : ((r >> 1) & 3);
+#pragma unroll
+          for (int ch = 0; ch < NCHUNK; ch++) {
+            const int cc = (ch * 64 + half * 32) >> 4;
+            sts128(rowaddr + (uint32_t)(((cc) ^ x) << 4), w[ch][0], w[ch][1], w[ch][2], w[ch][3]);
+            sts128(rowaddr + (uint32_t)(((cc + 1) ^ x) << 4), w[ch][4], w[ch][5], w[ch][6], w[ch][7]);
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
+        // (B) the tile is complete
+        asm volatile("bar.sync %0, 256;" ::"r"(1 + grp) : "memory");
+        if (elected && !dead) {
+          tma_store_2d(&map_out, out_tile, n0, mt * BM);     // rows past M and columns past N are dropped
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+        continue;
       }
       if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag, g.status, ST_EPILOGUE)) break;
       tcgen05_fence_after();
@@ -530,6 +651,8 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty[acc]);
     }
+    // the staging tiles must outlive the stores that read them
+    if (TMA_OUT && elected) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   }
 
   tcgen05_fence_before();
@@ -600,11 +723,14 @@ bool make_map(CUtensorMap *map, const void *base, int rows, int K, int box_rows,
   return true;
 }
 
-template <int MODE, int BN_TILE, int BKB, bool PARTIAL>
-bool launch_cfg(Context &c, const CUtensorMap &ma, const CUtensorMap &mb, const TcParams &g, int grid)
+// the three tensor maps of a launch (the output map only matters with TMA stores)
+struct TcMaps { CUtensorMap a, b, out; };
+
+template <int MODE, int BN_TILE, int BKB, bool PARTIAL, bool TMA_OUT>
+bool launch_cfg(Context &c, const TcMaps &m, const TcParams &g, int grid)
 {
-  using L = SmemLayout<BN_TILE>;
-  auto kern = igemm_tc_kernel<MODE, BN_TILE, BKB, PARTIAL>;
+  using L = SmemLayout<BN_TILE, TMA_OUT>;
+  auto kern = igemm_tc_kernel<MODE, BN_TILE, BKB, PARTIAL, TMA_OUT>;
   static bool attr_set = false;     // per instantiation
   if (!attr_set) {
     if (!cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL),
@@ -614,35 +740,39 @@ bool launch_cfg(Context &c, const CUtensorMap &ma, const CUtensorMap &mb, const 
   }
   // every configuration asks for more than half of an SM's shared memory, so exactly one CTA (and
   // its 512 tensor-memory columns) lives on an SM
-  kern<<<grid, NUM_THREADS, L::TOTAL, c.stream>>>(ma, mb, g);
+  kern<<<grid, NUM_THREADS, L::TOTAL, c.stream>>>(m.a, m.b, m.out, g);
   count_launch();
   return cuda_ok(cudaGetLastError(), "igemm_tc launch");
 }
 
-template <int MODE, int BN_TILE, bool PARTIAL>
-bool launch_bk(Context &c, const CUtensorMap &ma, const CUtensorMap &mb, const TcParams &g, int bkb, int grid)
+template <int MODE, int BN_TILE, bool PARTIAL, bool TMA_OUT>
+bool launch_bk(Context &c, const TcMaps &m, const TcParams &g, int bkb, int grid)
 {
-  if (bkb == 32) return launch_cfg<MODE, BN_TILE, 32, PARTIAL>(c, ma, mb, g, grid);
-  if (bkb == 64) return launch_cfg<MODE, BN_TILE, 64, PARTIAL>(c, ma, mb, g, grid);
-  return launch_cfg<MODE, BN_TILE, 128, PARTIAL>(c, ma, mb, g, grid);
+  if (bkb == 32) return launch_cfg<MODE, BN_TILE, 32, PARTIAL, TMA_OUT>(c, m, g, grid);
+  if (bkb == 64) return launch_cfg<MODE, BN_TILE, 64, PARTIAL, TMA_OUT>(c, m, g, grid);
+  return launch_cfg<MODE, BN_TILE, 128, PARTIAL, TMA_OUT>(c, m, g, grid);
 }
 
 template <int MODE, bool PARTIAL>
-bool launch_bn(Context &c, const CUtensorMap &ma, const CUtensorMap &mb, const TcParams &g, int bn, int bkb, int grid)
+bool launch_bn(Context &c, const TcMaps &m, const TcParams &g, int bn, int bkb, int grid, bool tma_out)
 {
-  if (bn == 64)  return launch_bk<MODE, 64, PARTIAL>(c, ma, mb, g, bkb, grid);
-  if (bn == 128) return launch_bk<MODE, 128, PARTIAL>(c, ma, mb, g, bkb, grid);
-  return launch_bk<MODE, 256, PARTIAL>(c, ma, mb, g, bkb, grid);
+  if constexpr (!PARTIAL && MODE != EPI_RAW32) {
+    if (tma_out && bn == 64)  return launch_bk<MODE, 64, false, true>(c, m, g, bkb, grid);
+    if (tma_out && bn == 128) return launch_bk<MODE, 128, false, true>(c, m, g, bkb, grid);
+  }
+  if (bn == 64)  return launch_bk<MODE, 64, PARTIAL, false>(c, m, g, bkb, grid);
+  if (bn == 128) return launch_bk<MODE, 128, PARTIAL, false>(c, m, g, bkb, grid);
+  return launch_bk<MODE, 256, PARTIAL, false>(c, m, g, bkb, grid);
 }
 
-bool launch_final(Context &c, const CUtensorMap &ma, const CUtensorMap &mb, const TcParams &g, int bn, int bkb, int grid)
+bool launch_final(Context &c, const TcMaps &m, const TcParams &g, int bn, int bkb, int grid, bool tma_out)
 {
   switch (g.epi.mode) {
-    case EPI_NONE: return launch_bn<EPI_NONE, false>(c, ma, mb, g, bn, bkb, grid);
-    case EPI_MULT: return launch_bn<EPI_MULT, false>(c, ma, mb, g, bn, bkb, grid);
-    case EPI_BN32: return launch_bn<EPI_BN32, false>(c, ma, mb, g, bn, bkb, grid);
-    case EPI_BN64: return launch_bn<EPI_BN64, false>(c, ma, mb, g, bn, bkb, grid);
-    default:       return launch_bn<EPI_RAW32, false>(c, ma, mb, g, bn, bkb, grid);
+    case EPI_NONE: return launch_bn<EPI_NONE, false>(c, m, g, bn, bkb, grid, tma_out);
+    case EPI_MULT: return launch_bn<EPI_MULT, false>(c, m, g, bn, bkb, grid, tma_out);
+    case EPI_BN32: return launch_bn<EPI_BN32, false>(c, m, g, bn, bkb, grid, tma_out);
+    case EPI_BN64: return launch_bn<EPI_BN64, false>(c, m, g, bn, bkb, grid, tma_out);
+    default:       return launch_bn<EPI_RAW32, false>(c, m, g, bn, bkb, grid, false);
   }
 }
 
@@ -665,44 +795,58 @@ bool launch_igemm_tc(Context &c, const ConvProblem &p)
   TcParams g;
   g.M = p.B * p.Ho * p.Wo; g.N = p.Cout; g.K = p.Cin;
   g.epi = p.epi;
-  const int bn = g.N <= 64 ? 64 : (g.N <= 128 ? 128 : 256);
+  const bool raw = p.epi.mode == EPI_RAW32;
   // K-slab width: the narrowest box that does not fetch bytes beyond K; wider boxes for long K
   int bkb = 128;
   if (g.K <= 32) bkb = 32;
   else if (g.K <= 64) bkb = 64;
   else if (g.K < 128 && g.K % 64 != 0) bkb = 32;       // 80, 96, 112: no padded fetch with 32-byte slabs
   g.m_tiles = (g.M + BM - 1) / BM;
-  g.n_tiles = (g.N + bn - 1) / bn;
   g.total_slabs = (g.K + bkb - 1) / bkb;
   const int sms = c.sm_count > 0 ? c.sm_count : 148;
+  // uint8 tiles can leave through TMA stores (staged in shared memory, at most 128 columns wide)
+  const bool out_ok = !raw && g.N % 16 == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0;
 
-  // split K only when the tiles alone cannot occupy the GPU and there is enough K to share
-  int slices = 1;
-  const int tiles = g.m_tiles * g.n_tiles;
-  if (c.opt_split_k > 0) slices = c.opt_split_k;
-  else if (tiles * 2 <= sms && g.total_slabs >= 8) {
-    slices = sms / tiles;
-    if (slices > g.total_slabs / 4) slices = g.total_slabs / 4;
-    if (slices > 16) slices = 16;
-  }
-  if (slices > g.total_slabs) slices = g.total_slabs;
-  if (slices < 1) slices = 1;
-  g.slabs_per_slice = (g.total_slabs + slices - 1) / slices;
-  g.k_slices = (g.total_slabs + g.slabs_per_slice - 1) / g.slabs_per_slice;
-
-  // W stays in shared memory when one n-tile covers it, K is not split and it leaves room for at
-  // least four stages of A
-  const int a_bytes = BM * bkb, b_bytes = bn * bkb;
-  const long long wres = (long long)g.total_slabs * b_bytes;
-  g.w_resident = (g.n_tiles == 1 && g.k_slices == 1 && wres + 4LL * a_bytes <= PIPE_BYTES) ? 1 : 0;
-  const int stage_bytes = g.w_resident ? a_bytes : a_bytes + b_bytes;
-  int n_stages = (int)((PIPE_BYTES - (g.w_resident ? wres : 0)) / stage_bytes);
-  if (n_stages > MAX_STAGES) n_stages = MAX_STAGES;
-  // a stage must always be refilled by the same producer warp (its parity waits assume it has seen
-  // every earlier round of that stage)
-  n_stages -= n_stages % NPROD;
-  if (n_stages < NPROD) { set_error(PULPNN_ERR_UNSUPPORTED, "igemm: operand ring too small"); return false; }
-  g.n_stages = n_stages;
+  int bn = 0, tiles = 0;
+  bool tma_out = false;
+  auto configure = [&](int bn_try, bool tma_try) {
+    bn = bn_try;
+    g.n_tiles = (g.N + bn - 1) / bn;
+    tiles = g.m_tiles * g.n_tiles;
+    // split K only when the tiles alone cannot occupy the GPU and there is enough K to share
+    int slices = 1;
+    if (c.opt_split_k > 0) slices = c.opt_split_k;
+    else if (tiles * 2 <= sms && g.total_slabs >= 8) {
+      slices = sms / tiles;
+      if (slices > g.total_slabs / 4) slices = g.total_slabs / 4;
+      if (slices > 16) slices = 16;
+    }
+    if (slices > g.total_slabs) slices = g.total_slabs;
+    if (slices < 1) slices = 1;
+    g.slabs_per_slice = (g.total_slabs + slices - 1) / slices;
+    g.k_slices = (g.total_slabs + g.slabs_per_slice - 1) / g.slabs_per_slice;
+    tma_out = tma_try && g.k_slices == 1;
+    // The CTA's n-tile of W stays in shared memory when K is not split and it leaves room for at
+    // least four stages of A. Such CTAs keep their n-tile and walk down the m-tiles.
+    const int pipe = pipe_bytes(bn, tma_out);
+    const int a_bytes = BM * bkb, b_bytes = bn * bkb;
+    const long long wres = (long long)g.total_slabs * b_bytes;
+    g.w_resident = (g.k_slices == 1 && g.n_tiles <= sms && wres + 4LL * a_bytes <= pipe) ? 1 : 0;
+    g.stationary = g.w_resident;
+    const int stage_bytes = g.w_resident ? a_bytes : a_bytes + b_bytes;
+    int n_stages = (int)((pipe - (g.w_resident ? wres : 0)) / stage_bytes);
+    if (n_stages > MAX_STAGES) n_stages = MAX_STAGES;
+    g.n_stages = n_stages;
+  };
+  // Measured on MobileNet's pointwise layers: 64-column tiles are too short-lived for the staging
+  // round trip to pay; wide outputs with K above 256 run faster as 256-column tiles (half as many
+  // tiles and slabs for the single-thread roles to get through).
+  if (g.N <= 64) configure(64, false);
+  else if (g.N <= 128 || (out_ok && g.K <= 256)) configure(128, out_ok);
+  else configure(256, false);
+  // a 128-column slice of a wide W that does not fit is re-streamed for every m-tile: the 256-column
+  // tile (plain stores) halves that traffic
+  if (g.N > 128 && bn == 128 && !g.w_resident) configure(256, false);
 
   if (!c.status_word) {
     if (!cuda_ok(cudaMalloc(&c.status_word, sizeof(int)), "cudaMalloc(status)")) return false;
@@ -710,20 +854,25 @@ bool launch_igemm_tc(Context &c, const ConvProblem &p)
   }
   g.status = c.status_word;
 
-  CUtensorMap ma, mb;
-  if (!make_map(&ma, p.in, g.M, g.K, BM, bkb)) return false;
-  if (!make_map(&mb, p.w, g.N, g.K, bn, bkb)) return false;
+  TcMaps maps;
+  if (!make_map(&maps.a, p.in, g.M, g.K, BM, bkb)) return false;
+  if (!make_map(&maps.b, p.w, g.N, g.K, bn, bkb)) return false;
+  maps.out = maps.a;
+  if (tma_out && !make_map(&maps.out, p.out, g.M, g.N, BM, bn)) return false;    // box = bn bytes x 128 rows
 
   const int units = tiles * g.k_slices;
-  const int grid = units < sms ? units : sms;
-  const bool raw = p.epi.mode == EPI_RAW32;
+  int grid = units < sms ? units : sms;
+  if (g.stationary) {
+    const int per = sms / g.n_tiles;
+    grid = g.n_tiles * (per < g.m_tiles ? per : g.m_tiles);
+  }
 
   if (g.k_slices == 1) {
     g.out = p.out;
     const int align = raw ? 4 : 16;
     g.vec_store = (g.N % align == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
     if (!raw && g.vec_store && g.N % 32 == 0 && (reinterpret_cast<uintptr_t>(p.out) & 31) == 0) g.vec_store = 2;
-    return launch_final(c, ma, mb, g, bn, bkb, grid);
+    return launch_final(c, maps, g, bn, bkb, grid, tma_out);
   }
   const size_t part_bytes = (size_t)g.k_slices * g.M * g.N * sizeof(int);
   int *partials = static_cast<int *>(ctx_scratch(c, part_bytes));
@@ -731,7 +880,7 @@ bool launch_igemm_tc(Context &c, const ConvProblem &p)
   g.out = partials;
   g.vec_store = (g.N % 4 == 0);
   // partial sums need no epilogue mode: one instantiation serves them all
-  if (!launch_bn<EPI_NONE, true>(c, ma, mb, g, bn, bkb, grid)) return false;
+  if (!launch_bn<EPI_NONE, true>(c, maps, g, bn, bkb, grid, false)) return false;
   const size_t total = (size_t)g.M * g.N;
   const unsigned blocks = (unsigned)((total + 255) / 256 < (size_t)sms * 8 ? (total + 255) / 256 : (size_t)sms * 8);
   switch (p.epi.mode) {
@@ -846,19 +995,21 @@ extern "C" int pulpnn_linear_out_32_static_scratch(const uint8_t *pInBuffer, con
   if (!partials) return c.err;
 
   g.w_resident = 0;
+  g.stationary = 0;
   g.n_stages = PIPE_BYTES / (BM * bkb + bn * bkb);
   if (g.n_stages > MAX_STAGES) g.n_stages = MAX_STAGES;
   g.status = nullptr;                      // the status word of the ordinary path is allocated; do without
   g.out = partials;
   g.vec_store = (g.N % 4 == 0);
-  CUtensorMap ma, mb;
-  if (!make_map(&ma, p.in, g.M, g.K, BM, bkb)) return c.err;
-  if (!make_map(&mb, p.w, g.N, g.K, bn, bkb)) return c.err;
+  TcMaps maps;
+  if (!make_map(&maps.a, p.in, g.M, g.K, BM, bkb)) return c.err;
+  if (!make_map(&maps.b, p.w, g.N, g.K, bn, bkb)) return c.err;
+  maps.out = maps.a;
   const int sms = c.sm_count > 0 ? c.sm_count : 148;
   const int units = g.m_tiles * g.n_tiles * g.k_slices;
   // Nothing in the scratch has to start at zero: the GEMM below writes every partial sum the
   // reduction reads (each slice owns at least one K slab, every tile of every slice is a unit).
-  if (!launch_bn<EPI_NONE, true>(c, ma, mb, g, bn, bkb, units < sms ? units : sms)) return c.err;
+  if (!launch_bn<EPI_NONE, true>(c, maps, g, bn, bkb, units < sms ? units : sms, false)) return c.err;
   const size_t total = (size_t)g.M * g.N;
   const unsigned blocks = (unsigned)((total + 255) / 256 < (size_t)sms * 8 ? (total + 255) / 256 : (size_t)sms * 8);
   splitk_reduce_kernel<EPI_RAW32><<<blocks, 256, 0, c.stream>>>(partials, pOutBuffer, p.epi, g.M, g.N, g.k_slices);
