@@ -297,7 +297,7 @@ def run_gpu_arm(args):
         per_layer.append({"layer": L["name"], "ms": round(float(t_ms), 4),
                           "GOPs": round(gop / (t_ms / 1e3), 1), "GBs": round(gb / (t_ms / 1e3), 1),
                           "hbm_frac": round(gb / (t_ms / 1e3) / hbm_peak, 3)})
-        kname = {"conv": "conv_smallcin_kernel", "depthwise": "depthwise_hwc3x3_kernel",
+        kname = {"conv": "conv_smallcin_tc_kernel", "depthwise": "depthwise_hwc3x3_tma_kernel",
                  "pointwise": "igemm_tc_kernel", "avgpool": "avgpool_kernel",
                  "linear32": "igemm_tc_kernel"}[L["op"]]
         k = by_kernel.setdefault(kname, {"ms": 0.0, "bytes": 0.0, "launches": 0})

@@ -10,15 +10,16 @@
 // bytes of filter row fy followed by zeros, chunk 3 = zeros, and the filters are re-packed the same
 // way once per CTA. So K = 64, two MMAs of K = 32 per tile of 128 pixels x BN output channels.
 //
-// Roles in a CTA (15 warps, persistent over units = 4 consecutive output rows of one image):
+// Roles in a CTA (23 warps, persistent over units = 4 consecutive output rows of one image):
 //   warp 0, one lane   TMA: the 3*SY+3 input rows a unit needs, as one 4-D box of the input seen
-//                      as [B][H][W*Cin/16][16 bytes]; rows above and below the image are zeros
+//                      as [B][H][pieces of a row][32 or 16 bytes]; rows above and below the image
+//                      are zeros
 //   warps 1..4         builders: thread = output column. Per input row three aligned words, one
 //                      funnel shift each and a mask (columns left/right of the image) give the
 //                      window's 9 bytes; 16-byte stores put them into the four tiles of the unit
 //   warps 5..6         one lane each issues the two tcgen05.mma of alternate tiles
-//   warps 7..14        epilogue, two groups that alternate tiles: tcgen05.ld (lane = pixel), bias,
-//                      requantisation, one 32-byte store per 32 output channels
+//   warps 7..22        epilogue, four groups that take tiles in turn: tcgen05.ld (lane = pixel),
+//                      bias, requantisation, one 32-byte store per 32 output channels
 // Every mbarrier wait is bounded (sm100_primitives.cuh).
 #include "internal.cuh"
 #include "sm100_primitives.cuh"
@@ -33,7 +34,10 @@ constexpr int ROWS_OUT = 4;        // output rows (= tiles) per unit
 constexpr int NA = 8;              // ring of im2col tiles = ring of accumulators
 constexpr int NIN = 3;             // ring of input-row stages
 constexpr int A_TILE_BYTES = 128 * 64;
-constexpr int BUILD_WARPS = 4, MMA_WARPS = 2, EPI_GROUP_WARPS = 4, EPI_GROUPS_N = 2;
+// a warp needs about a thousand cycles to drain its quarter of an accumulator (tcgen05.ld, 32 x
+// requantise, store: one dependent chain), so four groups keep four tiles in flight
+constexpr int BUILD_WARPS = 4, MMA_WARPS = 2, EPI_GROUP_WARPS = 4, EPI_GROUPS_N = 4;
+static_assert(NA % EPI_GROUPS_N == 0 && NA % MMA_WARPS == 0, "a ring slot must always meet the same warps");
 constexpr int FIRST_BUILD = 1, FIRST_MMA = FIRST_BUILD + BUILD_WARPS, FIRST_EPILOGUE = FIRST_MMA + MMA_WARPS;
 constexpr int THREADS = 32 * (FIRST_EPILOGUE + EPI_GROUP_WARPS * EPI_GROUPS_N);
 constexpr int ST_C1_TMA = 0x1000, ST_C1_BUILD = 0x2000, ST_C1_MMA = 0x4000, ST_C1_EPI = 0x8000;
@@ -238,7 +242,7 @@ conv_smallcin_tc_kernel(const __grid_constant__ CUtensorMap map_in, const SmallT
       }
     }
   } else {
-    // ------------------------------ epilogue: two groups alternate tiles -----------------------
+    // ------------------------------ epilogue: the groups take tiles in turn ---------------------
     const int grp = (warp - FIRST_EPILOGUE) / EPI_GROUP_WARPS;
     const int quad = warp & 3;                               // the TMEM lanes this warp may read
     const int ox = quad * 32 + lane;
@@ -361,11 +365,13 @@ bool launch_conv_smallcin_tc(Context &c, const ConvProblem &p)
   g.units = p.B * g.groups;
   g.status = ctx_status_word(c);
   if (!g.status) return false;
-  // the input as [B][H][row_bytes/16][16]: one box = all the 16-byte pieces of rows_in rows
+  // the input as [B][H][row_bytes/piece][piece]: one box = all the pieces of rows_in rows. Pieces
+  // of 32 bytes where the row allows it: the TMA unit fetches whole 32-byte sectors either way.
+  const unsigned piece = g.row_bytes % 32 == 0 ? 32 : 16;
   CUtensorMap map;
-  cuuint64_t dims[4] = {16, (cuuint64_t)(g.row_bytes / 16), (cuuint64_t)p.H, (cuuint64_t)p.B};
-  cuuint64_t strides[3] = {16, (cuuint64_t)g.row_bytes, (cuuint64_t)p.H * g.row_bytes};
-  cuuint32_t box[4] = {16, (cuuint32_t)(g.row_bytes / 16), (cuuint32_t)rows_in_of(p.sy), 1};
+  cuuint64_t dims[4] = {piece, (cuuint64_t)(g.row_bytes / piece), (cuuint64_t)p.H, (cuuint64_t)p.B};
+  cuuint64_t strides[3] = {piece, (cuuint64_t)g.row_bytes, (cuuint64_t)p.H * g.row_bytes};
+  cuuint32_t box[4] = {piece, (cuuint32_t)(g.row_bytes / piece), (cuuint32_t)rows_in_of(p.sy), 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   const CUresult r = encode_tiled_fn()(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<uint8_t *>(p.in), dims, strides, box,
                                        estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,

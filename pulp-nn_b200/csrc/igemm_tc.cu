@@ -278,7 +278,8 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   constexpr int NUM_ACC = L::NUM_ACC;
   constexpr uint32_t TMEM_COLS = 512;
   extern __shared__ uint8_t smem_raw[];
-  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  // aligned by an offset, not by a cast, so that the compiler still knows this is shared memory
+  uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint8_t *params_all = smem + L::PARAM_OFFSET;
   uint64_t *full_bar = reinterpret_cast<uint64_t *>(smem + L::BAR_OFFSET);
   uint64_t *empty_bar = full_bar + MAX_STAGES;
