@@ -10,15 +10,15 @@
 // bytes of filter row fy followed by zeros, chunk 3 = zeros, and the filters are re-packed the same
 // way once per CTA. So K = 64, two MMAs of K = 32 per tile of 128 pixels x BN output channels.
 //
-// Roles in a CTA (23 warps, persistent over units = 4 consecutive output rows of one image):
+// Roles in a CTA (25 warps, persistent over units = 4 consecutive output rows of one image):
 //   warp 0, one lane   TMA: the 3*SY+3 input rows a unit needs, as one 4-D box of the input seen
 //                      as [B][H][pieces of a row][32 or 16 bytes]; rows above and below the image
 //                      are zeros
 //   warps 1..4         builders: thread = output column. Per input row three aligned words, one
 //                      funnel shift each and a mask (columns left/right of the image) give the
 //                      window's 9 bytes; 16-byte stores put them into the four tiles of the unit
-//   warps 5..6         one lane each issues the two tcgen05.mma of alternate tiles
-//   warps 7..22        epilogue, four groups that take tiles in turn: tcgen05.ld (lane = pixel),
+//   warps 5..8         one lane each issues the two tcgen05.mma of every fourth tile
+//   warps 9..24        epilogue, four groups that take tiles in turn: tcgen05.ld (lane = pixel),
 //                      bias, requantisation, one 32-byte store per 32 output channels
 // Every mbarrier wait is bounded (sm100_primitives.cuh).
 #include "internal.cuh"
@@ -36,7 +36,7 @@ constexpr int NIN = 3;             // ring of input-row stages
 constexpr int A_TILE_BYTES = 128 * 64;
 // a warp needs about a thousand cycles to drain its quarter of an accumulator (tcgen05.ld, 32 x
 // requantise, store: one dependent chain), so four groups keep four tiles in flight
-constexpr int BUILD_WARPS = 4, MMA_WARPS = 2, EPI_GROUP_WARPS = 4, EPI_GROUPS_N = 4;
+constexpr int BUILD_WARPS = 4, MMA_WARPS = 4, EPI_GROUP_WARPS = 4, EPI_GROUPS_N = 4;
 static_assert(NA % EPI_GROUPS_N == 0 && NA % MMA_WARPS == 0, "a ring slot must always meet the same warps");
 constexpr int FIRST_BUILD = 1, FIRST_MMA = FIRST_BUILD + BUILD_WARPS, FIRST_EPILOGUE = FIRST_MMA + MMA_WARPS;
 constexpr int THREADS = 32 * (FIRST_EPILOGUE + EPI_GROUP_WARPS * EPI_GROUPS_N);

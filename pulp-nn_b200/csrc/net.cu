@@ -169,11 +169,15 @@ int run_impl(pulpnn_net *net, const uint8_t *input, void *output, int n, int n_l
   if (in_dev) {
     if (!run_device(c, net, din, dout, n, n_layers)) return c.err;
   } else {
-    // Host input: copy in slices on a second stream so that the copy of slice i+1 overlaps the
-    // compute of slice i. A slice is a whole number of micro-batches.
+    // Host input: copy in about four slices on a second stream, each slice going through the whole
+    // stack as soon as it has landed, so that the copy of slice i+1 overlaps the compute of slice i
+    // (the copy is the longer of the two: 154 MB of images take longer to cross PCIe than to
+    // classify). A slice is a whole number of micro-batches, or a quarter of the images when the
+    // micro-batch is larger than that.
     const int micro = net->micro > 0 ? net->micro : n;
-    int slice = micro;
-    while (slice < n && slice * 4 < n) slice += micro;          // about four slices
+    const int quarter = (n + 3) / 4;
+    int slice = micro < quarter ? micro : quarter;
+    while (slice < n && slice * 4 < n) slice += micro;
     const size_t img_in = net->layers.front().in_bytes, img_out = net->layers[n_layers - 1].out_bytes;
     int idx = 0;
     for (int i0 = 0; i0 < n; i0 += slice, idx++) {
