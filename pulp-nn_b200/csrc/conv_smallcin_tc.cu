@@ -36,7 +36,7 @@ constexpr int NIN = 3;             // ring of input-row stages
 constexpr int A_TILE_BYTES = 128 * 64;
 // a warp needs about a thousand cycles to drain its quarter of an accumulator (tcgen05.ld, 32 x
 // requantise, store: one dependent chain), so four groups keep four tiles in flight
-constexpr int BUILD_WARPS = 4, MMA_WARPS = 4, EPI_GROUP_WARPS = 4, EPI_GROUPS_N = 4;
+constexpr int BUILD_WARPS = 4, MMA_WARPS = 2, EPI_GROUP_WARPS = 4, EPI_GROUPS_N = 2;
 static_assert(NA % EPI_GROUPS_N == 0 && NA % MMA_WARPS == 0, "a ring slot must always meet the same warps");
 constexpr int FIRST_BUILD = 1, FIRST_MMA = FIRST_BUILD + BUILD_WARPS, FIRST_EPILOGUE = FIRST_MMA + MMA_WARPS;
 constexpr int THREADS = 32 * (FIRST_EPILOGUE + EPI_GROUP_WARPS * EPI_GROUPS_N);
@@ -246,6 +246,17 @@ conv_smallcin_tc_kernel(const __grid_constant__ CUtensorMap map_in, const SmallT
     const int grp = (warp - FIRST_EPILOGUE) / EPI_GROUP_WARPS;
     const int quad = warp & 3;                               // the TMEM lanes this warp may read
     const int ox = quad * 32 + lane;
+    // 32 filters with 32-bit batch normalisation: k and lambda live in registers for the CTA's
+    // lifetime, so a tile costs one multiply-add and one shift per output and no parameter loads
+    constexpr bool REG_PARAMS = MODE == EPI_BN32 && BN == 32;
+    int kr[32], lr[32];
+    if (REG_PARAMS) {
+#pragma unroll
+      for (int j = 0; j < 32; j++) {
+        kr[j] = reinterpret_cast<const int *>(params)[j];
+        lr[j] = reinterpret_cast<const int *>(params)[BN + j];
+      }
+    }
     int i = 0;
     bool ok = true;
     for (int u = blockIdx.x; u < g.units && ok; u += gridDim.x) {
@@ -268,7 +279,10 @@ conv_smallcin_tc_kernel(const __grid_constant__ CUtensorMap map_in, const SmallT
 #pragma unroll
           for (int j = 0; j < 32; j += 4) {
             int q[4];
-            if (MODE == EPI_BN32) {
+            if (REG_PARAMS) {
+#pragma unroll
+              for (int t = 0; t < 4; t++) q[t] = (int)((unsigned)kr[j + t] * v[j + t] + (unsigned)lr[j + t]) >> e.shift;
+            } else if (MODE == EPI_BN32) {
               const int4 kk = *reinterpret_cast<const int4 *>(reinterpret_cast<const int *>(params) + c0 + j);
               const int4 ll = *reinterpret_cast<const int4 *>(reinterpret_cast<const int *>(params) + BN + c0 + j);
               q[0] = (int)((unsigned)kk.x * v[j + 0] + (unsigned)ll.x) >> e.shift;
