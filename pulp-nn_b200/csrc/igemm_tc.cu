@@ -302,7 +302,8 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < MAX_STAGES; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    for (int b = 0; b < NUM_ACC; b++) { mbar_init(&tmem_full[b], 1); mbar_init(&tmem_empty[b], EPI_WARPS); }
+    // an accumulator is free again once every warp that drains it has arrived (see the epilogue)
+    for (int b = 0; b < NUM_ACC; b++) { mbar_init(&tmem_full[b], 1); mbar_init(&tmem_empty[b], BN_TILE == 256 ? 16 : 8); }
     mbar_init(wres_bar, 1);
     *abort_flag = 0;
     *tiles_landed = 0;
@@ -440,17 +441,21 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       }
     }
   } else {
-    // ------------------------------ epilogue (warps 2..9) ------------------------------------
-    // A warp may only read the 32 TMEM lanes 32*(warp%4)..+31. Two warps share each lane quarter
-    // and split the accumulator's 32-column chunks between them (even chunks / odd chunks).
+    // ------------------------------ epilogue ----------------------------------------------------
+    // A warp may only read the 32 TMEM lanes 32*(warp%4)..+31. NSPLIT warps share each lane quarter
+    // of a tile and deal its 32-column chunks out among them. A 256-column tile takes all sixteen
+    // warps (there are only two accumulators, so the sooner one is drained the better); narrower
+    // tiles take eight, and the two groups of eight alternate tiles.
+    constexpr int NSPLIT = BN_TILE == 256 ? 4 : 2;
+    constexpr int GROUPS = EPI_WARPS * EPI_GROUPS / (4 * NSPLIT);
     const int quad = warp & 3;
-    const int half = ((warp - FIRST_EPI) >> 2) & 1;
-    const int grp = (warp - FIRST_EPI) >> 3;
-    constexpr int HALF_COLS = BN_TILE / 2;     // columns this warp is responsible for
+    const int half = ((warp - FIRST_EPI) >> 2) % NSPLIT;      // which share of the chunks
+    const int grp = (warp - FIRST_EPI) / (4 * NSPLIT);
+    constexpr int HALF_COLS = BN_TILE / NSPLIT;     // columns this warp is responsible for
     // each epilogue warp keeps its own copy of the per-channel parameters of ITS columns, so
     // staging them needs no barrier between warps (a warp that gave up can never strand the others)
     uint8_t *params = params_all + (warp - FIRST_EPI) * (L::PARAM_BYTES / 2);
-    static_assert(NUM_ACC % EPI_GROUPS == 0, "a group must always meet the same accumulators");
+    static_assert(NUM_ACC % GROUPS == 0, "a group must always meet the same accumulators");
     const Epilogue &e = g.epi;
     int *p_bias = reinterpret_cast<int *>(params);                 // non-BN modes
     int *p_k32 = reinterpret_cast<int *>(params);                  // EPI_BN32: k, lambda'
@@ -463,7 +468,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const bool elected = ((warp - FIRST_EPI) & 7) == 0 && lane == 0;
     bool dead = false;      // TMA_OUT: a wait ran out; keep meeting the group's barriers, do no work
     // i counts the CTA's tiles; tile i lives in accumulator i % NUM_ACC
-    for (int i = grp;; i += EPI_GROUPS) {
+    for (int i = grp;; i += GROUPS) {
       int nt, mt, ks;
       if (!unit_at(g, i, units, nt0, m0, m_step, nt, mt, ks)) break;
       const int acc = i % NUM_ACC;
@@ -472,10 +477,10 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       if (!PARTIAL && nt != staged_nt) {
         // per-channel parameters of this warp's columns -> shared memory. The bias is folded into
         // lambda: k*(acc+b)+lambda == k*acc + (k*b+lambda) in wrap-around arithmetic.
-        // Local slot i holds column (i/32)*64 + half*32 + i%32 of the tile.
+        // Local slot i holds column (i/32)*32*NSPLIT + half*32 + i%32 of the tile.
         __syncwarp();
         for (int i = lane; i < HALF_COLS; i += 32) {
-          const int n = n0 + (i >> 5) * 64 + half * 32 + (i & 31);
+          const int n = n0 + (i >> 5) * (32 * NSPLIT) + half * 32 + (i & 31);
           const bool v = n < g.N;
           if (MODE == EPI_BN32) {
             const int k = v ? __ldg(reinterpret_cast<const int *>(e.k) + n) : 0;
@@ -508,7 +513,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN_TILE);
 #pragma unroll
           for (int ch = 0; ch < NCHUNK; ch++) {
-            const int lc = ch * 32, c0 = ch * 64 + half * 32;
+            const int lc = ch * 32, c0 = ch * (32 * NSPLIT) + half * 32;
             uint32_t v[32];
             tmem_ld_32(t_row + (uint32_t)c0, v);
             tmem_wait_ld();
@@ -554,7 +559,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           const int x = BN_TILE == 128 ? (r & 7) : ((r >> 1) & 3);
 #pragma unroll
           for (int ch = 0; ch < NCHUNK; ch++) {
-            const int cc = (ch * 64 + half * 32) >> 4;
+            const int cc = (ch * (32 * NSPLIT) + half * 32) >> 4;
             sts128(rowaddr + (uint32_t)(((cc) ^ x) << 4), w[ch][0], w[ch][1], w[ch][2], w[ch][3]);
             sts128(rowaddr + (uint32_t)(((cc + 1) ^ x) << 4), w[ch][4], w[ch][5], w[ch][6], w[ch][7]);
           }
@@ -575,7 +580,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN_TILE);
 #pragma unroll 1
       for (int lc = 0; lc < HALF_COLS; lc += 32) {   // lc: offset inside this warp's parameter copy
-        const int c0 = (lc >> 5) * 64 + half * 32;   // column offset inside the tile
+        const int c0 = (lc >> 5) * (32 * NSPLIT) + half * 32;   // column offset inside the tile
         if (n0 + c0 >= g.N) break;                   // uniform across the warp
         uint32_t v[32];
         tmem_ld_32(t_row + (uint32_t)c0, v);
