@@ -114,7 +114,17 @@ int  pulpnn_get_option(int option);
  *                                                           split the rows, so they share one kernel
  *  pulp_nn_pointwise_HoWo_parallel  pulp_nn_kernels.h:140   1x1 convolution; kernel/pad/stride
  *                                                           arguments are ignored as in the reference
+ *  pulp_nn_conv_Co_parallel         pulp_nn_kernels.h:84    the remaining core-slicing variants: the
+ *  pulp_nn_pointwise_Ho_parallel    pulp_nn_kernels.h:168   same function of the same arguments as
+ *  pulp_nn_pointwise_Co_parallel    pulp_nn_kernels.h:196   the two above (a grid has no cores to
+ *                                                           slice over), so they share their kernels.
+ *                                                           Defined as the convolution itself: the
+ *                                                           reference's Co-parallel files mis-step
+ *                                                           their bias and weight pointers between
+ *                                                           channel chunks, which is not imitated
  *  pulp_nn_depthwise_generic        pulp_nn_kernels.h:282   CHW in, HWC out
+ *  pulp_nn_depthwise_generic_less_4_weights  :311           same, for kernels of fewer than 4 taps
+ *                                                           (accepts any number of taps)
  *  pulp_nn_linear                   pulp_nn_kernels.h:224   uint8 output, requantised
  *  pulp_nn_linear_out_32            pulp_nn_kernels.h:239   raw int32 output; bias is read as int32[]
  *  pulp_nn_maxpool                  pulp_nn_kernels.h:264   Im_in is left intact unless
@@ -129,7 +139,11 @@ int  pulpnn_get_option(int option);
   void pulp_nn_conv_Ho_parallel##SFX(PULPNN_CONV_PARAMS(BN_T));                               \
   void pulp_nn_conv_HoWo_parallel##SFX(PULPNN_CONV_PARAMS(BN_T));                             \
   void pulp_nn_pointwise_HoWo_parallel##SFX(PULPNN_CONV_PARAMS(BN_T));                        \
+  void pulp_nn_conv_Co_parallel##SFX(PULPNN_CONV_PARAMS(BN_T));                               \
+  void pulp_nn_pointwise_Ho_parallel##SFX(PULPNN_CONV_PARAMS(BN_T));                          \
+  void pulp_nn_pointwise_Co_parallel##SFX(PULPNN_CONV_PARAMS(BN_T));                          \
   void pulp_nn_depthwise_generic##SFX(PULPNN_DW_PARAMS(BN_T));                                \
+  void pulp_nn_depthwise_generic_less_4_weights##SFX(PULPNN_DW_PARAMS(BN_T));                 \
   void pulpnn_depthwise_hwc##SFX(PULPNN_DW_PARAMS(BN_T));                                     \
   void pulp_nn_linear##SFX(uint8_t *pInBuffer, int8_t *bias, uint8_t *pOutBuffer,             \
                            int8_t *pWeights, BN_T *k, BN_T *lambda, uint16_t out_mult,        \
@@ -146,6 +160,15 @@ int  pulpnn_get_option(int option);
 
 PULPNN_DECLARE_TREE(_bn32, int32_t)
 PULPNN_DECLARE_TREE(_bn64, int64_t)
+
+/*
+ * Layout change of uint8 activations, CHW <-> HWC, for the images of the current batch. No
+ * counterpart in the reference, which needs one all the same: pulp_nn_depthwise_generic reads CHW
+ * (32bit/src/pulp_nn_depthwise_generic.c:74) while every kernel of the library, the depthwise one
+ * included, writes HWC (ibid. :81,179). In and out must not overlap.
+ */
+void pulpnn_chw_to_hwc(const uint8_t *Im_in, uint8_t *Im_out, uint16_t dim_im_x, uint16_t dim_im_y, uint16_t ch_im);
+void pulpnn_hwc_to_chw(const uint8_t *Im_in, uint8_t *Im_out, uint16_t dim_im_x, uint16_t dim_im_y, uint16_t ch_im);
 
 /*
  * pulpnn_linear_out_32_static_scratch -- no counterpart in the reference.

@@ -126,6 +126,9 @@ def _conv_like(name):
 pulp_nn_conv_Ho_parallel = _conv_like("pulp_nn_conv_Ho_parallel")
 pulp_nn_conv_HoWo_parallel = _conv_like("pulp_nn_conv_HoWo_parallel")
 pulp_nn_pointwise_HoWo_parallel = _conv_like("pulp_nn_pointwise_HoWo_parallel")
+pulp_nn_conv_Co_parallel = _conv_like("pulp_nn_conv_Co_parallel")
+pulp_nn_pointwise_Ho_parallel = _conv_like("pulp_nn_pointwise_Ho_parallel")
+pulp_nn_pointwise_Co_parallel = _conv_like("pulp_nn_pointwise_Co_parallel")
 
 
 def _dw_like(name):
@@ -148,6 +151,7 @@ def _dw_like(name):
 
 
 pulp_nn_depthwise_generic = _dw_like("pulp_nn_depthwise_generic")
+pulp_nn_depthwise_generic_less_4_weights = _dw_like("pulp_nn_depthwise_generic_less_4_weights")
 pulpnn_depthwise_hwc = _dw_like("pulpnn_depthwise_hwc")
 
 
@@ -203,6 +207,20 @@ def pulp_nn_add(bits, Im_in_1, Im_in_2, Im_out, out_mult1, out_mult2, out_shift,
                              C.c_uint16(out_mult2), C.c_uint16(out_shift),
                              C.c_uint16(dim_im_in_h), C.c_uint16(dim_im_in_w),
                              C.c_uint16(ch_im_in))
+    _check()
+
+
+def pulpnn_chw_to_hwc(Im_in, Im_out, dim_im_x, dim_im_y, ch_im):
+    """[batch][C][H][W] -> [batch][H][W][C] (no counterpart in the reference)."""
+    _lib.load_library().pulpnn_chw_to_hwc(_ptr(Im_in), _ptr(Im_out), C.c_uint16(dim_im_x),
+                                          C.c_uint16(dim_im_y), C.c_uint16(ch_im))
+    _check()
+
+
+def pulpnn_hwc_to_chw(Im_in, Im_out, dim_im_x, dim_im_y, ch_im):
+    """[batch][H][W][C] -> [batch][C][H][W] (no counterpart in the reference)."""
+    _lib.load_library().pulpnn_hwc_to_chw(_ptr(Im_in), _ptr(Im_out), C.c_uint16(dim_im_x),
+                                          C.c_uint16(dim_im_y), C.c_uint16(ch_im))
     _check()
 
 

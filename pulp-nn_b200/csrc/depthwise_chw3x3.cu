@@ -41,12 +41,8 @@ template <int MODE>
 __device__ __forceinline__ int requant_one(int acc, long long k, long long l, int bias, const Epilogue &e)
 {
   if (MODE == EPI_BN32) return (int)((unsigned)(int)k * (unsigned)acc + (unsigned)(int)l) >> e.shift;
-  if (MODE == EPI_BN64) {
-    // l already holds k*bias + lambda; when k fits in 32 bits the product is a single wide multiply
-    const long long t = (k == (long long)(int)k) ? (long long)(int)k * acc + l
-                                                 : (long long)((unsigned long long)k * (unsigned long long)(long long)acc + (unsigned long long)l);
-    return (int)(t >> e.shift);
-  }
+  if (MODE == EPI_BN64)   // l already holds k*bias + lambda
+    return (int)((long long)((unsigned long long)k * (unsigned long long)(long long)acc + (unsigned long long)l) >> e.shift);
   if (MODE == EPI_MULT) return (int)(short)((int)((unsigned)e.out_mult * (unsigned)(acc + bias)) >> e.shift);
   return (acc + bias) >> e.shift;
 }
@@ -75,6 +71,7 @@ __global__ void __launch_bounds__(256) depthwise_chw3x3_kernel(const Chw3Params 
     const int c0 = c_base + 4 * q;
     int wa[4][3], wb[4][3], bias[4];
     long long kk[4], ll[4];
+    bool k32 = true;                     // 64-bit mode: all four k of this thread fit in 32 bits
 #pragma unroll
     for (int j = 0; j < 4; j++) {
       const bool c_on = q_on && c0 + j < p.C;
@@ -98,6 +95,7 @@ __global__ void __launch_bounds__(256) depthwise_chw3x3_kernel(const Chw3Params 
         kk[j] = k;
         ll[j] = (long long)((unsigned long long)k * (unsigned long long)(long long)bias[j] +
                             (unsigned long long)__ldg(reinterpret_cast<const long long *>(e.lambda) + c));
+        k32 = k32 && (k == (long long)(int)k);
       }
     }
     const unsigned *chan0 = reinterpret_cast<const unsigned *>(p.in + ((size_t)b * p.C + (q_on ? c0 : 0)) * p.H * p.W);
@@ -173,8 +171,15 @@ __global__ void __launch_bounds__(256) depthwise_chw3x3_kernel(const Chw3Params 
         for (int fy = 0; fy < 3 - S; fy++) { x0[j][fy] = x0[j][fy + S]; x1[j][fy] = x1[j][fy + S]; xr[j][fy] = xr[j][fy + S]; }
 #pragma unroll
         for (int t = 0; t < S; t++) { x0[j][3 - S + t] = n0[j][t]; x1[j][3 - S + t] = n1[j][t]; xr[j][3 - S + t] = nr[j][t]; }
-        res[j] = pack4_sat_u8(requant_one<MODE>(a0, kk[j], ll[j], bias[j], e), requant_one<MODE>(a1, kk[j], ll[j], bias[j], e),
-                              requant_one<MODE>(a2, kk[j], ll[j], bias[j], e), requant_one<MODE>(a3, kk[j], ll[j], bias[j], e));
+        if (MODE == EPI_BN64 && k32) {
+          // every k of this thread fits in 32 bits: one wide multiply-add per output
+          const long long kj = (long long)(int)kk[j];
+          res[j] = pack4_sat_u8((int)((kj * a0 + ll[j]) >> e.shift), (int)((kj * a1 + ll[j]) >> e.shift),
+                                (int)((kj * a2 + ll[j]) >> e.shift), (int)((kj * a3 + ll[j]) >> e.shift));
+        } else {
+          res[j] = pack4_sat_u8(requant_one<MODE>(a0, kk[j], ll[j], bias[j], e), requant_one<MODE>(a1, kk[j], ll[j], bias[j], e),
+                                requant_one<MODE>(a2, kk[j], ll[j], bias[j], e), requant_one<MODE>(a3, kk[j], ll[j], bias[j], e));
+        }
       }
       // res[j] = channel j, pixels 0..3  ->  pix[i] = pixel i, channels 0..3
       const unsigned ta = prmt(res[0], res[1], 0x5140), tb = prmt(res[0], res[1], 0x7362);

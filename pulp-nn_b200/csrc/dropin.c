@@ -27,7 +27,11 @@
 void pulp_nn_conv_Ho_parallel(PULPNN_CONV_PARAMS(BN_T)) { SFX(pulp_nn_conv_Ho_parallel)(CONV_ARGS); }
 void pulp_nn_conv_HoWo_parallel(PULPNN_CONV_PARAMS(BN_T)) { SFX(pulp_nn_conv_HoWo_parallel)(CONV_ARGS); }
 void pulp_nn_pointwise_HoWo_parallel(PULPNN_CONV_PARAMS(BN_T)) { SFX(pulp_nn_pointwise_HoWo_parallel)(CONV_ARGS); }
+void pulp_nn_conv_Co_parallel(PULPNN_CONV_PARAMS(BN_T)) { SFX(pulp_nn_conv_Co_parallel)(CONV_ARGS); }
+void pulp_nn_pointwise_Ho_parallel(PULPNN_CONV_PARAMS(BN_T)) { SFX(pulp_nn_pointwise_Ho_parallel)(CONV_ARGS); }
+void pulp_nn_pointwise_Co_parallel(PULPNN_CONV_PARAMS(BN_T)) { SFX(pulp_nn_pointwise_Co_parallel)(CONV_ARGS); }
 void pulp_nn_depthwise_generic(PULPNN_DW_PARAMS(BN_T)) { SFX(pulp_nn_depthwise_generic)(DW_ARGS); }
+void pulp_nn_depthwise_generic_less_4_weights(PULPNN_DW_PARAMS(BN_T)) { SFX(pulp_nn_depthwise_generic_less_4_weights)(DW_ARGS); }
 void pulpnn_depthwise_hwc(PULPNN_DW_PARAMS(BN_T)) { SFX(pulpnn_depthwise_hwc)(DW_ARGS); }
 void pulp_nn_linear(uint8_t *pInBuffer, int8_t *bias, uint8_t *pOutBuffer, int8_t *pWeights, BN_T *k,
                     BN_T *lambda, uint16_t out_mult, int8_t out_shift, uint16_t dim_vec,

@@ -111,15 +111,16 @@ void conv_entry(const char *who, bool pointwise, const uint8_t *in, const int8_t
 // The reference equals a zero-padded depthwise convolution only inside this domain; outside it
 // its strip builder reads neighbouring bytes, so such calls are rejected rather than imitated.
 bool depthwise_domain(const char *who, int W, int H, int Wo, int Ho, int kx, int ky, int pt, int pb,
-                      int pl, int pr, int sx, int sy)
+                      int pl, int pr, int sx, int sy, bool need_four_taps)
 {
   if (!(kx & 1) || pl != kx / 2) {
     // right-hand zero padding is derived from kx/2 (32bit/src/pulp_nn_depthwise_generic.c:316)
     set_error(PULPNN_ERR_UNSUPPORTED, "%s: needs odd dim_kernel_x and padding_x_left == dim_kernel_x/2", who);
     return false;
   }
-  if (kx * ky < 4) {
-    // the tap loop is a do-while over groups of four (ibid. :157-166)
+  if (need_four_taps && kx * ky < 4) {
+    // the tap loop is a do-while over groups of four (ibid. :157-166); the _less_4_weights variant
+    // tests before the first group (pulp_nn_depthwise_generic_less_4_weights.c:156) and takes any count
     set_error(PULPNN_ERR_UNSUPPORTED, "%s: needs at least 4 taps", who);
     return false;
   }
@@ -145,7 +146,7 @@ bool depthwise_domain(const char *who, int W, int H, int Wo, int Ho, int kx, int
 }
 
 template <typename BN_T>
-void depthwise_entry(const char *who, bool in_is_hwc, const uint8_t *in, const int8_t *bias, uint8_t *out,
+void depthwise_entry(const char *who, bool in_is_hwc, bool need_four_taps, const uint8_t *in, const int8_t *bias, uint8_t *out,
                      const int8_t *w, BN_T *k, BN_T *lambda, int out_mult, int out_shift, int W, int H,
                      int ch_in, int Wo, int Ho, int ch_out, int kx, int ky, int pt, int pb, int pl,
                      int pr, int sx, int sy, int8_t flag_relu, int8_t flag_bn)
@@ -159,7 +160,7 @@ void depthwise_entry(const char *who, bool in_is_hwc, const uint8_t *in, const i
   const int mode = dw_mode<BN_T>(flag_relu, flag_bn);
   if (!check_shift(mode, out_shift, who)) return;
   REQUIRE(mode < EPI_BN32 || (k && lambda), PULPNN_ERR_INVALID_ARG, "%s: batch-norm mode needs k and lambda", who);
-  if (!depthwise_domain(who, W, H, Wo, Ho, kx, ky, pt, pb, pl, pr, sx, sy)) return;
+  if (!depthwise_domain(who, W, H, Wo, Ho, kx, ky, pt, pb, pl, pr, sx, sy, need_four_taps)) return;
 
   Stager st(c);
   DepthwiseProblem p;
@@ -360,10 +361,44 @@ using namespace pulpnn;
                      ch_out, dim_kernel_x, dim_kernel_y, padding_y_top, padding_y_bottom,               \
                      padding_x_left, padding_x_right, stride_x, stride_y, flag_relu, flag_batch_norm);  \
   }                                                                                                     \
+  /* the other core-slicing variants of the reference compute the same function */                      \
+  extern "C" void pulp_nn_conv_Co_parallel##SFX(PULPNN_CONV_PARAMS(BN_T))                               \
+  {                                                                                                     \
+    (void)pIm2ColBuffer;                                                                                \
+    conv_entry<BN_T>("pulp_nn_conv_Co_parallel", false, pInBuffer, bias, pOutBuffer, pWeight, k, lambda, \
+                     out_mult, out_shift, dim_in_x, dim_in_y, ch_in, dim_out_x, dim_out_y, ch_out,      \
+                     dim_kernel_x, dim_kernel_y, padding_y_top, padding_y_bottom, padding_x_left,       \
+                     padding_x_right, stride_x, stride_y, flag_relu, flag_batch_norm);                  \
+  }                                                                                                     \
+  extern "C" void pulp_nn_pointwise_Ho_parallel##SFX(PULPNN_CONV_PARAMS(BN_T))                          \
+  {                                                                                                     \
+    (void)pIm2ColBuffer;                                                                                \
+    conv_entry<BN_T>("pulp_nn_pointwise_Ho_parallel", true, pInBuffer, bias, pOutBuffer, pWeight, k,    \
+                     lambda, out_mult, out_shift, dim_in_x, dim_in_y, ch_in, dim_out_x, dim_out_y,      \
+                     ch_out, dim_kernel_x, dim_kernel_y, padding_y_top, padding_y_bottom,               \
+                     padding_x_left, padding_x_right, stride_x, stride_y, flag_relu, flag_batch_norm);  \
+  }                                                                                                     \
+  extern "C" void pulp_nn_pointwise_Co_parallel##SFX(PULPNN_CONV_PARAMS(BN_T))                          \
+  {                                                                                                     \
+    (void)pIm2ColBuffer;                                                                                \
+    conv_entry<BN_T>("pulp_nn_pointwise_Co_parallel", true, pInBuffer, bias, pOutBuffer, pWeight, k,    \
+                     lambda, out_mult, out_shift, dim_in_x, dim_in_y, ch_in, dim_out_x, dim_out_y,      \
+                     ch_out, dim_kernel_x, dim_kernel_y, padding_y_top, padding_y_bottom,               \
+                     padding_x_left, padding_x_right, stride_x, stride_y, flag_relu, flag_batch_norm);  \
+  }                                                                                                     \
+  extern "C" void pulp_nn_depthwise_generic_less_4_weights##SFX(PULPNN_DW_PARAMS(BN_T))                 \
+  {                                                                                                     \
+    (void)bufferC; (void)bufferB;                                                                       \
+    depthwise_entry<BN_T>("pulp_nn_depthwise_generic_less_4_weights", false, false, Im_in, bias, Im_out, \
+                          wt, k, lambda, out_mult, out_shift, dim_im_in_x, dim_im_in_y, ch_im_in,       \
+                          dim_im_out_x, dim_im_out_y, ch_im_out, dim_kernel_x, dim_kernel_y,            \
+                          padding_y_top, padding_y_bottom, padding_x_left, padding_x_right, stride_x,   \
+                          stride_y, FLAG_RELU, FLAG_BATCH_NORM);                                        \
+  }                                                                                                     \
   extern "C" void pulp_nn_depthwise_generic##SFX(PULPNN_DW_PARAMS(BN_T))                                \
   {                                                                                                     \
     (void)bufferC; (void)bufferB;                                                                       \
-    depthwise_entry<BN_T>("pulp_nn_depthwise_generic", false, Im_in, bias, Im_out, wt, k, lambda,       \
+    depthwise_entry<BN_T>("pulp_nn_depthwise_generic", false, true, Im_in, bias, Im_out, wt, k, lambda, \
                           out_mult, out_shift, dim_im_in_x, dim_im_in_y, ch_im_in, dim_im_out_x,        \
                           dim_im_out_y, ch_im_out, dim_kernel_x, dim_kernel_y, padding_y_top,           \
                           padding_y_bottom, padding_x_left, padding_x_right, stride_x, stride_y,        \
@@ -372,7 +407,7 @@ using namespace pulpnn;
   extern "C" void pulpnn_depthwise_hwc##SFX(PULPNN_DW_PARAMS(BN_T))                                     \
   {                                                                                                     \
     (void)bufferC; (void)bufferB;                                                                       \
-    depthwise_entry<BN_T>("pulpnn_depthwise_hwc", true, Im_in, bias, Im_out, wt, k, lambda, out_mult,   \
+    depthwise_entry<BN_T>("pulpnn_depthwise_hwc", true, true, Im_in, bias, Im_out, wt, k, lambda, out_mult, \
                           out_shift, dim_im_in_x, dim_im_in_y, ch_im_in, dim_im_out_x, dim_im_out_y,    \
                           ch_im_out, dim_kernel_x, dim_kernel_y, padding_y_top, padding_y_bottom,       \
                           padding_x_left, padding_x_right, stride_x, stride_y, FLAG_RELU,               \

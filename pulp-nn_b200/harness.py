@@ -62,26 +62,28 @@ class GpuKernels:
         sy, sx = strides
         k, lam = self._bn(bits, k, lam)
         out = self._out((B, Ho, Wo, Cout), np.uint8)
-        fn = {"Ho": api.pulp_nn_conv_Ho_parallel, "HoWo": api.pulp_nn_conv_HoWo_parallel}[variant]
+        fn = {"Ho": api.pulp_nn_conv_Ho_parallel, "HoWo": api.pulp_nn_conv_HoWo_parallel,
+              "Co": api.pulp_nn_conv_Co_parallel}[variant]
         api.set_batch(B)
         fn(bits, self._in(x), None, self._in(bias), out, self._in(w), self._in(k), self._in(lam),
            out_mult, out_shift, W, H, Cin, Wo, Ho, Cout, kx, ky, pt, pb, pl, pr, sx, sy, relu, bn)
         return self._np(out)
 
-    def pointwise(self, bits, x, w, k, lam, *, bias=None, out_mult=1, out_shift=0, relu=1, bn=1):
+    def pointwise(self, bits, x, w, k, lam, *, bias=None, out_mult=1, out_shift=0, relu=1, bn=1,
+                  variant="HoWo"):
         B, H, W, Cin = x.shape
         Cout = w.shape[0]
         k, lam = self._bn(bits, k, lam)
         out = self._out((B, H, W, Cout), np.uint8)
         api.set_batch(B)
-        api.pulp_nn_pointwise_HoWo_parallel(bits, self._in(x), None, self._in(bias), out,
-                                            self._in(w), self._in(k), self._in(lam), out_mult,
-                                            out_shift, W, H, Cin, W, H, Cout, 1, 1, 0, 0, 0, 0, 1,
-                                            1, relu, bn)
+        fn = {"HoWo": api.pulp_nn_pointwise_HoWo_parallel, "Ho": api.pulp_nn_pointwise_Ho_parallel,
+              "Co": api.pulp_nn_pointwise_Co_parallel}[variant]
+        fn(bits, self._in(x), None, self._in(bias), out, self._in(w), self._in(k), self._in(lam), out_mult,
+           out_shift, W, H, Cin, W, H, Cout, 1, 1, 0, 0, 0, 0, 1, 1, relu, bn)
         return self._np(out)
 
     def depthwise(self, bits, x, w, k, lam, *, bias=None, out_mult=1, out_shift=0, out_hw, kernel,
-                  pads, strides, relu=1, bn=1, in_is_hwc=False):
+                  pads, strides, relu=1, bn=1, in_is_hwc=False, less_4_weights=False):
         if in_is_hwc:
             B, H, W, Cc = x.shape
         else:
@@ -93,6 +95,8 @@ class GpuKernels:
         k, lam = self._bn(bits, k, lam)
         out = self._out((B, Ho, Wo, Cc), np.uint8)
         fn = api.pulpnn_depthwise_hwc if in_is_hwc else api.pulp_nn_depthwise_generic
+        if less_4_weights:
+            fn = api.pulp_nn_depthwise_generic_less_4_weights
         api.set_batch(B)
         fn(bits, self._in(x), None, self._in(bias), out, self._in(w), None, self._in(k),
            self._in(lam), out_mult, out_shift, W, H, Cc, Wo, Ho, Cc, kx, ky, pt, pb, pl, pr, sx, sy,
@@ -144,6 +148,20 @@ class GpuKernels:
         api.set_batch(B)
         api.pulp_nn_avgpool(bits, self._in(x), out, lam, out_shift, out_add, W, H, Cc, Wo, Ho, kx,
                             ky, pt, pb, pl, pr, sx, sy, requant)
+        return self._np(out)
+
+    def chw_to_hwc(self, x):
+        B, Cc, H, W = x.shape
+        out = self._out((B, H, W, Cc), np.uint8)
+        api.set_batch(B)
+        api.pulpnn_chw_to_hwc(self._in(x), out, W, H, Cc)
+        return self._np(out)
+
+    def hwc_to_chw(self, x):
+        B, H, W, Cc = x.shape
+        out = self._out((B, Cc, H, W), np.uint8)
+        api.set_batch(B)
+        api.pulpnn_hwc_to_chw(self._in(x), out, W, H, Cc)
         return self._np(out)
 
     def add(self, a, b, *, m1, m2, out_shift, bits=32):

@@ -92,11 +92,42 @@ def build_case(name, B, pkg):
             fn = lambda: api.pulp_nn_linear_out_32(32, x, None, o, w, 4096, 4096)  # noqa: E731
             nbytes = B * 4096 * 5 + 4096 * 4096
         return fn, 2.0 * B * 4096 * 4096, nbytes, (x, w, bias, o)
+    if name in ("chw_to_hwc", "hwc_to_chw"):
+        # the layout change a reference-style chain needs before every depthwise call: dw2's tensor
+        H, C = 112, 64
+        x = torch.randint(0, 256, (B, C, H, H) if name == "chw_to_hwc" else (B, H, H, C), dtype=torch.uint8, device="cuda")
+        o = torch.empty((B, H, H, C) if name == "chw_to_hwc" else (B, C, H, H), dtype=torch.uint8, device="cuda")
+        call = api.pulpnn_chw_to_hwc if name == "chw_to_hwc" else api.pulpnn_hwc_to_chw
+        return (lambda: call(x, o, H, H, C)), 0.0, 2 * B * C * H * H, (x, o)
     raise SystemExit("unknown case %r" % name)
+
+
+def int8_peak(reps):
+    """Practical int8 tensor peak of this GPU: the library GEMM (torch._int_mm, cuBLASLt) on a large
+    square, the denominator for the tensor-bound fraction of the GEMM layers."""
+    import torch
+    n = 8192
+    a = torch.randint(-8, 8, (n, n), dtype=torch.int8, device="cuda")
+    b = torch.randint(-8, 8, (n, n), dtype=torch.int8, device="cuda").t().contiguous().t()   # column-major B
+    for _ in range(3):
+        torch._int_mm(a, b)
+    torch.cuda.synchronize()
+    best = 1e30
+    for _ in range(max(3, reps)):
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        torch._int_mm(a, b)
+        ev1.record()
+        torch.cuda.synchronize()
+        best = min(best, ev0.elapsed_time(ev1))
+    return {"case": "int8_peak", "how": "torch._int_mm %d^3, best of %d" % (n, max(3, reps)),
+            "ms_per_call": round(best, 4), "TOPs": round(2.0 * n ** 3 / best / 1e9, 1)}
 
 
 def run_case(name, B, reps, pkg):
     import torch
+    if name == "int8_peak":
+        return int8_peak(reps)
     api = pkg.api
     api.set_batch(B)
     fn, ops, nbytes, keep = build_case(name, B, pkg)

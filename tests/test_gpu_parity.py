@@ -286,6 +286,41 @@ def test_depthwise_against_compiled_reference(gpu, reference64):
     same(gpu.depthwise(64, c["x"], c["w"], c["k"], c["lam"], **dw_kw(c)), want)
 
 
+# ---- the remaining entry points of the reference header ------------------------------------------
+@pytest.mark.parametrize("bits", [32, 64])
+def test_slicing_variants_and_short_kernels(bits, gpu, restatement, reference32, reference64):
+    """pulp_nn_conv_Co_parallel, pulp_nn_pointwise_Ho_parallel / _Co_parallel and
+    pulp_nn_depthwise_generic_less_4_weights through the C ABI: the checker is the compiled
+    reference wherever it computes the convolution (it does not for pointwise_Co), and the
+    restatement everywhere."""
+    ref = reference32 if bits == 32 else reference64
+    c = wl.conv_case(60, 11, 9, 8, 20, strides=(2, 1), batch=3, bits=bits, with_bias=True, out_shift=10)
+    want = restatement.conv(bits, c["x"], c["w"], c["k"], c["lam"], **conv_kw(c))
+    same(ref.conv(bits, c["x"], c["w"], c["k"], c["lam"], variant="Co", **conv_kw(c)), want)
+    same(gpu.conv(bits, c["x"], c["w"], c["k"], c["lam"], variant="Co", **conv_kw(c)), want)
+    c = wl.pointwise_case(61, 6, 10, 32, 48, batch=3, bits=bits, with_bias=True)
+    want = restatement.pointwise(bits, c["x"], c["w"], c["k"], c["lam"], **pw_kw(c))
+    same(ref.pointwise(bits, c["x"], c["w"], c["k"], c["lam"], variant="Ho", **pw_kw(c)), want)
+    for variant in ("Ho", "Co"):
+        same(gpu.pointwise(bits, c["x"], c["w"], c["k"], c["lam"], variant=variant, **pw_kw(c)), want)
+    for kernel, pads in (((1, 3), (0, 0, 1, 1)), ((3, 1), (1, 1, 0, 0)), ((1, 1), (0, 0, 0, 0)), ((3, 3), (1, 1, 1, 1))):
+        c = wl.depthwise_case(62, 9, 12, 8, kernel=kernel, pads=pads, batch=2, bits=bits, out_shift=6, with_bias=True)
+        want = ref.depthwise(bits, c["x"], c["w"], c["k"], c["lam"], less4=True, **dw_kw(c))
+        same(gpu.depthwise(bits, c["x"], c["w"], c["k"], c["lam"], less_4_weights=True, **dw_kw(c)), want)
+
+
+def test_layout_change(gpu, gpu_host):
+    """CHW <-> HWC against numpy's transpose: whole tiles, ragged tiles, sizes that rule out 32-bit
+    accesses on either side, and the round trip."""
+    rng = np.random.default_rng(63)
+    for (B, Cc, H, W) in ((2, 64, 8, 16), (3, 5, 7, 9), (1, 130, 3, 67), (2, 32, 56, 56), (1, 3, 224, 224)):
+        x = rng.integers(0, 256, size=(B, Cc, H, W), dtype=np.uint8)
+        hwc = gpu.chw_to_hwc(x)
+        same(hwc, np.ascontiguousarray(x.transpose(0, 2, 3, 1)))
+        same(gpu.hwc_to_chw(hwc), x)
+    same(gpu_host.chw_to_hwc(x), np.ascontiguousarray(x.transpose(0, 2, 3, 1)))
+
+
 # ---- linear --------------------------------------------------------------------------------
 def lin_kw(c):
     return dict(bias=c["bias"], out_mult=c["out_mult"], out_shift=c["out_shift"], relu=c["relu"],

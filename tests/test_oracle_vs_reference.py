@@ -212,3 +212,34 @@ def test_add(m1, m2, shift, restatement, reference32, reference64):
     got = restatement.add(a, b, m1=m1, m2=m2, out_shift=shift)
     for ref in (reference32, reference64):
         assert np.array_equal(got, ref.add(a, b, m1=m1, m2=m2, out_shift=shift))
+
+
+# ---- the remaining core-slicing variants and the short-kernel depthwise -------------------------
+def test_slicing_variants_compute_the_same_function(restatement, reference32, reference64):
+    """pulp_nn_conv_Co_parallel and pulp_nn_pointwise_Ho_parallel (single core) give the bytes of the
+    plain convolution. pulp_nn_pointwise_Co_parallel does not, even on one core (it mis-steps its
+    bias pointer, 32bit/src/pulp_nn_pointwise_Co_parallel.c): the library defines that name as the
+    convolution itself, so the checker for it is the restatement."""
+    for bits, ref in ((32, reference32), (64, reference64)):
+        c = wl.conv_case(50, 9, 8, 8, 12, batch=2, bits=bits, with_bias=True, out_shift=10)
+        kw = dict(bias=c["bias"], out_mult=c["out_mult"], out_shift=c["out_shift"], out_hw=c["out_hw"],
+                  kernel=c["kernel"], pads=c["pads"], strides=c["strides"], relu=c["relu"], bn=c["bn"])
+        want = restatement.conv(bits, c["x"], c["w"], c["k"], c["lam"], **kw)
+        assert np.array_equal(ref.conv(bits, c["x"], c["w"], c["k"], c["lam"], variant="Co", **kw), want)
+        c = wl.pointwise_case(51, 7, 9, 16, 24, batch=2, bits=bits, with_bias=True)
+        kw = dict(bias=c["bias"], out_mult=c["out_mult"], out_shift=c["out_shift"], relu=c["relu"], bn=c["bn"])
+        want = restatement.pointwise(bits, c["x"], c["w"], c["k"], c["lam"], **kw)
+        assert np.array_equal(ref.pointwise(bits, c["x"], c["w"], c["k"], c["lam"], variant="Ho", **kw), want)
+
+
+@pytest.mark.parametrize("kernel,pads", [((1, 3), (0, 0, 1, 1)), ((3, 1), (1, 1, 0, 0)), ((1, 1), (0, 0, 0, 0)),
+                                         ((3, 3), (1, 1, 1, 1))])
+def test_depthwise_less_4_weights(kernel, pads, restatement, reference32, reference64):
+    for bits, ref in ((32, reference32), (64, reference64)):
+        c = wl.depthwise_case(52, 9, 11, 6, kernel=kernel, pads=pads, batch=2, bits=bits, out_shift=6,
+                              with_bias=True)
+        kw = dict(bias=c["bias"], out_mult=c["out_mult"], out_shift=c["out_shift"], out_hw=c["out_hw"],
+                  kernel=c["kernel"], pads=c["pads"], strides=c["strides"], relu=c["relu"], bn=c["bn"])
+        want = restatement.depthwise(bits, c["x"], c["w"], c["k"], c["lam"], **kw)
+        assert np.count_nonzero(want) > want.size // 10
+        assert np.array_equal(ref.depthwise(bits, c["x"], c["w"], c["k"], c["lam"], less4=True, **kw), want)
