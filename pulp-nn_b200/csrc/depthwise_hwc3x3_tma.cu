@@ -1,18 +1,20 @@
 // depthwise_hwc3x3_tma.cu -- 3x3 depthwise convolution on HWC input (padding 1, stride 1 or 2) for
-// channel counts that are a multiple of 128, with input and output staged through shared memory by
+// channel counts that are a multiple of 32, with input and output staged through shared memory by
 // TMA. Arithmetic is that of depthwise.cu (32bit/src/pulp_nn_depthwise_generic.c:133-180) and the
 // register scheme is that of depthwise_hwc3x3.cu: a thread owns four channels and four adjacent
 // output columns, transposes four pixel words into four channel words with byte permutes, and
 // pays one dp4a per output and filter row.
 //
-// What this file changes is everything around that arithmetic. A CTA owns a tile of 128 channels x
-// 4*NGX output columns and slides down the image. A ring of three groups of input rows is kept full
-// by 4-D TMA loads (tensor [B][H][W][C]); rows and columns outside the image arrive as zeros from
-// the TMA unit, which IS the zero padding, so the inner loop has no boundary test at all. Results
-// go to a double-buffered tile in shared memory and leave with one TMA store per group of rows,
-// which also clips columns and rows past the output's edge. One warp = the 32 channel words of one
-// pixel, so every shared-memory access is a conflict-free 128-byte row, and with the tile width a
-// template parameter every address in the row loop is "one register + constant".
+// What this file changes is everything around that arithmetic. A CTA owns a tile of CI = 128, 64 or
+// 32 channel bytes x 4*NGX output columns and slides down the image. A ring of three groups of
+// input rows is kept full by 4-D TMA loads (tensor [B][H][W][C]); rows and columns outside the
+// image arrive as zeros from the TMA unit, which IS the zero padding, so the inner loop has no
+// boundary test at all. Results go to a double-buffered tile in shared memory and leave with one
+// TMA store per group of rows, which also clips columns and rows past the output's edge. With
+// CI = 128 one warp = the 32 channel words of one pixel, so every shared-memory access is a
+// conflict-free 128-byte row; narrower chunks put several column groups in a warp (see Rot below).
+// With the tile width a template parameter every address in the row loop is "one register +
+// constant".
 //
 // Synchronisation per group of rows: one mbarrier wait (data landed), one __syncthreads (all
 // threads finished reading the group and writing the output tile), after which thread 0 issues the
@@ -367,6 +369,7 @@ depthwise_hwc3x3_tma_kernel(const __grid_constant__ CUtensorMap map_in, const __
     if (!dead) {
       consumed = j + 1;
       const uint32_t ia = in_thr + grp * G::GROUP_STRIDE, oa = out_thr + half * G::TILE_STRIDE;
+      const int rows_here = oyB - (oyA + (j - 1) * G::ROWS_OUT);     // output rows this group still owes
       uint32_t ra[4];
 #pragma unroll
       for (int i = 0; i < 4; i++) ra[i] = ia + CI + rot.off[i];
@@ -375,16 +378,20 @@ depthwise_hwc3x3_tma_kernel(const __grid_constant__ CUtensorMap map_in, const __
         unsigned cur[6]; Win1 w;
         load_row1<CI>(ia, ra, 0, cur);
         windows1(cur, rot, w);
-        load_row1<CI>(ia, ra, G::IN_PITCH, cur);
+        if (rows_here > 1) load_row1<CI>(ia, ra, G::IN_PITCH, cur);
         mac1<true, true>(w, wa, wb, init, acc[0], acc[A1], acc[A2]);
         finalize_row<MODE, CI>(acc[0], q, e, k32, oa);
-        windows1(cur, rot, w);
-        load_row1<CI>(ia, ra, 2 * G::IN_PITCH, cur);
-        mac1<true, true>(w, wa, wb, init, acc[A1], acc[A2], acc[0]);
-        finalize_row<MODE, CI>(acc[A1], q, e, k32, oa + G::OUT_PITCH);
-        windows1(cur, rot, w);
-        mac1<true, true>(w, wa, wb, init, acc[A2], acc[0], acc[A1]);
-        finalize_row<MODE, CI>(acc[A2], q, e, k32, oa + 2 * G::OUT_PITCH);
+        if (rows_here > 1) {            // the strip's last group may end before its third row
+          windows1(cur, rot, w);
+          if (rows_here > 2) load_row1<CI>(ia, ra, 2 * G::IN_PITCH, cur);
+          mac1<true, true>(w, wa, wb, init, acc[A1], acc[A2], acc[0]);
+          finalize_row<MODE, CI>(acc[A1], q, e, k32, oa + G::OUT_PITCH);
+          if (rows_here > 2) {
+            windows1(cur, rot, w);
+            mac1<true, true>(w, wa, wb, init, acc[A2], acc[0], acc[A1]);
+            finalize_row<MODE, CI>(acc[A2], q, e, k32, oa + 2 * G::OUT_PITCH);
+          }
+        }
       } else {
         unsigned cur[9]; Win2 w;
         load_row2<CI>(ia, ra, 0, cur);                          // input row 2m
@@ -392,17 +399,19 @@ depthwise_hwc3x3_tma_kernel(const __grid_constant__ CUtensorMap map_in, const __
         load_row2<CI>(ia, ra, G::IN_PITCH, cur);                // 2m+1: closes row m, opens m+1
         mac2<false>(w, wa[1], wb[1], init, acc[0]);
         windows2(cur, rot, w);
-        load_row2<CI>(ia, ra, 2 * G::IN_PITCH, cur);
+        if (rows_here > 1) load_row2<CI>(ia, ra, 2 * G::IN_PITCH, cur);
         mac2<false>(w, wa[2], wb[2], init, acc[0]);
         finalize_row<MODE, CI>(acc[0], q, e, k32, oa);
-        mac2<true>(w, wa[0], wb[0], init, acc[0]);
-        windows2(cur, rot, w);
-        load_row2<CI>(ia, ra, 3 * G::IN_PITCH, cur);
-        mac2<false>(w, wa[1], wb[1], init, acc[0]);
-        windows2(cur, rot, w);
-        mac2<false>(w, wa[2], wb[2], init, acc[0]);
-        finalize_row<MODE, CI>(acc[0], q, e, k32, oa + G::OUT_PITCH);
-        mac2<true>(w, wa[0], wb[0], init, acc[0]);
+        if (rows_here > 1) {
+          mac2<true>(w, wa[0], wb[0], init, acc[0]);
+          windows2(cur, rot, w);
+          load_row2<CI>(ia, ra, 3 * G::IN_PITCH, cur);
+          mac2<false>(w, wa[1], wb[1], init, acc[0]);
+          windows2(cur, rot, w);
+          mac2<false>(w, wa[2], wb[2], init, acc[0]);
+          finalize_row<MODE, CI>(acc[0], q, e, k32, oa + G::OUT_PITCH);
+          mac2<true>(w, wa[0], wb[0], init, acc[0]);
+        }
       }
       fence_proxy_async();            // the tile words written above, before the TMA store reads them
     }
