@@ -208,16 +208,18 @@ struct TcParams {
 // per group of warps in shared memory, which the ring has to make room for.
 __host__ __device__ constexpr int pipe_bytes(int bn, bool tma_out)
 {
-  return (tma_out && bn == 128) ? 176 * 1024 : PIPE_BYTES;
+  if (tma_out && bn == 128) return 176 * 1024;
+  return bn == 256 ? 208 * 1024 : PIPE_BYTES;      // 256-column tiles: four warps share a lane quarter, smaller copies
 }
 
 template <int BN_TILE, bool TMA_OUT>
 struct SmemLayout {
   static constexpr int PIPE = pipe_bytes(BN_TILE, TMA_OUT);
-  static constexpr int PARAM_BYTES = BN_TILE * 16;    // k and lambda, up to 8 bytes each, split over 8 warps
+  // every epilogue warp keeps its own copy of the k and lambda (up to 8 bytes each) of its columns
+  static constexpr int WARP_PARAM_BYTES = BN_TILE / (BN_TILE == 256 ? 4 : 2) * 16;
   static constexpr int PARAM_OFFSET = PIPE;
   static constexpr int OUT_TILE_BYTES = TMA_OUT ? BM * BN_TILE : 0;        // per epilogue group
-  static constexpr int OUT_OFFSET = PARAM_OFFSET + 4 * EPI_GROUPS * PARAM_BYTES;
+  static constexpr int OUT_OFFSET = PARAM_OFFSET + EPI_WARPS * EPI_GROUPS * WARP_PARAM_BYTES;
   static constexpr int BAR_OFFSET = OUT_OFFSET + EPI_GROUPS * OUT_TILE_BYTES;
   static constexpr int TOTAL = BAR_OFFSET + 1024 + 1024;  // barriers + slack for 1024-byte alignment
   static_assert(TOTAL <= 232448, "shared memory of one CTA");
@@ -454,7 +456,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     constexpr int HALF_COLS = BN_TILE / NSPLIT;     // columns this warp is responsible for
     // each epilogue warp keeps its own copy of the per-channel parameters of ITS columns, so
     // staging them needs no barrier between warps (a warp that gave up can never strand the others)
-    uint8_t *params = params_all + (warp - FIRST_EPI) * (L::PARAM_BYTES / 2);
+    uint8_t *params = params_all + (warp - FIRST_EPI) * L::WARP_PARAM_BYTES;
     static_assert(NUM_ACC % GROUPS == 0, "a group must always meet the same accumulators");
     const Epilogue &e = g.epi;
     int *p_bias = reinterpret_cast<int *>(params);                 // non-BN modes
