@@ -209,7 +209,7 @@ struct TcParams {
 __host__ __device__ constexpr int pipe_bytes(int bn, bool tma_out)
 {
   if (tma_out && bn == 128) return 176 * 1024;
-  return bn == 256 ? 208 * 1024 : PIPE_BYTES;      // 256-column tiles: four warps share a lane quarter, smaller copies
+  return (bn == 256 && !tma_out) ? 208 * 1024 : PIPE_BYTES;      // 256-column tiles: four warps share a lane quarter, smaller copies
 }
 
 template <int BN_TILE, bool TMA_OUT>
@@ -218,9 +218,12 @@ struct SmemLayout {
   // every epilogue warp keeps its own copy of the k and lambda (up to 8 bytes each) of its columns
   static constexpr int WARP_PARAM_BYTES = BN_TILE / (BN_TILE == 256 ? 4 : 2) * 16;
   static constexpr int PARAM_OFFSET = PIPE;
-  static constexpr int OUT_TILE_BYTES = TMA_OUT ? BM * BN_TILE : 0;        // per epilogue group
+  // staging tile of the TMA stores: 128 rows of at most 128 bytes, one per group of epilogue warps
+  // (a 256-column tile is drained by all sixteen warps and leaves in two halves through one tile)
+  static constexpr int OUT_ROW_BYTES = BN_TILE < 128 ? BN_TILE : 128;
+  static constexpr int OUT_TILE_BYTES = TMA_OUT ? BM * OUT_ROW_BYTES : 0;
   static constexpr int OUT_OFFSET = PARAM_OFFSET + EPI_WARPS * EPI_GROUPS * WARP_PARAM_BYTES;
-  static constexpr int BAR_OFFSET = OUT_OFFSET + EPI_GROUPS * OUT_TILE_BYTES;
+  static constexpr int BAR_OFFSET = OUT_OFFSET + (BN_TILE == 256 ? 1 : EPI_GROUPS) * OUT_TILE_BYTES;
   static constexpr int TOTAL = BAR_OFFSET + 1024 + 1024;  // barriers + slack for 1024-byte alignment
   static_assert(TOTAL <= 232448, "shared memory of one CTA");
   // accumulators in tensor memory: all 512 columns are used, so a narrow tile gets a deep ring
@@ -276,7 +279,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 const __grid_constant__ CUtensorMap map_out, const TcParams g)
 {
   using L = SmemLayout<BN_TILE, TMA_OUT>;
-  static_assert(!TMA_OUT || (!PARTIAL && MODE != EPI_RAW32 && BN_TILE <= 128), "TMA stores carry uint8 tiles of at most 128 columns");
+  static_assert(!TMA_OUT || (!PARTIAL && MODE != EPI_RAW32), "TMA stores carry uint8 tiles");
   constexpr int A_BYTES = BM * BKB, B_BYTES = BN_TILE * BKB;
   constexpr int NUM_ACC = L::NUM_ACC;
   constexpr uint32_t TMEM_COLS = 512;
@@ -467,7 +470,8 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     int staged_nt = -1;
     // TMA_OUT: the group's staging tile, and the one thread of the group that issues its stores
     uint8_t *out_tile = smem + L::OUT_OFFSET + grp * L::OUT_TILE_BYTES;
-    const bool elected = ((warp - FIRST_EPI) & 7) == 0 && lane == 0;
+    const bool elected = ((warp - FIRST_EPI) % (4 * NSPLIT)) == 0 && lane == 0;
+    constexpr int GROUP_THREADS = 32 * 4 * NSPLIT;       // threads that meet at the group's barrier
     bool dead = false;      // TMA_OUT: a wait ran out; keep meeting the group's barriers, do no work
     // i counts the CTA's tiles; tile i lives in accumulator i % NUM_ACC
     for (int i = grp;; i += GROUPS) {
@@ -550,28 +554,36 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           __syncwarp();
           if (lane == 0) mbar_arrive(&tmem_empty[acc]);
         }
-        // (A) the store of this group's previous tile has finished reading the staging tile
-        if (elected) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-        asm volatile("bar.sync %0, 256;" ::"r"(1 + grp) : "memory");
-        if (!dead) {
-          // row r of the tile, 16-byte chunks cc, cc+1 of each 32-column chunk, swizzled the way the
-          // TMA store expects (BN_TILE-byte rows with the BN_TILE-byte swizzle): no bank conflicts
-          const int r = quad * 32 + lane;
-          const uint32_t rowaddr = smem_u32(out_tile) + (uint32_t)(r * BN_TILE);
-          const int x = BN_TILE == 128 ? (r & 7) : ((r >> 1) & 3);
+        // The tile leaves in rounds of at most 128 columns (one round, or two for 256 columns).
+        constexpr int ROUNDS = BN_TILE == 256 ? 2 : 1;
+        constexpr int CPR = NCHUNK / ROUNDS;                 // 32-column chunks of this warp per round
 #pragma unroll
-          for (int ch = 0; ch < NCHUNK; ch++) {
-            const int cc = (ch * (32 * NSPLIT) + half * 32) >> 4;
-            sts128(rowaddr + (uint32_t)(((cc) ^ x) << 4), w[ch][0], w[ch][1], w[ch][2], w[ch][3]);
-            sts128(rowaddr + (uint32_t)(((cc + 1) ^ x) << 4), w[ch][4], w[ch][5], w[ch][6], w[ch][7]);
+        for (int rd = 0; rd < ROUNDS; rd++) {
+          // (A) the previous store from the staging tile has finished reading it
+          if (elected) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          asm volatile("bar.sync %0, %1;" ::"r"(1 + grp), "n"(GROUP_THREADS) : "memory");
+          if (!dead) {
+            // row r of the staging tile, 16-byte chunks cc, cc+1 of each 32-column chunk, swizzled
+            // the way the TMA store expects (rows of OUT_ROW_BYTES with the matching swizzle): no
+            // bank conflicts
+            const int r = quad * 32 + lane;
+            const uint32_t rowaddr = smem_u32(out_tile) + (uint32_t)(r * L::OUT_ROW_BYTES);
+            const int x = L::OUT_ROW_BYTES == 128 ? (r & 7) : ((r >> 1) & 3);
+#pragma unroll
+            for (int cr = 0; cr < CPR; cr++) {
+              const int ch = rd * CPR + cr;
+              const int cc = ((ch * (32 * NSPLIT) + half * 32) - rd * 128) >> 4;
+              sts128(rowaddr + (uint32_t)(((cc) ^ x) << 4), w[ch][0], w[ch][1], w[ch][2], w[ch][3]);
+              sts128(rowaddr + (uint32_t)(((cc + 1) ^ x) << 4), w[ch][4], w[ch][5], w[ch][6], w[ch][7]);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           }
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        }
-        // (B) the tile is complete
-        asm volatile("bar.sync %0, 256;" ::"r"(1 + grp) : "memory");
-        if (elected && !dead) {
-          tma_store_2d(&map_out, out_tile, n0, mt * BM);     // rows past M and columns past N are dropped
-          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          // (B) the round's columns are complete
+          asm volatile("bar.sync %0, %1;" ::"r"(1 + grp), "n"(GROUP_THREADS) : "memory");
+          if (elected && !dead) {
+            tma_store_2d(&map_out, out_tile, n0 + rd * 128, mt * BM);   // rows past M, columns past N are dropped
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
         }
         continue;
       }
@@ -768,6 +780,7 @@ bool launch_bn(Context &c, const TcMaps &m, const TcParams &g, int bn, int bkb, 
   if constexpr (!PARTIAL && MODE != EPI_RAW32) {
     if (tma_out && bn == 64)  return launch_bk<MODE, 64, false, true>(c, m, g, bkb, grid);
     if (tma_out && bn == 128) return launch_bk<MODE, 128, false, true>(c, m, g, bkb, grid);
+    if (tma_out && bn == 256) return launch_bk<MODE, 256, false, true>(c, m, g, bkb, grid);
   }
   if (bn == 64)  return launch_bk<MODE, 64, PARTIAL, false>(c, m, g, bkb, grid);
   if (bn == 128) return launch_bk<MODE, 128, PARTIAL, false>(c, m, g, bkb, grid);
@@ -852,10 +865,10 @@ bool launch_igemm_tc(Context &c, const ConvProblem &p)
   // tiles and slabs for the single-thread roles to get through).
   if (g.N <= 64) configure(64, false);
   else if (g.N <= 128 || (out_ok && g.K <= 256)) configure(128, out_ok);
-  else configure(256, false);
+  else configure(256, out_ok);
   // a 128-column slice of a wide W that does not fit is re-streamed for every m-tile: the 256-column
   // tile (plain stores) halves that traffic
-  if (g.N > 128 && bn == 128 && !g.w_resident) configure(256, false);
+  if (g.N > 128 && bn == 128 && !g.w_resident) configure(256, out_ok);
 
   if (!c.status_word) {
     if (!cuda_ok(cudaMalloc(&c.status_word, sizeof(int)), "cudaMalloc(status)")) return false;
@@ -867,7 +880,7 @@ bool launch_igemm_tc(Context &c, const ConvProblem &p)
   if (!make_map(&maps.a, p.in, g.M, g.K, BM, bkb)) return false;
   if (!make_map(&maps.b, p.w, g.N, g.K, bn, bkb)) return false;
   maps.out = maps.a;
-  if (tma_out && !make_map(&maps.out, p.out, g.M, g.N, BM, bn)) return false;    // box = bn bytes x 128 rows
+  if (tma_out && !make_map(&maps.out, p.out, g.M, g.N, BM, bn < 128 ? bn : 128)) return false;   // box = at most 128 bytes x 128 rows
 
   const int units = tiles * g.k_slices;
   int grid = units < sms ? units : sms;
