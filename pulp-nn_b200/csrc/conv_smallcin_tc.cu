@@ -55,10 +55,6 @@ struct SmallTcParams {
 // swizzle (address bits 4..5 are XORed with bits 7..8)
 __device__ __forceinline__ uint32_t swz64(int r, int c) { return (uint32_t)(r * 64 + ((c ^ ((r >> 1) & 3)) << 4)); }
 
-__device__ __forceinline__ void sts128(uint32_t addr, unsigned a, unsigned b, unsigned c, unsigned d)
-{
-  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
-}
 __device__ __forceinline__ unsigned lds32(uint32_t addr)
 {
   unsigned v;

@@ -37,10 +37,13 @@
 #include <mutex>
 
 #include "internal.cuh"
+#include "sm100_primitives.cuh"
 
 namespace pulpnn {
 
 namespace {
+
+using namespace sm100;
 
 constexpr int BM = 128;            // rows per tile = TMEM lanes
 constexpr int UMMA_K = 32;         // K per tcgen05.mma for 8-bit operands
@@ -56,140 +59,10 @@ constexpr int FIRST_EPI = NPROD + NMMA;
 constexpr int NUM_THREADS = 32 * (FIRST_EPI + EPI_WARPS * EPI_GROUPS);
 constexpr int MAX_STAGES = 44;     // short-K stages are small: what counts is the bytes in flight
 constexpr int PIPE_BYTES = 192 * 1024;   // operand ring (+ resident W) per CTA
-constexpr unsigned long long WAIT_LIMIT_NS = 1000000000ull;
 
 // status codes (or-ed into the global status word)
 constexpr int ST_PRODUCER = 0x1, ST_MMA_FULL = 0x2, ST_MMA_TMEM = 0x4, ST_EPILOGUE = 0x8, ST_DRAIN = 0x10,
               ST_MMA_WRES = 0x20;
-
-// ---- PTX wrappers --------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void *p)
-{
-  return (uint32_t)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count)
-{
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t bytes)
-{
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t *bar)
-{
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
-{
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ unsigned long long global_ns()
-{
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-// Bounded wait. Returns false when the limit ran out or another role already gave up.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
-                                          int *status, int code)
-{
-  // the clock is first read once a wait has lasted 256 polls: short waits never pay for it
-  unsigned long long t0 = 0;
-  for (unsigned spin = 1;; spin++) {
-    if (mbar_try_wait(bar, parity)) return true;
-    __nanosleep(32);      // a waiting warp must not take issue slots from the working ones
-    if ((spin & 255u) == 0) {
-      if (*abort_flag) return false;
-      if (t0 == 0) t0 = global_ns();
-      else if (global_ns() - t0 > WAIT_LIMIT_NS) {
-        *abort_flag = 1;
-        if (status) atomicOr(status, code);
-        return false;
-      }
-    }
-  }
-}
-__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, uint64_t *bar, int x, int y)
-{
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
-      : "memory");
-}
-__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tmem_alloc(uint32_t *slot, uint32_t ncols)
-{
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(ncols)
-               : "memory");
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols)
-{
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t *bar)
-{
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-               : "memory");
-}
-// D(tmem) (+)= A(smem) * B(smem)^T, u8 x s8 -> s32
-__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                        uint32_t accumulate)
-{
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld_32(uint32_t taddr, uint32_t (&r)[32])
-{
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor of a K-major tile whose rows are BKB bytes long and stored with
-// the BKB-byte swizzle (32, 64 or 128): groups of 8 rows are 8*BKB bytes apart (stride byte
-// offset), descriptor version 1, layout type 6 / 4 / 2 = SWIZZLE_32B / 64B / 128B. Addresses and
-// offsets are encoded in 16-byte units.
-template <int BKB>
-__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr)
-{
-  constexpr uint64_t layout = BKB == 128 ? 2 : (BKB == 64 ? 4 : 6);
-  uint64_t d = 0;
-  d |= (uint64_t)((saddr & 0x3ffffu) >> 4);          // start address
-  d |= (uint64_t)1 << 16;                            // leading byte offset (unused with swizzle)
-  d |= (uint64_t)((8 * BKB) >> 4) << 32;             // stride byte offset
-  d |= (uint64_t)1 << 46;                            // version
-  d |= layout << 61;
-  return d;
-}
-// Instruction descriptor: D = s32 (2 at bit 4), A = unsigned 8-bit (0 at bit 7), B = signed 8-bit
-// (1 at bit 10), both K-major (bits 15, 16 clear), N/8 at bit 17, M/16 at bit 24.
-__host__ __device__ constexpr uint32_t idesc_u8s8(int n)
-{
-  return (2u << 4) | (0u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-}
 
 // ---- kernel parameters ---------------------------------------------------------------------
 struct TcParams {
@@ -260,17 +133,6 @@ __device__ __forceinline__ bool unit_at(const TcParams &g, int i, int units, int
   return true;
 }
 
-__device__ __forceinline__ void sts128(uint32_t addr, unsigned a, unsigned b, unsigned c, unsigned d)
-{
-  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
-}
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, const void *src, int x, int y)
-{
-  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
-               ::"l"(map), "r"(smem_u32(src)), "r"(x), "r"(y)
-               : "memory");
-}
-
 // MODE: the final epilogue; PARTIAL: store raw int32 partial sums instead (split-K); TMA_OUT: the
 // uint8 output tile is staged in shared memory and leaves with one TMA store per tile
 template <int MODE, int BN_TILE, int BKB, bool PARTIAL, bool TMA_OUT>
@@ -317,9 +179,9 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == NPROD) tmem_alloc(tmem_slot, TMEM_COLS);
-  tcgen05_fence_before();
+  tc_fence_before();
   __syncthreads();
-  tcgen05_fence_after();
+  tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
   const int units = g.m_tiles * g.n_tiles * g.k_slices;
@@ -380,7 +242,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     // ------------------------------ MMA issuers ---------------------------------------------
     // tile i of the CTA (accumulator i % NUM_ACC) belongs to MMA warp i % NMMA
     if (lane == 0) {
-      constexpr uint32_t idesc = idesc_u8s8(BN_TILE);
+      constexpr uint32_t idesc = umma_idesc_u8s8(BN_TILE);
       // an accumulator must always be filled by the same MMA warp: no more warps than accumulators
       constexpr int NM = NMMA < NUM_ACC ? NMMA : NUM_ACC;
       static_assert(NUM_ACC % NM == 0, "an accumulator must always be filled by the same MMA warp");
@@ -421,15 +283,15 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         const int acc = i % NUM_ACC;
         const uint32_t acc_phase = (uint32_t)(i / NUM_ACC) & 1u;
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, g.status, ST_MMA_TMEM)) break;
-        tcgen05_fence_after();
+        tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN_TILE);
         for (int s = slab0; s < slab1; s++) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag, g.status, ST_MMA_FULL)) { ok = false; break; }
           if (NMMA > 1 && s == slab1 - 1) *tiles_landed = i + 1;    // the next tile's warp may go ahead
-          tcgen05_fence_after();
+          tc_fence_after();
           const uint32_t a_addr = smem_u32(ring + stage * stage_bytes);
           const uint32_t b_addr = g.w_resident ? smem_u32(smem + s * B_BYTES) : a_addr + A_BYTES;
-          const uint64_t da = smem_desc<BKB>(a_addr), db = smem_desc<BKB>(b_addr);
+          const uint64_t da = umma_smem_desc<BKB>(a_addr), db = umma_smem_desc<BKB>(b_addr);
           // bytes of this slab that lie inside K; the rest of the tile is zero-filled by TMA
           const int kbytes = min(BKB, g.K - s * BKB);
           const int n_mma = (kbytes + UMMA_K - 1) / UMMA_K;
@@ -515,7 +377,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         unsigned w[NCHUNK][8];
         if (!dead && !mbar_wait(&tmem_full[acc], acc_phase, abort_flag, g.status, ST_EPILOGUE)) dead = true;
         if (!dead) {
-          tcgen05_fence_after();
+          tc_fence_after();
           const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN_TILE);
 #pragma unroll
           for (int ch = 0; ch < NCHUNK; ch++) {
@@ -550,7 +412,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             }
           }
           // the accumulator is in registers: hand it back to the MMA warps before the stores
-          tcgen05_fence_before();
+          tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&tmem_empty[acc]);
         }
@@ -588,7 +450,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         continue;
       }
       if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag, g.status, ST_EPILOGUE)) break;
-      tcgen05_fence_after();
+      tc_fence_after();
       const int m = mt * BM + quad * 32 + lane;
       const bool row_ok = m < g.M;
       const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN_TILE);
@@ -668,7 +530,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           }
         }
       }
-      tcgen05_fence_before();
+      tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty[acc]);
     }
@@ -676,10 +538,10 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     if (TMA_OUT && elected) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   }
 
-  tcgen05_fence_before();
+  tc_fence_before();
   __syncthreads();
   if (warp == NPROD) {
-    tcgen05_fence_after();
+    tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
@@ -706,30 +568,11 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const int *partials,
 }
 
 // ---- host side -------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
-                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                  CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn()
-{
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void *p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-  });
-  return fn;
-}
-
 // [rows][K] byte matrix, K contiguous; box = bkb bytes of K x box_rows rows, bkb-byte swizzle.
 // Elements outside the matrix read as zero.
 bool make_map(CUtensorMap *map, const void *base, int rows, int K, int box_rows, int bkb)
 {
-  EncodeTiledFn enc = encode_fn();
+  EncodeTiledFn enc = encode_tiled_fn();
   if (!enc) { set_error(PULPNN_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver"); return false; }
   cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)K};
