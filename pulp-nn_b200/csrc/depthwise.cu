@@ -265,6 +265,7 @@ bool launch_depthwise(Context &c, const DepthwiseProblem &p)
 {
   if (!c.opt_force_generic && depthwise_hwc3x3_tma_supported(p)) return launch_depthwise_hwc3x3_tma(c, p);
   if (!c.opt_force_generic && depthwise_hwc3x3_supported(p)) return launch_depthwise_hwc3x3(c, p);
+  if (!c.opt_force_generic && depthwise_chw3x3_tma_supported(p)) return launch_depthwise_chw3x3_tma(c, p);
   if (!c.opt_force_generic && depthwise_chw3x3_supported(p)) return launch_depthwise_chw3x3(c, p);
   switch (p.epi.mode) {
     case EPI_NONE: return launch_dw_mode<EPI_NONE>(c, p);

@@ -82,6 +82,14 @@ __device__ __forceinline__ void transpose4(const unsigned m0, const unsigned m1,
   t[2] = prmt(b, d, rot.sel_lo); t[3] = prmt(b, d, rot.sel_hi);
 }
 
+// a 32 x 32 -> 64-bit multiply-add in one instruction
+__device__ __forceinline__ long long mad_wide_s32(int a, int b, long long c)
+{
+  long long d;
+  asm("mad.wide.s32 %0, %1, %2, %3;" : "=l"(d) : "r"(a), "r"(b), "l"(c));
+  return d;
+}
+
 // geometry of a tile, all compile-time
 template <int S, int NGX, int CI> struct Geo {
   static constexpr int LPC = CI / 4;                          // lanes (channel words) per pixel
@@ -125,7 +133,7 @@ __device__ __forceinline__ void finalize_k(const int (&acc)[4][4], const QuantT<
       if (MODE == EPI_BN32)
         v[j] = (int)((unsigned)q.k[j] * (unsigned)acc[i][j] + (unsigned)q.l[j]) >> e.shift;
       else if (MODE == EPI_BN64 && K32)      // every k fits in 32 bits: one wide multiply-add
-        v[j] = (int)(((long long)(int)q.k[j] * acc[i][j] + (long long)q.l[j]) >> e.shift);
+        v[j] = (int)(mad_wide_s32((int)q.k[j], acc[i][j], (long long)q.l[j]) >> e.shift);
       else if (MODE == EPI_BN64)
         v[j] = (int)((long long)((unsigned long long)q.k[j] * (unsigned long long)(long long)acc[i][j] +
                                  (unsigned long long)q.l[j]) >> e.shift);
@@ -439,6 +447,263 @@ depthwise_hwc3x3_tma_kernel(const __grid_constant__ CUtensorMap map_in, const __
   }
 }
 
+// ---- CHW input (the reference's own layout for this kernel, pulp_nn_depthwise_generic.c:74) -------
+// The same accumulate / requantise code as above, fed differently: a CTA stages 32 channels x whole
+// input rows ([c][row][x], the TMA box of a [B][C][H][W] tensor), a thread owns four channels and
+// four adjacent output columns as before, but here the lanes of a warp run along x, so a channel's
+// four (stride 1) or eight (stride 2) input bytes ARE the channel word and no byte transpose is
+// needed on the way in: two funnel shifts make the shifted windows. The output is HWC: pixel words
+// go to a tile whose pixels are 36 bytes apart (so that lanes four pixels apart meet at most
+// two-way in a bank), and after the group's barrier all threads copy the tile out, eight words =
+// 32 channel bytes per pixel, in whole 32-byte sectors.
+template <int S, int LPQ> struct GeoChw {
+  static constexpr int CT = 32;                         // channels per tile
+  static constexpr int WOP = 4 * LPQ;                   // output columns the lanes of a quad cover
+  static constexpr int ROWS_IN = S == 1 ? 3 : 4;
+  static constexpr int ROWS_OUT = S == 1 ? 3 : 2;
+  static constexpr int PP = CT + 4;                     // pixel pitch of the output tile, bytes
+  static constexpr int OUT_PITCH = WOP * PP;
+  static constexpr int TILE_BYTES = ROWS_OUT * OUT_PITCH;
+  static constexpr int THREADS = 8 * LPQ;               // eight channel quads x LPQ column groups
+  static constexpr int HEADER = 128;                    // barriers and the abort flag, ahead of the ring
+};
+
+struct ChwTmaParams {
+  DepthwiseProblem p;
+  int chunks, strips, rows_per_strip;
+  int stage_bytes;                 // ROWS_IN * W * 32
+  int *status;
+};
+
+__device__ __forceinline__ void lds64(uint32_t addr, unsigned &lo, unsigned &hi)
+{
+  asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(lo), "=r"(hi) : "r"(addr));
+}
+
+// one staged row of the thread's four channels -> windows; base[j] = the channel's word at row 0
+__device__ __forceinline__ void load_win_chw(const uint32_t (&base)[4], uint32_t roff, unsigned lmask, unsigned rmask, Win1 &w)
+{
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    const uint32_t a = base[j] + roff;
+    const unsigned m = lds32(a), left = lds32(a - 4) & lmask, right = lds32(a + 4) & rmask;
+    w.T[j] = m;
+    w.A[j] = __funnelshift_r(left, m, 24);        // [left, p0, p1, p2]
+    w.B[j] = __funnelshift_r(m, right, 8);        // [p1, p2, p3, right]
+  }
+}
+__device__ __forceinline__ void load_win_chw(const uint32_t (&base)[4], uint32_t roff, unsigned lmask, unsigned, Win2 &w)
+{
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    const uint32_t a = base[j] + roff;
+    unsigned m0, m1;
+    lds64(a, m0, m1);
+    const unsigned left = lds32(a - 4) & lmask;
+    w.T[j] = m0; w.U[j] = m1;
+    w.A[j] = __funnelshift_r(left, m0, 24);       // [left, p0, p1, p2]
+    w.C[j] = __funnelshift_r(m0, m1, 24);         // [p3, p4, p5, p6]
+  }
+}
+
+template <int MODE, int S, int LPQ>
+__global__ void __launch_bounds__(GeoChw<S, LPQ>::THREADS, 512 / GeoChw<S, LPQ>::THREADS)
+depthwise_chw3x3_tma_kernel(const __grid_constant__ CUtensorMap map_in, const ChwTmaParams g)
+{
+  using G = GeoChw<S, LPQ>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t pad = (128u - (smem_u32(smem_raw) & 127u)) & 127u;
+  uint8_t *sm = smem_raw + pad;
+  uint64_t *full = reinterpret_cast<uint64_t *>(sm);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(full + RING);
+  uint8_t *ring_p = sm + G::HEADER;
+  const uint32_t stage = (uint32_t)g.stage_bytes;
+  const uint32_t ring = smem_u32(ring_p), tiles = ring + RING * stage;
+
+  const DepthwiseProblem &p = g.p;
+  const Epilogue &e = p.epi;
+  const int tid = threadIdx.x, gx = tid % LPQ, qd = tid / LPQ;
+
+  int t = blockIdx.x;
+  const int strip = t % g.strips; t /= g.strips;
+  const int chunk = t % g.chunks;
+  const int b = t / g.chunks;
+  const int c_base = chunk * G::CT;
+  const int oyA = strip * g.rows_per_strip, oyB = min(oyA + g.rows_per_strip, p.Ho);
+  const int ngroups = 1 + (oyB - oyA + G::ROWS_OUT - 1) / G::ROWS_OUT;
+  const int in_y0 = S == 1 ? oyA - 2 : 2 * oyA - 4;
+
+  if (tid == 0) {
+    for (int s = 0; s < RING; s++) mbar_init(&full[s], 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    const int first = ngroups < RING ? ngroups : RING;
+    for (int j = 0; j < first; j++) {
+      mbar_arrive_expect_tx(&full[j], stage);
+      tma_load_4d(ring_p + j * stage, &map_in, &full[j], 0, in_y0 + j * G::ROWS_IN, c_base, b);
+    }
+  }
+
+  // a quad past the last channel (a partial chunk) works on the last real quad; nothing of it is stored
+  const int c = min(c_base + 4 * qd, p.C - 4);
+  int wa[3][4], wb[3][4];
+  {
+    unsigned W[9];
+    const unsigned *wp = reinterpret_cast<const unsigned *>(p.w + (size_t)c * 9);
+#pragma unroll
+    for (int i = 0; i < 9; i++) W[i] = __ldg(wp + i);
+#pragma unroll
+    for (int j = 0; j < 4; j++)
+#pragma unroll
+      for (int fy = 0; fy < 3; fy++) {
+        wa[fy][j] = taps3(W, j * 9 + fy * 3);
+        wb[fy][j] = (int)((unsigned)wa[fy][j] << 8);
+      }
+  }
+  QuantT<MODE> q;
+  int init[4];
+  bool k32 = true;
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    q.bias[j] = e.bias ? (int)__ldg(reinterpret_cast<const int8_t *>(e.bias) + c + j) : 0;
+    q.k[j] = 0; q.l[j] = 0;
+    init[j] = (MODE == EPI_BN32 || MODE == EPI_BN64) ? 0 : q.bias[j];
+    if (MODE == EPI_BN32) {
+      const int k = __ldg(reinterpret_cast<const int *>(e.k) + c + j);
+      q.k[j] = k;
+      q.l[j] = (int)((unsigned)k * (unsigned)q.bias[j] + (unsigned)__ldg(reinterpret_cast<const int *>(e.lambda) + c + j));
+    } else if (MODE == EPI_BN64) {
+      const long long k = __ldg(reinterpret_cast<const long long *>(e.k) + c + j);
+      q.k[j] = k;
+      q.l[j] = (long long)((unsigned long long)k * (unsigned long long)(long long)q.bias[j] +
+                           (unsigned long long)__ldg(reinterpret_cast<const long long *>(e.lambda) + c + j));
+      k32 = k32 && (k == (long long)(int)k);
+    }
+  }
+  __syncthreads();                                   // the barriers are initialised
+
+  // lanes past the last column group read column group 0 (their results are never copied out)
+  const uint32_t W = (uint32_t)p.W;
+  const bool col_on = 4 * gx < p.Wo;
+  const uint32_t xoff = col_on ? (uint32_t)(4 * S * gx) : 0u;
+  const unsigned lmask = (col_on && gx) ? 0xffffffffu : 0u;                        // column -1 is padding
+  const unsigned rmask = (S == 1 && xoff + 4 < W) ? 0xffffffffu : 0u;              // so is column W
+  uint32_t cb[4];
+#pragma unroll
+  for (int j = 0; j < 4; j++) cb[j] = ring + (uint32_t)((4 * qd + j) * G::ROWS_IN) * W + xoff;
+  const uint32_t out_thr = tiles + (uint32_t)(4 * gx) * G::PP + 4u * qd;
+
+  bool dead = false;
+  int issued = ngroups < RING ? ngroups : RING;
+  int consumed = 0;
+  auto refill = [&](int j_next, int grp_) {          // thread 0 only
+    mbar_arrive_expect_tx(&full[grp_], stage);
+    tma_load_4d(ring_p + grp_ * stage, &map_in, &full[grp_], 0, in_y0 + j_next * G::ROWS_IN, c_base, b);
+    issued = j_next + 1;
+  };
+  // all threads: the finished tile -> HWC output, one 32-bit word (four channels of a pixel) at a time
+  const int cw = tid & 7, cp = tid >> 3;
+  const bool cw_on = c_base + 4 * cw < p.C;
+  auto copy_out = [&](int half, int oy0, int nrows) {
+    for (int r = 0; r < nrows; r++) {
+      uint8_t *orow = p.out + (((size_t)b * p.Ho + oy0 + r) * p.Wo) * p.C + c_base + 4 * cw;
+      const uint32_t trow = tiles + half * G::TILE_BYTES + r * G::OUT_PITCH + 4u * cw;
+      if (cw_on)
+        for (int px = cp; px < p.Wo; px += G::THREADS / 8)
+          *reinterpret_cast<unsigned *>(orow + (size_t)px * p.C) = lds32(trow + px * G::PP);
+    }
+  };
+
+  int acc[S == 1 ? 3 : 1][4][4];
+#pragma unroll
+  for (int a = 0; a < (S == 1 ? 3 : 1); a++)
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+      for (int j = 0; j < 4; j++) acc[a][i][j] = 0;
+
+  // ---- group 0: the rows above the strip's first output row only open accumulators ---------------
+  if (!mbar_wait(&full[0], 0, abort_flag, g.status, ST_HWC_TMA)) dead = true;
+  if (!dead) {
+    consumed = 1;
+    if constexpr (S == 1) {
+      Win1 w;
+      load_win_chw(cb, W, lmask, rmask, w);                       // input row oyA-1
+      mac1<false, false>(w, wa, wb, init, acc[0], acc[0], acc[0]);
+      load_win_chw(cb, 2 * W, lmask, rmask, w);                   // input row oyA
+      mac1<false, true>(w, wa, wb, init, acc[0], acc[0], acc[S == 1 ? 1 : 0]);
+    } else {
+      Win2 w;
+      load_win_chw(cb, 3 * W, lmask, rmask, w);                   // input row 2*oyA-1
+      mac2<true>(w, wa[0], wb[0], init, acc[0]);
+    }
+  }
+  __syncthreads();
+  if (tid == 0 && !dead && RING < ngroups) refill(RING, 0);
+
+  int grp = 0, half = 0;
+  uint32_t parity = 0;
+  for (int j = 1; j < ngroups; j++) {
+    if (++grp == RING) { grp = 0; parity ^= 1; }
+    if (!dead && !mbar_wait(&full[grp], parity, abort_flag, g.status, ST_HWC_TMA)) dead = true;
+    const int oy0 = oyA + (j - 1) * G::ROWS_OUT;
+    const int rows_here = min(oyB - oy0, G::ROWS_OUT);
+    if (!dead) {
+      consumed = j + 1;
+      const uint32_t oa = out_thr + half * G::TILE_BYTES;
+      uint32_t ia[4];
+#pragma unroll
+      for (int jj = 0; jj < 4; jj++) ia[jj] = cb[jj] + grp * stage;
+      if constexpr (S == 1) {
+        constexpr int A1 = S == 1 ? 1 : 0, A2 = S == 1 ? 2 : 0;
+        Win1 w;
+        load_win_chw(ia, 0, lmask, rmask, w);
+        mac1<true, true>(w, wa, wb, init, acc[0], acc[A1], acc[A2]);
+        finalize_row<MODE, G::PP>(acc[0], q, e, k32, oa);
+        if (rows_here > 1) {
+          load_win_chw(ia, W, lmask, rmask, w);
+          mac1<true, true>(w, wa, wb, init, acc[A1], acc[A2], acc[0]);
+          finalize_row<MODE, G::PP>(acc[A1], q, e, k32, oa + G::OUT_PITCH);
+          if (rows_here > 2) {
+            load_win_chw(ia, 2 * W, lmask, rmask, w);
+            mac1<true, true>(w, wa, wb, init, acc[A2], acc[0], acc[A1]);
+            finalize_row<MODE, G::PP>(acc[A2], q, e, k32, oa + 2 * G::OUT_PITCH);
+          }
+        }
+      } else {
+        Win2 w, v;
+        load_win_chw(ia, 0, lmask, rmask, w);                     // input row 2m
+        load_win_chw(ia, W, lmask, rmask, v);                     // 2m+1: closes row m, opens m+1
+        mac2<false>(w, wa[1], wb[1], init, acc[0]);
+        if (rows_here > 1) load_win_chw(ia, 2 * W, lmask, rmask, w);
+        mac2<false>(v, wa[2], wb[2], init, acc[0]);
+        finalize_row<MODE, G::PP>(acc[0], q, e, k32, oa);
+        if (rows_here > 1) {
+          mac2<true>(v, wa[0], wb[0], init, acc[0]);
+          load_win_chw(ia, 3 * W, lmask, rmask, v);
+          mac2<false>(w, wa[1], wb[1], init, acc[0]);
+          mac2<false>(v, wa[2], wb[2], init, acc[0]);
+          finalize_row<MODE, G::PP>(acc[0], q, e, k32, oa + G::OUT_PITCH);
+          mac2<true>(v, wa[0], wb[0], init, acc[0]);
+        }
+      }
+    }
+    __syncthreads();           // the group has been read and the tile written by everyone
+    if (tid == 0 && !dead && j + RING < ngroups) refill(j + RING, grp);
+    // the other half is written by the next group; this half again only after the next barrier
+    if (!dead) copy_out(half, oy0, rows_here);
+    half ^= 1;
+  }
+  if (tid == 0 && *abort_flag) {
+    // no TMA write may still be in flight when the CTA's shared memory is released
+    for (int qn = consumed; qn < issued; qn++) {
+      const unsigned long long t0 = global_ns();
+      while (!mbar_try_wait(&full[qn % RING], (uint32_t)(qn / RING) & 1u))
+        if (global_ns() - t0 > WAIT_LIMIT_NS) break;
+    }
+  }
+}
+
 // ---- host side ----------------------------------------------------------------------------------
 bool encode_4d(CUtensorMap *map, const void *base, int C, int Wd, int Hd, int B, int ci, int box_w, int box_h)
 {
@@ -538,7 +803,78 @@ bool launch_stride(Context &c, const DepthwiseProblem &p)
   return p.sx == 1 ? launch_ci<MODE, 1>(c, p) : launch_ci<MODE, 2>(c, p);
 }
 
+// ---- CHW input ------------------------------------------------------------------------------------
+template <int MODE, int S, int LPQ>
+bool launch_chw_geo(Context &c, const DepthwiseProblem &p)
+{
+  using G = GeoChw<S, LPQ>;
+  ChwTmaParams g;
+  g.p = p;
+  g.chunks = (p.C + G::CT - 1) / G::CT;
+  g.stage_bytes = G::ROWS_IN * p.W * G::CT;
+  g.status = ctx_status_word(c);
+  if (!g.status) return false;
+  const int smem = 128 + G::HEADER + RING * g.stage_bytes + 2 * G::TILE_BYTES;
+  auto kern = depthwise_chw3x3_tma_kernel<MODE, S, LPQ>;
+  static thread_local int smem_set = 0;
+  if (smem > smem_set) {
+    if (!cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
+                 "cudaFuncSetAttribute(depthwise_chw3x3_tma)"))
+      return false;
+    smem_set = smem;
+  }
+  int resident = 0;
+  if (!cuda_ok(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, kern, G::THREADS, smem), "occupancy query")) return false;
+  if (resident < 1) resident = 1;
+  const long long columns = (long long)p.B * g.chunks;
+  const long long want = 4LL * (c.sm_count > 0 ? c.sm_count : 148) * resident;
+  int strips = 1;
+  while (columns * strips < want && p.Ho / (strips * 2) >= 4 * G::ROWS_OUT) strips *= 2;
+  int rows = (p.Ho + strips - 1) / strips;
+  rows = (rows + G::ROWS_OUT - 1) / G::ROWS_OUT * G::ROWS_OUT;
+  g.rows_per_strip = rows;
+  g.strips = (p.Ho + rows - 1) / rows;
+  const long long total = columns * g.strips;
+  if (total > 0x7fffffffLL) { set_error(PULPNN_ERR_UNSUPPORTED, "depthwise: too many tiles"); return false; }
+  // [B][C][H][W]: whole rows of 32 channels per box
+  CUtensorMap map_in;
+  if (!encode_4d(&map_in, p.in, p.W, p.H, p.C, p.B, p.W, G::ROWS_IN, G::CT)) return false;
+  kern<<<(unsigned)total, G::THREADS, smem, c.stream>>>(map_in, g);
+  count_launch();
+  return cuda_ok(cudaGetLastError(), "depthwise_chw3x3_tma launch");
+}
+
+template <int MODE>
+bool launch_chw_stride(Context &c, const DepthwiseProblem &p)
+{
+  const bool wide = p.Wo > 64;
+  if (p.sx == 1) return wide ? launch_chw_geo<MODE, 1, 32>(c, p) : launch_chw_geo<MODE, 1, 16>(c, p);
+  return wide ? launch_chw_geo<MODE, 2, 32>(c, p) : launch_chw_geo<MODE, 2, 16>(c, p);
+}
+
 }  // namespace
+
+bool depthwise_chw3x3_tma_supported(const DepthwiseProblem &p)
+{
+  if (p.in_is_hwc || p.ky != 3 || p.kx != 3 || p.pt != 1 || p.pl != 1) return false;
+  if (p.sx != p.sy || (p.sx != 1 && p.sx != 2)) return false;
+  // whole rows are TMA boxes: 16-byte multiples, at most 256 bytes; the lanes of a quad span a row
+  if (p.W % 16 != 0 || p.W > 256 || p.C % 4 != 0) return false;
+  if (p.Wo <= 16 || p.Wo > 128) return false;
+  if ((reinterpret_cast<uintptr_t>(p.in) & 15) || (reinterpret_cast<uintptr_t>(p.out) & 3)) return false;
+  if (reinterpret_cast<uintptr_t>(p.w) & 3) return false;
+  return encode_tiled_fn() != nullptr;
+}
+
+bool launch_depthwise_chw3x3_tma(Context &c, const DepthwiseProblem &p)
+{
+  switch (p.epi.mode) {
+    case EPI_NONE: return launch_chw_stride<EPI_NONE>(c, p);
+    case EPI_MULT: return launch_chw_stride<EPI_MULT>(c, p);
+    case EPI_BN32: return launch_chw_stride<EPI_BN32>(c, p);
+    default:       return launch_chw_stride<EPI_BN64>(c, p);
+  }
+}
 
 bool depthwise_hwc3x3_tma_supported(const DepthwiseProblem &p)
 {

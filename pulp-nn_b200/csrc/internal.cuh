@@ -184,6 +184,8 @@ bool depthwise_hwc3x3_supported(const DepthwiseProblem &p);
 bool launch_depthwise_hwc3x3(Context &c, const DepthwiseProblem &p);
 bool depthwise_hwc3x3_tma_supported(const DepthwiseProblem &p);
 bool launch_depthwise_hwc3x3_tma(Context &c, const DepthwiseProblem &p);
+bool depthwise_chw3x3_tma_supported(const DepthwiseProblem &p);
+bool launch_depthwise_chw3x3_tma(Context &c, const DepthwiseProblem &p);
 bool depthwise_chw3x3_supported(const DepthwiseProblem &p);
 bool launch_depthwise_chw3x3(Context &c, const DepthwiseProblem &p);
 int *ctx_status_word(Context &c);               // allocated on first use; nullptr on failure

@@ -264,6 +264,28 @@ def test_depthwise_hwc_tma_kernel(bits, relu, bn, stride, gpu, restatement):
     assert api.device_status() == 0
 
 
+@pytest.mark.parametrize("bits", [32, 64])
+@pytest.mark.parametrize("relu,bn", MODES)
+@pytest.mark.parametrize("stride", [1, 2])
+def test_depthwise_chw_tma_kernel(bits, relu, bn, stride, gpu, restatement):
+    """CHW input whose rows are a multiple of 16 bytes and wider than 16 outputs takes the
+    TMA-staged kernel: 16 and 32 lanes per channel quad, a partly empty last column group, a
+    ragged last chunk of 32 channels, heights that are not a multiple of the rows a group
+    completes, strips (batch 1), and (64-bit tree) k that does not fit 32 bits."""
+    for (H, W, C, B) in ((9, 32 * stride, 8, 2), (13, 48 * stride, 36, 2), (7, 80 * stride, 12, 2), (56, 112, 64, 1),
+                         (10, 128, 4, 3), (33, 64, 32, 1)):
+        big = bits == 64 and H == 7
+        c = wl.depthwise_case(38, H, W, C, strides=(stride, stride), batch=B, bits=bits, out_shift=9,
+                              with_bias=True, out_mult=3, relu=relu, bn=bn,
+                              k_range=(1, 2 ** 33) if big else (1, 64),
+                              lam_range=(-2 ** 34, 2 ** 34) if big else (-32768, 32767))
+        if big:
+            c["out_shift"] = 30
+        want = restatement.depthwise(bits, c["x"], c["w"], c["k"], c["lam"], **dw_kw(c))
+        same(gpu.depthwise(bits, c["x"], c["w"], c["k"], c["lam"], **dw_kw(c)), want)
+    assert api.device_status() == 0
+
+
 def test_depthwise_hwc_tma_small_batch_strips(gpu, restatement):
     """Batch 1 splits the height into strips (each with its own opening group of rows)."""
     for (H, W, C, s) in ((56, 56, 128, 1), (56, 56, 128, 2), (112, 20, 128, 1)):
