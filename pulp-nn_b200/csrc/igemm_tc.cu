@@ -74,8 +74,23 @@ struct TcParams {
   int w_resident;        // 1: the CTA's n-tile of W sits in shared memory for the CTA's lifetime
   int stationary;        // 1: a CTA keeps one n-tile (blockIdx % n_tiles) and walks down the m-tiles
   int n_stages;          // depth of the operand ring
+  // Spatial convolution (conv = 1): an m-tile is a patch of TH x TW output pixels (TH * TW = 128,
+  // TW = 1 << tw_log2) of one image, and the A operand of slab s = (filter tap, chunk of Cin) is
+  // the 4-D TMA box of the input pixels that tap reads for the patch. Pixels outside the image
+  // arrive as zeros from the TMA unit: the zero padding (32bit/src/pulp_nn_conv_Ho_parallel.c:80-164).
+  int conv, tw_log2, tiles_x, tiles_y, chunks_per_tap, kx, sx, sy, pl, pt, Ho, Wo;
   int *status;
 };
+
+// m-tile index of a convolution -> image and first output pixel of the patch
+__device__ __forceinline__ void conv_patch(const TcParams &g, int mt, int &b, int &y0, int &x0)
+{
+  const int r = mt / g.tiles_x, tx = mt - r * g.tiles_x;
+  b = r / g.tiles_y;
+  const int ty = r - b * g.tiles_y;
+  x0 = tx << g.tw_log2;
+  y0 = ty << (7 - g.tw_log2);
+}
 
 // bytes of the operand ring (+ resident W). With TMA stores the epilogue stages one output tile
 // per group of warps in shared memory, which the ring has to make room for.
@@ -207,12 +222,24 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         if (!unit_at(g, i, units, nt0, m0, m_step, nt, mt, ks)) break;
         const int slab0 = ks * g.slabs_per_slice;
         const int slab1 = min(slab0 + g.slabs_per_slice, g.total_slabs);
+        int cb = 0, cy = 0, cx = 0;             // convolution: image and first input pixel of the patch
+        if (g.conv) {
+          conv_patch(g, mt, cb, cy, cx);
+          cy = cy * g.sy - g.pt;
+          cx = cx * g.sx - g.pl;
+        }
         for (int s = slab0; s < slab1; s++) {
           if ((st & (NPROD - 1)) == warp) {
             if (!mbar_wait(&empty_bar[st], ph ^ 1, abort_flag, g.status, ST_PRODUCER)) { ok = false; break; }
             uint8_t *a_dst = ring + st * stage_bytes;
             mbar_arrive_expect_tx(&full_bar[st], (uint32_t)stage_bytes);
-            tma_load_2d(a_dst, &map_a, &full_bar[st], s * BKB, mt * BM);
+            if (g.conv) {
+              const int tap = s / g.chunks_per_tap, chunk = s - tap * g.chunks_per_tap;
+              const int fy = tap / g.kx, fx = tap - fy * g.kx;
+              tma_load_4d(a_dst, &map_a, &full_bar[st], chunk * BKB, cx + fx, cy + fy, cb);
+            } else {
+              tma_load_2d(a_dst, &map_a, &full_bar[st], s * BKB, mt * BM);
+            }
             if (!g.w_resident) tma_load_2d(a_dst + A_BYTES, &map_b, &full_bar[st], s * BKB, nt * BN_TILE);
             issued_parity[st] = (uint8_t)(1u + ph);
           }
@@ -443,7 +470,14 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           // (B) the round's columns are complete
           asm volatile("bar.sync %0, %1;" ::"r"(1 + grp), "n"(GROUP_THREADS) : "memory");
           if (elected && !dead) {
-            tma_store_2d(&map_out, out_tile, n0 + rd * 128, mt * BM);   // rows past M, columns past N are dropped
+            // rows past M (pixels past the image's edge), columns past N are dropped
+            if (g.conv) {
+              int cb, cy, cx;
+              conv_patch(g, mt, cb, cy, cx);
+              tma_store_4d(&map_out, out_tile, n0 + rd * 128, cx, cy, cb);
+            } else {
+              tma_store_2d(&map_out, out_tile, n0 + rd * 128, mt * BM);
+            }
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
           }
         }
@@ -451,8 +485,17 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       }
       if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag, g.status, ST_EPILOGUE)) break;
       tc_fence_after();
-      const int m = mt * BM + quad * 32 + lane;
-      const bool row_ok = m < g.M;
+      int m = mt * BM + quad * 32 + lane;
+      bool row_ok = m < g.M;
+      if (g.conv) {        // row of the tile -> pixel of the patch -> row of the output
+        int cb, cy, cx;
+        conv_patch(g, mt, cb, cy, cx);
+        const int r = quad * 32 + lane;
+        cy += r >> g.tw_log2;
+        cx += r & ((1 << g.tw_log2) - 1);
+        row_ok = cy < g.Ho && cx < g.Wo;
+        m = (cb * g.Ho + cy) * g.Wo + cx;
+      }
       const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN_TILE);
 #pragma unroll 1
       for (int lc = 0; lc < HALF_COLS; lc += 32) {   // lc: offset inside this warp's parameter copy
@@ -587,6 +630,41 @@ bool make_map(CUtensorMap *map, const void *base, int rows, int K, int box_rows,
   return true;
 }
 
+// [B][H][W][C] image, boxes of box_c bytes x box_w x box_h pixels of one image, every sx-th (sy-th)
+// pixel of the box taken: the pixels one filter tap reads for a patch of outputs
+bool make_map_4d(CUtensorMap *map, const void *base, int C, int Wd, int Hd, int B, int box_c, int box_w, int box_h,
+                 int sx, int sy)
+{
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) { set_error(PULPNN_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver"); return false; }
+  cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)Wd, (cuuint64_t)Hd, (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)C, (cuuint64_t)Wd * C, (cuuint64_t)Hd * Wd * C};
+  cuuint32_t box[4] = {(cuuint32_t)box_c, (cuuint32_t)((box_w - 1) * sx + 1), (cuuint32_t)((box_h - 1) * sy + 1), 1};
+  cuuint32_t estr[4] = {1, (cuuint32_t)sx, (cuuint32_t)sy, 1};
+  const CUtensorMapSwizzle sw = box_c == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                              : (box_c == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void *>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { set_error(PULPNN_ERR_CUDA, "cuTensorMapEncodeTiled (4-D) failed with code %d", (int)r); return false; }
+  return true;
+}
+
+// patch width (a power of two, the patch has 128 pixels) that covers the output with the fewest
+// wasted pixels; the wider one on a tie
+int pick_patch_width_log2(int Ho, int Wo, int sx, int sy)
+{
+  int best = -1;
+  long long best_cost = 0;
+  for (int l = 3; l <= 7; l++) {
+    const int tw = 1 << l, th = 128 >> l;
+    if ((tw - 1) * sx + 1 > 256 || (th - 1) * sy + 1 > 256) continue;
+    const long long cost = (long long)((Wo + tw - 1) / tw) * ((Ho + th - 1) / th);
+    if (best < 0 || cost <= best_cost) { best = l; best_cost = cost; }
+  }
+  return best;
+}
+
 // the three tensor maps of a launch (the output map only matters with TMA stores)
 struct TcMaps { CUtensorMap a, b, out; };
 
@@ -643,30 +721,49 @@ bool launch_final(Context &c, const TcMaps &m, const TcParams &g, int bn, int bk
 
 }  // namespace
 
+// a pointwise convolution or a fully connected layer: A is the plain [M][K] matrix
+static bool igemm_is_plain(const ConvProblem &p)
+{
+  return p.ky == 1 && p.kx == 1 && p.sy == 1 && p.sx == 1 && p.pt == 0 && p.pl == 0 && p.H == p.Ho && p.W == p.Wo;
+}
+
 bool igemm_tc_supported(const Context &c, const ConvProblem &p)
 {
   (void)c;
-  if (p.ky != 1 || p.kx != 1 || p.sy != 1 || p.sx != 1 || p.pt != 0 || p.pl != 0) return false;
-  if (p.H != p.Ho || p.W != p.Wo) return false;
-  if (p.Cin < 16 || p.Cin % 16 != 0) return false;      // TMA: row pitch must be a multiple of 16 bytes
   if ((reinterpret_cast<uintptr_t>(p.in) & 15) || (reinterpret_cast<uintptr_t>(p.w) & 15)) return false;
   const long long M = (long long)p.B * p.Ho * p.Wo;
   if (M > 0x7fffffffLL) return false;
-  return true;
+  if (igemm_is_plain(p)) return p.Cin >= 16 && p.Cin % 16 == 0;      // TMA: row pitch must be a multiple of 16 bytes
+  // spatial convolution: a K-slab is a chunk of one tap's channels, so Cin is a multiple of the slab
+  if (p.Cin % 32 != 0 || p.ky * p.kx > 121) return false;
+  if (p.sx > 16 || p.sy > 16) return false;
+  return pick_patch_width_log2(p.Ho, p.Wo, p.sx, p.sy) >= 0 && encode_tiled_fn() != nullptr;
 }
 
 bool launch_igemm_tc(Context &c, const ConvProblem &p)
 {
   TcParams g;
-  g.M = p.B * p.Ho * p.Wo; g.N = p.Cout; g.K = p.Cin;
+  g.M = p.B * p.Ho * p.Wo; g.N = p.Cout; g.K = p.ky * p.kx * p.Cin;
   g.epi = p.epi;
   const bool raw = p.epi.mode == EPI_RAW32;
+  g.conv = igemm_is_plain(p) ? 0 : 1;
+  g.tw_log2 = 7; g.tiles_x = g.tiles_y = 1; g.chunks_per_tap = 1;
+  g.kx = p.kx; g.sx = p.sx; g.sy = p.sy; g.pl = p.pl; g.pt = p.pt; g.Ho = p.Ho; g.Wo = p.Wo;
   // K-slab width: the narrowest box that does not fetch bytes beyond K; wider boxes for long K
   int bkb = 128;
-  if (g.K <= 32) bkb = 32;
-  else if (g.K <= 64) bkb = 64;
-  else if (g.K < 128 && g.K % 64 != 0) bkb = 32;       // 80, 96, 112: no padded fetch with 32-byte slabs
-  g.m_tiles = (g.M + BM - 1) / BM;
+  if (g.conv) {
+    bkb = p.Cin % 128 == 0 ? 128 : (p.Cin % 64 == 0 ? 64 : 32);
+    g.chunks_per_tap = p.Cin / bkb;
+    g.tw_log2 = pick_patch_width_log2(p.Ho, p.Wo, p.sx, p.sy);
+    g.tiles_x = (p.Wo + (1 << g.tw_log2) - 1) >> g.tw_log2;
+    g.tiles_y = (p.Ho + (128 >> g.tw_log2) - 1) / (128 >> g.tw_log2);
+    g.m_tiles = p.B * g.tiles_x * g.tiles_y;
+  } else {
+    if (g.K <= 32) bkb = 32;
+    else if (g.K <= 64) bkb = 64;
+    else if (g.K < 128 && g.K % 64 != 0) bkb = 32;       // 80, 96, 112: no padded fetch with 32-byte slabs
+    g.m_tiles = (g.M + BM - 1) / BM;
+  }
   g.total_slabs = (g.K + bkb - 1) / bkb;
   const int sms = c.sm_count > 0 ? c.sm_count : 148;
   // uint8 tiles can leave through TMA stores (staged in shared memory, at most 128 columns wide)
@@ -681,7 +778,7 @@ bool launch_igemm_tc(Context &c, const ConvProblem &p)
     // split K only when the tiles alone cannot occupy the GPU and there is enough K to share
     int slices = 1;
     if (c.opt_split_k > 0) slices = c.opt_split_k;
-    else if (tiles * 2 <= sms && g.total_slabs >= 8) {
+    else if (tiles * 8 <= sms + 8 && g.total_slabs >= 8) {   // measured: from about 32 tiles on the second pass costs more than it saves
       slices = sms / tiles;
       if (slices > g.total_slabs / 4) slices = g.total_slabs / 4;
       if (slices > 16) slices = 16;
@@ -720,10 +817,17 @@ bool launch_igemm_tc(Context &c, const ConvProblem &p)
   g.status = c.status_word;
 
   TcMaps maps;
-  if (!make_map(&maps.a, p.in, g.M, g.K, BM, bkb)) return false;
+  const int tw = 1 << g.tw_log2, th = 128 >> g.tw_log2;
+  if (g.conv) {
+    if (!make_map_4d(&maps.a, p.in, p.Cin, p.W, p.H, p.B, bkb, tw, th, p.sx, p.sy)) return false;
+  } else if (!make_map(&maps.a, p.in, g.M, g.K, BM, bkb)) return false;
   if (!make_map(&maps.b, p.w, g.N, g.K, bn, bkb)) return false;
   maps.out = maps.a;
-  if (tma_out && !make_map(&maps.out, p.out, g.M, g.N, BM, bn < 128 ? bn : 128)) return false;   // box = at most 128 bytes x 128 rows
+  if (tma_out) {        // box = at most 128 bytes x 128 rows
+    if (g.conv) {
+      if (!make_map_4d(&maps.out, p.out, g.N, p.Wo, p.Ho, p.B, bn < 128 ? bn : 128, tw, th, 1, 1)) return false;
+    } else if (!make_map(&maps.out, p.out, g.M, g.N, BM, bn < 128 ? bn : 128)) return false;
+  }
 
   const int units = tiles * g.k_slices;
   int grid = units < sms ? units : sms;
@@ -833,6 +937,8 @@ extern "C" int pulpnn_linear_out_32_static_scratch(const uint8_t *pInBuffer, con
   TcParams g;
   g.M = n_vectors; g.N = num_o_neurons; g.K = dim_vec;
   g.epi = p.epi;
+  g.conv = 0; g.tw_log2 = 7; g.tiles_x = g.tiles_y = 1; g.chunks_per_tap = 1;
+  g.kx = g.sx = g.sy = 1; g.pl = g.pt = 0; g.Ho = g.Wo = 1;
   const int bn = g.N <= 64 ? 64 : (g.N <= 128 ? 128 : 256);
   int bkb = 128;
   if (g.K <= 32) bkb = 32;

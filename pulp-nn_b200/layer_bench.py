@@ -92,6 +92,12 @@ def build_case(name, B, pkg):
             fn = lambda: api.pulp_nn_linear_out_32(32, x, None, o, w, 4096, 4096)  # noqa: E731
             nbytes = B * 4096 * 5 + 4096 * 4096
         return fn, 2.0 * B * 4096 * 4096, nbytes, (x, w, bias, o)
+    if name == "fc":
+        # MobileNet's classifier: 1024 -> 1000, raw int32 logits
+        c = wl.linear_case(5, 1024, 1000, batch=B, bits=32, with_bias=False)
+        x, w, o = dev(c["x"]), dev(c["w"]), out((B, 1000), torch.int32)
+        fn = lambda: api.pulp_nn_linear_out_32(32, x, None, o, w, 1024, 1000)  # noqa: E731
+        return fn, 2.0 * B * 1024 * 1000, B * (1024 + 4000) + 1024 * 1000, (x, w, o)
     if name in ("chw_to_hwc", "hwc_to_chw"):
         # the layout change a reference-style chain needs before every depthwise call: dw2's tensor
         H, C = 112, 64
@@ -124,7 +130,7 @@ def int8_peak(reps):
             "ms_per_call": round(best, 4), "TOPs": round(2.0 * n ** 3 / best / 1e9, 1)}
 
 
-def run_case(name, B, reps, pkg):
+def run_case(name, B, reps, pkg, graph=False):
     import torch
     if name == "int8_peak":
         return int8_peak(reps)
@@ -135,17 +141,34 @@ def run_case(name, B, reps, pkg):
         fn()
     api.synchronize()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev0.record()
-    for _ in range(reps):
-        fn()
-    ev1.record()
+    if graph:
+        # the calls are captured once and replayed: no host time between the kernels, which is what
+        # a caller that chains layers in a CUDA graph sees (calls shorter than ~15 us are otherwise
+        # paced by the Python/ctypes call, not by the GPU)
+        stream = torch.cuda.Stream()
+        api.set_stream(stream)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            for _ in range(reps):
+                fn()
+        api.set_stream(None)
+        g.replay()
+        torch.cuda.synchronize()
+        ev0.record()
+        g.replay()
+        ev1.record()
+    else:
+        ev0.record()
+        for _ in range(reps):
+            fn()
+        ev1.record()
     torch.cuda.synchronize()
     ms = ev0.elapsed_time(ev1) / reps
     assert api.device_status() == 0
     peak = hbm_peak()
     return {"case": name, "batch": B, "ms_per_call": round(ms, 5), "GOPs": round(ops / ms / 1e6, 1),
             "GBs": round(nbytes / ms / 1e6, 1), "hbm_frac": round(nbytes / ms / 1e6 / peak, 3),
-            "algorithmic_bytes": int(nbytes), "working_set_larger_than_L2": bool(nbytes > 126e6)}
+            "timed": "graph replay" if graph else "calls", "algorithmic_bytes": int(nbytes), "working_set_larger_than_L2": bool(nbytes > 126e6)}
 
 
 def main():
@@ -154,18 +177,22 @@ def main():
     ap.add_argument("--batch", type=int, default=0, help="0 = the configuration's own batch (1024 for MobileNet layers)")
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--all", action="store_true")
+    ap.add_argument("--graph", action="store_true", help="capture the repetitions in one CUDA graph and time its replay")
+    ap.add_argument("--split-k", type=int, default=0, help="force this many K-slices in the GEMM (0 = automatic)")
     args = ap.parse_args()
     import torch
     if not torch.cuda.is_available():
         raise SystemExit("needs a CUDA device")
     pkg = entry.load_package()
     pkg.api.set_device(0)
+    if args.split_k:
+        pkg.api.set_option(3, args.split_k)      # PULPNN_OPT_SPLIT_K
     names = [args.case]
     if args.all:
         names = list(dict.fromkeys(["c1", "c2", "c3", "c4", "c4_out32", "conv1"] + sorted(POINTWISE) + sorted(DEPTHWISE)))
     for n in names:
         B = args.batch or DEFAULT_BATCH.get(n, 1024)
-        print(json.dumps(run_case(n, B, args.reps, pkg)), flush=True)
+        print(json.dumps(run_case(n, B, args.reps, pkg, args.graph)), flush=True)
 
 
 if __name__ == "__main__":

@@ -120,6 +120,32 @@ def test_conv_first_layer_tensor_core_kernel(bits, relu, bn, gpu, restatement):
     assert api.device_status() == 0
 
 
+@pytest.mark.parametrize("bits", [32, 64])
+@pytest.mark.parametrize("relu,bn", MODES)
+def test_conv_spatial_tensor_core_kernel(bits, relu, bn, gpu, restatement):
+    """Spatial kernels on a multiple of 32 input channels take the tensor-core GEMM with the im2col
+    done by 4-D TMA boxes: every K-slab width, 64-, 128- and 256-column tiles (plain and TMA
+    stores), strides 1 and 2 in either direction, 3x3 / 5x5 / 3x1 kernels, asymmetric padding,
+    ragged filter counts, patches that hang over the image's edge, more patches than SMs."""
+    cases = [  # H, W, Cin, Cout, kernel, strides, pads (top, bottom, left, right), batch
+        (32, 32, 32, 64, (3, 3), (1, 1), (1, 1, 1, 1), 2),
+        (14, 14, 64, 128, (3, 3), (1, 1), (1, 1, 1, 1), 3),
+        (9, 13, 32, 48, (3, 3), (2, 2), (1, 1, 1, 1), 2),
+        (12, 20, 128, 256, (3, 3), (1, 1), (1, 1, 1, 1), 2),
+        (11, 10, 32, 32, (5, 5), (1, 1), (2, 2, 2, 2), 2),
+        (10, 17, 64, 80, (3, 1), (1, 2), (1, 1, 0, 0), 2),
+        (7, 7, 256, 160, (3, 3), (1, 1), (0, 2, 2, 0), 2),
+        (16, 40, 32, 64, (3, 3), (2, 1), (1, 1, 1, 1), 40),
+    ]
+    for (H, W, Cin, Cout, kernel, strides, pads, batch) in cases:
+        c = wl.conv_case(41, H, W, Cin, Cout, kernel=kernel, strides=strides, pads=pads, batch=batch, bits=bits,
+                         out_shift=12, with_bias=True, out_mult=5, relu=relu, bn=bn,
+                         k_range=(-64, 64), lam_range=(-2 ** 20, 2 ** 20))
+        want = restatement.conv(bits, c["x"], c["w"], c["k"], c["lam"], **conv_kw(c))
+        same(gpu.conv(bits, c["x"], c["w"], c["k"], c["lam"], **conv_kw(c)), want)
+    assert api.device_status() == 0
+
+
 def test_conv_against_compiled_reference(gpu, reference32):
     c = wl.conv_case(14, 17, 19, 8, 12, batch=2, bits=32, out_shift=10, with_bias=True)
     want = reference32.conv(32, c["x"], c["w"], c["k"], c["lam"], variant="HoWo", **conv_kw(c))
