@@ -113,6 +113,7 @@ struct HwcTmaParams {
   DepthwiseProblem p;
   int col_tiles, chunks, strips;   // tiles across the width, 128-channel chunks, strips down the height
   int rows_per_strip;              // output rows per strip (a multiple of the rows a group completes)
+  int imgs_per_cta;                // consecutive images one CTA works through (its ring never drains between them)
   int *status;
 };
 
@@ -262,22 +263,30 @@ depthwise_hwc3x3_tma_kernel(const __grid_constant__ CUtensorMap map_in, const __
   const int col_tile = t % g.col_tiles; t /= g.col_tiles;
   const int strip = t % g.strips; t /= g.strips;
   const int chunk = t % g.chunks;
-  const int b = t / g.chunks;
+  const int b0 = (t / g.chunks) * g.imgs_per_cta;                        // the CTA's first image
+  const int nimg = min(g.imgs_per_cta, p.B - b0);
   const int c_base = chunk * CI, ox_base = col_tile * G::WT;
   const int oyA = strip * g.rows_per_strip, oyB = min(oyA + g.rows_per_strip, p.Ho);
   const int ngroups = 1 + (oyB - oyA + G::ROWS_OUT - 1) / G::ROWS_OUT;    // group 0 only opens accumulators
+  const int total = nimg * ngroups;                                      // groups of rows over all its images
   const int in_x = S * ox_base - 1;                                      // first staged input column
   const int in_y0 = S == 1 ? oyA - 2 : 2 * oyA - 4;                      // first staged row of group 0
 
+  // thread 0: the groups are numbered through the CTA's images; group n uses slot n % RING
+  int issued = 0, next_img = 0, next_j = 0;
+  auto issue_next = [&]() {
+    const int slot = issued % RING;
+    mbar_arrive_expect_tx(&full[slot], (uint32_t)G::GROUP_BYTES);
+    tma_load_4d(sm + slot * G::GROUP_STRIDE, &map_in, &full[slot], c_base, in_x, in_y0 + next_j * G::ROWS_IN, b0 + next_img);
+    issued++;
+    if (++next_j == ngroups) { next_j = 0; next_img++; }
+  };
   if (tid == 0) {
     for (int s = 0; s < RING; s++) mbar_init(&full[s], 1);
     *abort_flag = 0;
     mbar_fence_init();
-    const int first = ngroups < RING ? ngroups : RING;
-    for (int j = 0; j < first; j++) {
-      mbar_arrive_expect_tx(&full[j], (uint32_t)G::GROUP_BYTES);
-      tma_load_4d(sm + j * G::GROUP_STRIDE, &map_in, &full[j], c_base, in_x, in_y0 + j * G::ROWS_IN, b);
-    }
+    const int first = total < RING ? total : RING;
+    for (int j = 0; j < first; j++) issue_next();
   }
 
   // the thread's four channels: weights as [w0,w1,w2,0] and [0,w0,w1,w2] per filter row, and the
@@ -326,13 +335,7 @@ depthwise_hwc3x3_tma_kernel(const __grid_constant__ CUtensorMap map_in, const __
   // index inside the warp instead: one load instruction then touches NSUB different pixels mod 4.
   const Rot rot = make_rot<CI>(sub);
   bool dead = false;             // a wait ran out: keep pace at the barriers, do no more work
-  int issued = ngroups < RING ? ngroups : RING;      // thread 0: groups whose load has been issued
-  int consumed = 0;                                  // groups whose data this thread has seen land
-  auto refill = [&](int j_next, int grp_) {          // thread 0 only
-    mbar_arrive_expect_tx(&full[grp_], (uint32_t)G::GROUP_BYTES);
-    tma_load_4d(sm + grp_ * G::GROUP_STRIDE, &map_in, &full[grp_], c_base, in_x, in_y0 + j_next * G::ROWS_IN, b);
-    issued = j_next + 1;
-  };
+  int consumed = 0;              // groups whose data this thread has seen land
 
   // Accumulators. Stride 1: three sets, one per output row in flight (an input row is filter row 2
   // of one, row 1 of the next and row 0 of the one after). Stride 2: one set.
@@ -344,95 +347,91 @@ depthwise_hwc3x3_tma_kernel(const __grid_constant__ CUtensorMap map_in, const __
 #pragma unroll
       for (int j = 0; j < 4; j++) acc[a][i][j] = 0;
 
-  // ---- group 0: the rows above the strip's first output row only open accumulators ---------------
-  if (!mbar_wait(&full[0], 0, abort_flag, g.status, ST_HWC_TMA)) dead = true;
-  if (!dead) {
-    consumed = 1;
-    uint32_t ra[4];
-#pragma unroll
-    for (int i = 0; i < 4; i++) ra[i] = in_thr + CI + rot.off[i];
-    if constexpr (S == 1) {
-      unsigned cur[6]; Win1 w;
-      load_row1<CI>(in_thr, ra, 1 * G::IN_PITCH, cur);          // input row oyA-1
-      windows1(cur, rot, w);
-      load_row1<CI>(in_thr, ra, 2 * G::IN_PITCH, cur);          // input row oyA
-      mac1<false, false>(w, wa, wb, init, acc[0], acc[0], acc[0]);
-      windows1(cur, rot, w);
-      mac1<false, true>(w, wa, wb, init, acc[0], acc[0], acc[S == 1 ? 1 : 0]);
-    } else {
-      unsigned cur[9]; Win2 w;
-      load_row2<CI>(in_thr, ra, 3 * G::IN_PITCH, cur);          // input row 2*oyA-1
-      windows2(cur, rot, w);
-      mac2<true>(w, wa[0], wb[0], init, acc[0]);
-    }
-  }
-  __syncthreads();                                              // group 0 has been read by everyone
-  if (tid == 0 && !dead && RING < ngroups) refill(RING, 0);
-
-  int grp = 0, half = 0;
+  int grp = 0, half = 0, j = 0, img = 0;
   uint32_t parity = 0;
-  for (int j = 1; j < ngroups; j++) {
-    if (++grp == RING) { grp = 0; parity ^= 1; }
+  for (int n = 0; n < total; n++) {
     if (!dead && !mbar_wait(&full[grp], parity, abort_flag, g.status, ST_HWC_TMA)) dead = true;
     if (!dead) {
-      consumed = j + 1;
+      consumed = n + 1;
       const uint32_t ia = in_thr + grp * G::GROUP_STRIDE, oa = out_thr + half * G::TILE_STRIDE;
-      const int rows_here = oyB - (oyA + (j - 1) * G::ROWS_OUT);     // output rows this group still owes
       uint32_t ra[4];
 #pragma unroll
       for (int i = 0; i < 4; i++) ra[i] = ia + CI + rot.off[i];
-      if constexpr (S == 1) {
-        constexpr int A1 = S == 1 ? 1 : 0, A2 = S == 1 ? 2 : 0;
-        unsigned cur[6]; Win1 w;
-        load_row1<CI>(ia, ra, 0, cur);
-        windows1(cur, rot, w);
-        if (rows_here > 1) load_row1<CI>(ia, ra, G::IN_PITCH, cur);
-        mac1<true, true>(w, wa, wb, init, acc[0], acc[A1], acc[A2]);
-        finalize_row<MODE, CI>(acc[0], q, e, k32, oa);
-        if (rows_here > 1) {            // the strip's last group may end before its third row
+      if (j == 0) {
+        // ---- an image's group 0: the rows above the strip's first output row only open accumulators
+        if constexpr (S == 1) {
+          unsigned cur[6]; Win1 w;
+          load_row1<CI>(ia, ra, 1 * G::IN_PITCH, cur);          // input row oyA-1
           windows1(cur, rot, w);
-          if (rows_here > 2) load_row1<CI>(ia, ra, 2 * G::IN_PITCH, cur);
-          mac1<true, true>(w, wa, wb, init, acc[A1], acc[A2], acc[0]);
-          finalize_row<MODE, CI>(acc[A1], q, e, k32, oa + G::OUT_PITCH);
-          if (rows_here > 2) {
-            windows1(cur, rot, w);
-            mac1<true, true>(w, wa, wb, init, acc[A2], acc[0], acc[A1]);
-            finalize_row<MODE, CI>(acc[A2], q, e, k32, oa + 2 * G::OUT_PITCH);
-          }
+          load_row1<CI>(ia, ra, 2 * G::IN_PITCH, cur);          // input row oyA
+          mac1<false, false>(w, wa, wb, init, acc[0], acc[0], acc[0]);
+          windows1(cur, rot, w);
+          mac1<false, true>(w, wa, wb, init, acc[0], acc[0], acc[S == 1 ? 1 : 0]);
+        } else {
+          unsigned cur[9]; Win2 w;
+          load_row2<CI>(ia, ra, 3 * G::IN_PITCH, cur);          // input row 2*oyA-1
+          windows2(cur, rot, w);
+          mac2<true>(w, wa[0], wb[0], init, acc[0]);
         }
       } else {
-        unsigned cur[9]; Win2 w;
-        load_row2<CI>(ia, ra, 0, cur);                          // input row 2m
-        windows2(cur, rot, w);
-        load_row2<CI>(ia, ra, G::IN_PITCH, cur);                // 2m+1: closes row m, opens m+1
-        mac2<false>(w, wa[1], wb[1], init, acc[0]);
-        windows2(cur, rot, w);
-        if (rows_here > 1) load_row2<CI>(ia, ra, 2 * G::IN_PITCH, cur);
-        mac2<false>(w, wa[2], wb[2], init, acc[0]);
-        finalize_row<MODE, CI>(acc[0], q, e, k32, oa);
-        if (rows_here > 1) {
-          mac2<true>(w, wa[0], wb[0], init, acc[0]);
+        const int rows_here = oyB - (oyA + (j - 1) * G::ROWS_OUT);     // output rows this group still owes
+        if constexpr (S == 1) {
+          constexpr int A1 = S == 1 ? 1 : 0, A2 = S == 1 ? 2 : 0;
+          unsigned cur[6]; Win1 w;
+          load_row1<CI>(ia, ra, 0, cur);
+          windows1(cur, rot, w);
+          if (rows_here > 1) load_row1<CI>(ia, ra, G::IN_PITCH, cur);
+          mac1<true, true>(w, wa, wb, init, acc[0], acc[A1], acc[A2]);
+          finalize_row<MODE, CI>(acc[0], q, e, k32, oa);
+          if (rows_here > 1) {            // the strip's last group may end before its third row
+            windows1(cur, rot, w);
+            if (rows_here > 2) load_row1<CI>(ia, ra, 2 * G::IN_PITCH, cur);
+            mac1<true, true>(w, wa, wb, init, acc[A1], acc[A2], acc[0]);
+            finalize_row<MODE, CI>(acc[A1], q, e, k32, oa + G::OUT_PITCH);
+            if (rows_here > 2) {
+              windows1(cur, rot, w);
+              mac1<true, true>(w, wa, wb, init, acc[A2], acc[0], acc[A1]);
+              finalize_row<MODE, CI>(acc[A2], q, e, k32, oa + 2 * G::OUT_PITCH);
+            }
+          }
+        } else {
+          unsigned cur[9]; Win2 w;
+          load_row2<CI>(ia, ra, 0, cur);                          // input row 2m
           windows2(cur, rot, w);
-          load_row2<CI>(ia, ra, 3 * G::IN_PITCH, cur);
+          load_row2<CI>(ia, ra, G::IN_PITCH, cur);                // 2m+1: closes row m, opens m+1
           mac2<false>(w, wa[1], wb[1], init, acc[0]);
           windows2(cur, rot, w);
+          if (rows_here > 1) load_row2<CI>(ia, ra, 2 * G::IN_PITCH, cur);
           mac2<false>(w, wa[2], wb[2], init, acc[0]);
-          finalize_row<MODE, CI>(acc[0], q, e, k32, oa + G::OUT_PITCH);
-          mac2<true>(w, wa[0], wb[0], init, acc[0]);
+          finalize_row<MODE, CI>(acc[0], q, e, k32, oa);
+          if (rows_here > 1) {
+            mac2<true>(w, wa[0], wb[0], init, acc[0]);
+            windows2(cur, rot, w);
+            load_row2<CI>(ia, ra, 3 * G::IN_PITCH, cur);
+            mac2<false>(w, wa[1], wb[1], init, acc[0]);
+            windows2(cur, rot, w);
+            mac2<false>(w, wa[2], wb[2], init, acc[0]);
+            finalize_row<MODE, CI>(acc[0], q, e, k32, oa + G::OUT_PITCH);
+            mac2<true>(w, wa[0], wb[0], init, acc[0]);
+          }
         }
+        fence_proxy_async();            // the tile words written above, before the TMA store reads them
       }
-      fence_proxy_async();            // the tile words written above, before the TMA store reads them
     }
     // the store issued two groups ago read the half that the NEXT group will write
     if (tid == 0) bulk_wait_read_all();
-    __syncthreads();
+    __syncthreads();                    // the group has been read, the tile written, by everyone
     if (tid == 0 && !dead) {
-      tma_store_4d(&map_out, sm + RING * G::GROUP_STRIDE + half * G::TILE_STRIDE, c_base, ox_base,
-                   oyA + (j - 1) * G::ROWS_OUT, b);
-      bulk_commit();
-      if (j + RING < ngroups) refill(j + RING, grp);
+      if (j > 0) {
+        tma_store_4d(&map_out, sm + RING * G::GROUP_STRIDE + half * G::TILE_STRIDE, c_base, ox_base,
+                     oyA + (j - 1) * G::ROWS_OUT, b0 + img);
+        bulk_commit();
+      }
+      if (issued < total) issue_next();      // group n + RING goes into the slot just read
     }
-    half ^= 1;
+    if (j > 0) half ^= 1;
+    if (++j == ngroups) { j = 0; img++; }
+    if (++grp == RING) { grp = 0; parity ^= 1; }
   }
   if (tid == 0) {
     bulk_wait_all();
@@ -765,7 +764,18 @@ bool launch_geo(Context &c, const DepthwiseProblem &p)
   rows = (rows + G::ROWS_OUT - 1) / G::ROWS_OUT * G::ROWS_OUT;
   g.rows_per_strip = rows;
   g.strips = (p.Ho + rows - 1) / rows;
-  const long long total = columns * g.strips;
+  // More whole-image columns than CTAs fit on the GPU at once: a CTA takes several consecutive
+  // images, enough for one full wave, and its ring of row groups runs on from image to image.
+  g.imgs_per_cta = 1;
+  const long long per_image = (long long)g.chunks * g.col_tiles;
+  const long long slots = (long long)(c.sm_count > 0 ? c.sm_count : 148) * resident;
+  if (g.strips == 1 && columns > slots && per_image <= slots) {
+    const long long bgroups_max = slots / per_image;
+    long long imgs = (p.B + bgroups_max - 1) / bgroups_max;
+    if (imgs > 16) imgs = 16;
+    g.imgs_per_cta = (int)imgs;
+  }
+  const long long total = (long long)((p.B + g.imgs_per_cta - 1) / g.imgs_per_cta) * per_image * g.strips;
   if (total > 0x7fffffffLL) { set_error(PULPNN_ERR_UNSUPPORTED, "depthwise: too many tiles"); return false; }
   CUtensorMap map_in, map_out;
   if (!encode_4d(&map_in, p.in, p.C, p.W, p.H, p.B, CI, G::WBOX, G::ROWS_IN)) return false;

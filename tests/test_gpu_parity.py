@@ -197,6 +197,22 @@ def test_pointwise_against_compiled_reference(gpu, reference64):
     same(gpu.pointwise(64, c["x"], c["w"], c["k"], c["lam"], **pw_kw(c)), want)
 
 
+@pytest.mark.parametrize("bits", [32, 64])
+@pytest.mark.parametrize("relu,bn", MODES)
+def test_pointwise_short_reduction_folded_rows(bits, relu, bn, gpu, restatement):
+    """Many pixels with at most 64 input and 128 output channels: the GEMM folds 2, 4 or 8 pixels
+    into one row against a block-diagonal copy of the weights. Filter counts that are not a power
+    of two (the per-channel parameters wrap around inside a folded row), a pixel count that is odd
+    (no folding), and every requantisation mode."""
+    for (H, W, cin, cout, batch) in ((112, 112, 32, 64, 16), (56, 56, 64, 128, 32), (112, 112, 16, 32, 25),
+                                     (112, 112, 32, 48, 16), (113, 113, 32, 64, 13), (112, 112, 64, 16, 16)):
+        c = wl.pointwise_case(25, H, W, cin, cout, batch=batch, bits=bits, out_shift=9, with_bias=True,
+                              out_mult=3, relu=relu, bn=bn)
+        want = restatement.pointwise(bits, c["x"], c["w"], c["k"], c["lam"], **pw_kw(c))
+        same(gpu.pointwise(bits, c["x"], c["w"], c["k"], c["lam"], **pw_kw(c)), want)
+    assert api.device_status() == 0
+
+
 def test_pointwise_many_tiles_property(gpu, restatement):
     """Full config-2 batch: too large for the CPU checker in seconds, so check a size-independent
     property instead: the batched result equals the per-image results (images are independent),
