@@ -125,6 +125,16 @@ int  pulpnn_get_option(int option);
  *  pulp_nn_depthwise_generic        pulp_nn_kernels.h:282   CHW in, HWC out
  *  pulp_nn_depthwise_generic_less_4_weights  :311           same, for kernels of fewer than 4 taps
  *                                                           (accepts any number of taps)
+ *  pulp_nn_depthwise_3x3_s1         pulp_nn_kernels.h:340   CHW in (R x C), HWC out (R-2 x C): 3x3,
+ *                                                           stride 1, no vertical padding, no bias.
+ *                                                           Accepted for p_l = p_r = 1 and even C,
+ *                                                           where the reference is a zero-padded
+ *                                                           convolution; memory_chan is ignored
+ *  pulp_nn_matmul                   pulp_nn_kernels.h:248   the convolutions' inner kernel: two
+ *                                                           im2col columns (pInBuffer, pInBuffer +
+ *                                                           num_col_im2col) x ch_out filters into
+ *                                                           pOut and pOut2; returns pOut + 2*ch_out.
+ *                                                           The batch setting does not apply
  *  pulp_nn_linear                   pulp_nn_kernels.h:224   uint8 output, requantised
  *  pulp_nn_linear_out_32            pulp_nn_kernels.h:239   raw int32 output; bias is read as int32[]
  *  pulp_nn_maxpool                  pulp_nn_kernels.h:264   Im_in is left intact unless
@@ -145,6 +155,15 @@ int  pulpnn_get_option(int option);
   void pulp_nn_depthwise_generic##SFX(PULPNN_DW_PARAMS(BN_T));                                \
   void pulp_nn_depthwise_generic_less_4_weights##SFX(PULPNN_DW_PARAMS(BN_T));                 \
   void pulpnn_depthwise_hwc##SFX(PULPNN_DW_PARAMS(BN_T));                                     \
+  void pulp_nn_depthwise_3x3_s1##SFX(uint8_t *In_Img, uint8_t *Out_Img, int R, int C, int CH,  \
+                                     int p_l, int p_r, int8_t *Kernel, int8_t out_shift,      \
+                                     uint16_t out_mult, BN_T *kappa, BN_T *lambda,            \
+                                     int flag_relu, int flag_batch_norm,                      \
+                                     unsigned int *memory_chan);                              \
+  uint8_t *pulp_nn_matmul##SFX(const int8_t *pWeight, uint8_t *pInBuffer, uint16_t ch_out,    \
+                               uint16_t num_col_im2col, uint16_t out_shift, uint16_t out_mult,\
+                               BN_T *k, BN_T *lambda, const int8_t *bias, uint8_t *pOut,      \
+                               uint8_t *pOut2, int flag_relu, int flag_batch_norm);           \
   void pulp_nn_linear##SFX(uint8_t *pInBuffer, int8_t *bias, uint8_t *pOutBuffer,             \
                            int8_t *pWeights, BN_T *k, BN_T *lambda, uint16_t out_mult,        \
                            int8_t out_shift, uint16_t dim_vec, uint16_t num_o_neurons,        \

@@ -112,6 +112,25 @@ class Restatement:
                                   pt, pb, pl, pr, sx, sy, relu, bn, int(in_is_hwc), B, _ptr(acc))
         return (out, acc) if want_acc else out
 
+    def depthwise_3x3_s1(self, bits, x, w, k, lam, *, out_mult=1, out_shift=0, relu=1, bn=1, p_l=1, p_r=1):
+        """32bit/src/pulp_nn_depthwise_3x3_s1.c:28-210 inside its defined domain (p_l = p_r = 1, even
+        C): the zero-padded 3x3 stride-1 depthwise convolution without vertical padding and without
+        bias; its flag test is the convolutions' (flag_relu == 1, :120-135), not the generic
+        depthwise kernel's."""
+        assert p_l == 1 and p_r == 1 and x.shape[3] % 2 == 0
+        B, CH, R, Cw = x.shape
+        dw_relu = 1 if (relu == 1 or (relu and bn)) else 0     # relu = 2 without bn means "no requantisation"
+        return self.depthwise(bits, x, w, k, lam, bias=None, out_mult=out_mult, out_shift=out_shift,
+                              out_hw=(R - 2, Cw), kernel=(3, 3), pads=(0, 0, 1, 1), strides=(1, 1),
+                              relu=dw_relu, bn=bn)
+
+    def matmul(self, bits, x2, w, k, lam, *, bias=None, out_mult=1, out_shift=0, relu=1, bn=1):
+        """32bit/src/pulp_nn_matmul.c:27-298: two im2col columns against all filters = a 1x1
+        convolution over two pixels."""
+        K = x2.shape[1]
+        return self.pointwise(bits, x2.reshape(1, 1, 2, K), w, k, lam, bias=bias, out_mult=out_mult,
+                              out_shift=out_shift, relu=relu, bn=bn).reshape(2, -1)
+
     def linear(self, bits, x, w, k, lam, *, bias=None, out_mult=1, out_shift=0, relu=1, bn=1):
         B, K = x.shape
         N = w.shape[0]
@@ -171,7 +190,7 @@ class CompiledReference:
         self.threads = threads
         self.lib = C.CDLL(_REF_SO[bits])
         for name in ("refdrv_conv", "refdrv_depthwise", "refdrv_linear", "refdrv_maxpool",
-                     "refdrv_avgpool", "refdrv_add"):
+                     "refdrv_avgpool", "refdrv_add", "refdrv_depthwise_3x3_s1", "refdrv_matmul"):
             getattr(self.lib, name).restype = C.c_double
         self.lib.refdrv_init.argtypes = [C.c_size_t]
         assert self.lib.refdrv_bn_bits() == bits
@@ -233,6 +252,29 @@ class CompiledReference:
                                              Wo, Ho, kx, ky, pt, pb, pl, pr, sx, sy, relu, bn,
                                              int(in_is_hwc), B, self.threads, C.byref(glue)))
         self.last_glue_seconds = glue.value
+        return out
+
+    def depthwise_3x3_s1(self, bits, x, w, k, lam, *, out_mult=1, out_shift=0, relu=1, bn=1, p_l=1, p_r=1):
+        """pulp_nn_depthwise_3x3_s1: x [B][CH][R][C] -> [B][R-2][C][CH]."""
+        assert bits == self.bits
+        B, CH, R, Cw = x.shape
+        k, lam = _bn_arrays(bits, k, lam)
+        out = np.empty((B, R - 2, Cw, CH), np.uint8)
+        self._done(self.lib.refdrv_depthwise_3x3_s1(_ptr(x), _ptr(out), R, Cw, CH, p_l, p_r, _ptr(w), out_shift,
+                                                    out_mult, _ptr(k), _ptr(lam), relu, bn, B, self.threads))
+        return out
+
+    def matmul(self, bits, x2, w, k, lam, *, bias=None, out_mult=1, out_shift=0, relu=1, bn=1):
+        """pulp_nn_matmul: x2 [2][K] -> [2][ch_out]; checks the returned pointer (pOut + 2*ch_out)."""
+        assert bits == self.bits
+        K = x2.shape[1]
+        N = w.shape[0]
+        k, lam = _bn_arrays(bits, k, lam)
+        out = np.empty((2, N), np.uint8)
+        off = C.c_long(0)
+        self._done(self.lib.refdrv_matmul(_ptr(w), _ptr(x2), N, K, out_shift, out_mult, _ptr(k), _ptr(lam),
+                                          _ptr(bias), _ptr(out), relu, bn, C.byref(off)))
+        assert off.value == 2 * N
         return out
 
     def linear(self, bits, x, w, k, lam, *, bias=None, out_mult=1, out_shift=0, relu=1, bn=1):

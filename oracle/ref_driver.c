@@ -265,6 +265,67 @@ double refdrv_depthwise(int variant, const uint8_t *in, const int8_t *bias, uint
   return dt;
 }
 
+/* ================= depthwise 3x3 stride 1, matmul ========================== */
+typedef struct {
+  const uint8_t *in; uint8_t *out; const int8_t *w; bn_t *k; bn_t *lambda;
+  int R, C, CH, p_l, p_r, out_shift, out_mult, relu, bn;
+  size_t in_sz, out_sz;
+  uint8_t **s_in, **s_out;
+} dw3_ctx;
+
+static void dw3_image(void *vctx, int img, int tid)
+{
+  dw3_ctx *c = (dw3_ctx *)vctx;
+  memcpy(c->s_in[tid], c->in + (size_t)img * c->in_sz, c->in_sz);
+  pulp_nn_depthwise_3x3_s1(c->s_in[tid], c->s_out[tid], c->R, c->C, c->CH, c->p_l, c->p_r,
+                           (int8_t *)c->w, (int8_t)c->out_shift, (uint16_t)c->out_mult, c->k,
+                           c->lambda, c->relu, c->bn, NULL);
+  memcpy(c->out + (size_t)img * c->out_sz, c->s_out[tid], c->out_sz);
+}
+
+/* in: [batch][CH][R][C]; out: [batch][R-2][C][CH] */
+double refdrv_depthwise_3x3_s1(const uint8_t *in, uint8_t *out, int R, int C, int CH, int p_l,
+                               int p_r, const int8_t *w, int out_shift, int out_mult, void *k,
+                               void *lambda, int relu, int bn, int batch, int threads)
+{
+  dw3_ctx c;
+  memset(&c, 0, sizeof c);
+  c.in = in; c.out = out; c.w = w; c.k = (bn_t *)k; c.lambda = (bn_t *)lambda;
+  c.R = R; c.C = C; c.CH = CH; c.p_l = p_l; c.p_r = p_r; c.out_shift = out_shift;
+  c.out_mult = out_mult; c.relu = relu; c.bn = bn;
+  c.in_sz = (size_t)R * C * CH;
+  c.out_sz = (size_t)(R - 2) * C * CH;
+  threads = clamp_threads(threads, batch);
+  uint8_t *s_in[256], *s_out[256];
+  bump_t b = { 0 };
+  for (int t = 0; t < threads; t++) {
+    s_in[t] = bump(&b, c.in_sz); s_out[t] = bump(&b, c.out_sz);
+    if (!s_in[t] || !s_out[t]) return -1.0;
+  }
+  c.s_in = s_in; c.s_out = s_out;
+  return run_batch(dw3_image, &c, batch, threads);
+}
+
+/* in2: the two im2col columns [2][K]; out: [2][ch_out] (pOut, pOut2 = pOut + ch_out).
+ * *ret_offset receives (returned pointer - pOut). */
+double refdrv_matmul(const int8_t *w, const uint8_t *in2, int ch_out, int K, int out_shift,
+                     int out_mult, void *k, void *lambda, const int8_t *bias, uint8_t *out,
+                     int relu, int bn, long *ret_offset)
+{
+  bump_t b = { 0 };
+  uint8_t *s_in = bump(&b, 2 * (size_t)K), *s_out = bump(&b, 2 * (size_t)ch_out);
+  if (!s_in || !s_out) return -1.0;
+  memcpy(s_in, in2, 2 * (size_t)K);
+  double t0 = now_s();
+  uint8_t *r = pulp_nn_matmul(w, s_in, (uint16_t)ch_out, (uint16_t)K, (uint16_t)out_shift,
+                              (uint16_t)out_mult, (bn_t *)k, (bn_t *)lambda, bias, s_out,
+                              s_out + ch_out, relu, bn);
+  double dt = now_s() - t0;
+  memcpy(out, s_out, 2 * (size_t)ch_out);
+  if (ret_offset) *ret_offset = (long)(r - s_out);
+  return dt;
+}
+
 /* ============================== linear ==================================== */
 typedef struct {
   const uint8_t *in; const int8_t *bias; uint8_t *out8; int32_t *out32; const int8_t *w;

@@ -155,6 +155,28 @@ pulp_nn_depthwise_generic_less_4_weights = _dw_like("pulp_nn_depthwise_generic_l
 pulpnn_depthwise_hwc = _dw_like("pulpnn_depthwise_hwc")
 
 
+def pulp_nn_depthwise_3x3_s1(bits, In_Img, Out_Img, R, C_, CH, p_l, p_r, Kernel, out_shift, out_mult, kappa,
+                             lambda_, flag_relu, flag_batch_norm, memory_chan=None):
+    """32bit/include/pulp_nn_kernels.h:340: CHW in (R x C), HWC out (R-2 x C), 3x3, stride 1."""
+    _fn("pulp_nn_depthwise_3x3_s1", bits)(_ptr(In_Img), _ptr(Out_Img), C.c_int(R), C.c_int(C_), C.c_int(CH),
+                                          C.c_int(p_l), C.c_int(p_r), _ptr(Kernel), C.c_int8(out_shift),
+                                          C.c_uint16(out_mult), _ptr(kappa), _ptr(lambda_), C.c_int(flag_relu),
+                                          C.c_int(flag_batch_norm), _ptr(memory_chan))
+    _check()
+
+
+def pulp_nn_matmul(bits, pWeight, pInBuffer, ch_out, num_col_im2col, out_shift, out_mult, k, lambda_, bias,
+                   pOut, pOut2, flag_relu, flag_batch_norm):
+    """32bit/include/pulp_nn_kernels.h:248. Returns the address the reference returns: pOut + 2*ch_out."""
+    f = getattr(_lib.load_library(), "pulp_nn_matmul" + _sfx(bits))
+    f.restype = C.c_void_p
+    r = f(_ptr(pWeight), _ptr(pInBuffer), C.c_uint16(ch_out), C.c_uint16(num_col_im2col), C.c_uint16(out_shift),
+          C.c_uint16(out_mult), _ptr(k), _ptr(lambda_), _ptr(bias), _ptr(pOut), _ptr(pOut2), C.c_int(flag_relu),
+          C.c_int(flag_batch_norm))
+    _check()
+    return r
+
+
 def pulp_nn_linear(bits, pInBuffer, bias, pOutBuffer, pWeights, k, lambda_, out_mult, out_shift,
                    dim_vec, num_o_neurons, flag_relu, flag_batch_norm):
     _fn("pulp_nn_linear", bits)(_ptr(pInBuffer), _ptr(bias), _ptr(pOutBuffer), _ptr(pWeights),

@@ -10,16 +10,18 @@
 // bytes of filter row fy followed by zeros, chunk 3 = zeros, and the filters are re-packed the same
 // way once per CTA. So K = 64, two MMAs of K = 32 per tile of 128 pixels x BN output channels.
 //
-// Roles in a CTA (25 warps, persistent over units = 4 consecutive output rows of one image):
+// Roles in a CTA (15 warps, persistent over units = 4 consecutive output rows of one image):
 //   warp 0, one lane   TMA: the 3*SY+3 input rows a unit needs, as one 4-D box of the input seen
 //                      as [B][H][pieces of a row][32 or 16 bytes]; rows above and below the image
 //                      are zeros
 //   warps 1..4         builders: thread = output column. Per input row three aligned words, one
 //                      funnel shift each and a mask (columns left/right of the image) give the
 //                      window's 9 bytes; 16-byte stores put them into the four tiles of the unit
-//   warps 5..8         one lane each issues the two tcgen05.mma of every fourth tile
-//   warps 9..24        epilogue, four groups that take tiles in turn: tcgen05.ld (lane = pixel),
-//                      bias, requantisation, one 32-byte store per 32 output channels
+//   warps 5..6         one lane each issues the two tcgen05.mma of every other tile
+//   warps 7..14        epilogue, two groups that take tiles in turn: tcgen05.ld (lane = pixel),
+//                      bias, requantisation (k and lambda live in registers for 32 filters with
+//                      32-bit batch normalisation), one 32-byte store per 32 output channels
+// More MMA warps or epilogue groups were measured and gained nothing.
 // Every mbarrier wait is bounded (sm100_primitives.cuh).
 #include "internal.cuh"
 #include "sm100_primitives.cuh"

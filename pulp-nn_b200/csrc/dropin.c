@@ -33,6 +33,20 @@ void pulp_nn_pointwise_Co_parallel(PULPNN_CONV_PARAMS(BN_T)) { SFX(pulp_nn_point
 void pulp_nn_depthwise_generic(PULPNN_DW_PARAMS(BN_T)) { SFX(pulp_nn_depthwise_generic)(DW_ARGS); }
 void pulp_nn_depthwise_generic_less_4_weights(PULPNN_DW_PARAMS(BN_T)) { SFX(pulp_nn_depthwise_generic_less_4_weights)(DW_ARGS); }
 void pulpnn_depthwise_hwc(PULPNN_DW_PARAMS(BN_T)) { SFX(pulpnn_depthwise_hwc)(DW_ARGS); }
+void pulp_nn_depthwise_3x3_s1(uint8_t *In_Img, uint8_t *Out_Img, int R, int C, int CH, int p_l, int p_r,
+                              int8_t *Kernel, int8_t out_shift, uint16_t out_mult, BN_T *kappa, BN_T *lambda,
+                              int flag_relu, int flag_batch_norm, unsigned int *memory_chan)
+{
+  SFX(pulp_nn_depthwise_3x3_s1)(In_Img, Out_Img, R, C, CH, p_l, p_r, Kernel, out_shift, out_mult, kappa, lambda,
+                                flag_relu, flag_batch_norm, memory_chan);
+}
+uint8_t *pulp_nn_matmul(const int8_t *pWeight, uint8_t *pInBuffer, uint16_t ch_out, uint16_t num_col_im2col,
+                        uint16_t out_shift, uint16_t out_mult, BN_T *k, BN_T *lambda, const int8_t *bias,
+                        uint8_t *pOut, uint8_t *pOut2, int flag_relu, int flag_batch_norm)
+{
+  return SFX(pulp_nn_matmul)(pWeight, pInBuffer, ch_out, num_col_im2col, out_shift, out_mult, k, lambda, bias,
+                             pOut, pOut2, flag_relu, flag_batch_norm);
+}
 void pulp_nn_linear(uint8_t *pInBuffer, int8_t *bias, uint8_t *pOutBuffer, int8_t *pWeights, BN_T *k,
                     BN_T *lambda, uint16_t out_mult, int8_t out_shift, uint16_t dim_vec,
                     uint16_t num_o_neurons, int flag_relu, int flag_batch_norm)

@@ -180,6 +180,99 @@ void depthwise_entry(const char *who, bool in_is_hwc, bool need_four_taps, const
   st.finish();
 }
 
+// ---- pulp_nn_depthwise_3x3_s1 ------------------------------------------------------------------
+// 32bit/src/pulp_nn_depthwise_3x3_s1.c:28-210: CHW input of R rows x C columns, 3x3 filter, stride
+// 1, NO vertical padding (rows 0 .. R-3 are produced, :103), HWC output of R-2 rows x C columns,
+// no bias. Left and right columns are padded only when p_l / p_r are set (:105,196). The function
+// equals a zero-padded convolution only for p_l = p_r = 1 and even C: without p_l the row loop
+// starts at column 0 with the window of column 1 and runs two columns into the next row, and an
+// odd C makes the two-column loop (:140) write one pixel past the row. Such calls are rejected.
+template <typename BN_T>
+void depthwise_3x3_s1_entry(const uint8_t *in, uint8_t *out, int R, int C, int CH, int p_l, int p_r,
+                            const int8_t *w, int out_shift, int out_mult, BN_T *k, BN_T *lambda,
+                            int flag_relu, int flag_bn)
+{
+  const char *who = "pulp_nn_depthwise_3x3_s1";
+  Context &c = ctx();
+  if (!begin(c, who)) return;
+  REQUIRE(in && out && w, PULPNN_ERR_INVALID_ARG, "%s: NULL input, output or weight pointer", who);
+  REQUIRE(R >= 3 && C >= 2 && CH > 0 && R <= 65535 && C <= 65535 && CH <= 65535, PULPNN_ERR_INVALID_ARG,
+          "%s: needs 3 <= R, 2 <= C, 1 <= CH, all at most 65535", who);
+  REQUIRE(p_l == 1 && p_r == 1 && (C & 1) == 0, PULPNN_ERR_UNSUPPORTED,
+          "%s: only p_l = p_r = 1 with an even C is a zero-padded convolution in the reference", who);
+  const int mode = conv_mode<BN_T>(flag_relu, flag_bn);
+  if (!check_shift(mode, out_shift, who)) return;
+  REQUIRE(mode < EPI_BN32 || (k && lambda), PULPNN_ERR_INVALID_ARG, "%s: batch-norm mode needs kappa and lambda", who);
+  Stager st(c);
+  DepthwiseProblem p;
+  p.in = static_cast<const uint8_t *>(st.in(in, (size_t)c.batch * R * C * CH));
+  p.w = static_cast<const int8_t *>(st.in(w, (size_t)CH * 9));
+  p.out = static_cast<uint8_t *>(st.out(out, (size_t)c.batch * (R - 2) * C * CH));
+  p.epi.bias = nullptr;
+  p.epi.k = mode >= EPI_BN32 ? st.in(k, sizeof(BN_T) * CH) : nullptr;
+  p.epi.lambda = mode >= EPI_BN32 ? st.in(lambda, sizeof(BN_T) * CH) : nullptr;
+  if (!st.ok()) return;
+  p.epi.mode = mode;
+  p.epi.out_mult = (int)(int16_t)(uint16_t)out_mult;
+  p.epi.shift = out_shift;
+  p.B = c.batch; p.H = R; p.W = C; p.C = CH; p.Ho = R - 2; p.Wo = C; p.ky = 3; p.kx = 3;
+  p.pt = 0; p.pl = 1; p.sy = 1; p.sx = 1; p.in_is_hwc = false;
+  if (!launch_depthwise(c, p)) return;
+  st.finish();
+}
+
+// ---- pulp_nn_matmul --------------------------------------------------------------------------
+// The inner kernel of the reference's convolutions (32bit/src/pulp_nn_matmul.c:27-298): the two
+// im2col columns pInBuffer[0 .. K) and pInBuffer[K .. 2K) (:55-56) against all ch_out filters,
+// results to pOut and pOut2, the same three requantisation modes (:144-216). Two rows of the GEMM
+// that serves the convolutions; the batch setting does not apply.
+template <typename BN_T>
+void matmul_entry(const int8_t *w, const uint8_t *in, int ch_out, int K, int out_shift, int out_mult,
+                  BN_T *k, BN_T *lambda, const int8_t *bias, uint8_t *out, uint8_t *out2, int flag_relu,
+                  int flag_bn)
+{
+  const char *who = "pulp_nn_matmul";
+  Context &c = ctx();
+  if (!begin(c, who)) return;
+  REQUIRE(in && out && out2 && w, PULPNN_ERR_INVALID_ARG, "%s: NULL input, output or weight pointer", who);
+  REQUIRE(ch_out > 0 && K > 0, PULPNN_ERR_INVALID_ARG, "%s: zero dimension", who);
+  const int mode = conv_mode<BN_T>(flag_relu, flag_bn);
+  if (!check_shift(mode, out_shift, who)) return;
+  REQUIRE(mode < EPI_BN32 || (k && lambda), PULPNN_ERR_INVALID_ARG, "%s: batch-norm mode needs k and lambda", who);
+  Stager st(c);
+  ConvProblem p;
+  const uint8_t *din = static_cast<const uint8_t *>(st.in(in, 2 * (size_t)K));
+  p.w = static_cast<const int8_t *>(st.in(w, (size_t)ch_out * K));
+  uint8_t *dout[2];
+  const bool adjacent = out2 == out + ch_out;          // the usual call: one [2][ch_out] block
+  if (adjacent) {
+    dout[0] = static_cast<uint8_t *>(st.out(out, 2 * (size_t)ch_out));
+    dout[1] = dout[0] ? dout[0] + ch_out : nullptr;
+  } else {
+    dout[0] = static_cast<uint8_t *>(st.out(out, (size_t)ch_out));
+    dout[1] = static_cast<uint8_t *>(st.out(out2, (size_t)ch_out));
+  }
+  p.epi.bias = st.in(bias, ch_out);
+  p.epi.k = mode >= EPI_BN32 ? st.in(k, sizeof(BN_T) * ch_out) : nullptr;
+  p.epi.lambda = mode >= EPI_BN32 ? st.in(lambda, sizeof(BN_T) * ch_out) : nullptr;
+  if (!st.ok()) return;
+  p.epi.mode = mode;
+  p.epi.out_mult = (int)(int16_t)(uint16_t)out_mult;
+  p.epi.shift = out_shift;
+  p.B = 1; p.H = p.Ho = 1; p.Cin = K; p.Cout = ch_out; p.ky = p.kx = 1; p.pt = p.pl = 0; p.sy = p.sx = 1;
+  if (adjacent) {
+    p.W = p.Wo = 2; p.in = din; p.out = dout[0];
+    if (!launch_conv(c, p)) return;
+  } else {
+    p.W = p.Wo = 1;
+    for (int r = 0; r < 2; r++) {
+      p.in = din + (size_t)r * K; p.out = dout[r];
+      if (!launch_conv(c, p)) return;
+    }
+  }
+  st.finish();
+}
+
 // ---- linear --------------------------------------------------------------------------------
 template <typename BN_T>
 void linear_entry(const uint8_t *in, const int8_t *bias, uint8_t *out, const int8_t *w, BN_T *k,
@@ -412,6 +505,26 @@ using namespace pulpnn;
                           ch_im_out, dim_kernel_x, dim_kernel_y, padding_y_top, padding_y_bottom,       \
                           padding_x_left, padding_x_right, stride_x, stride_y, FLAG_RELU,               \
                           FLAG_BATCH_NORM);                                                             \
+  }                                                                                                     \
+  extern "C" void pulp_nn_depthwise_3x3_s1##SFX(uint8_t *In_Img, uint8_t *Out_Img, int R, int C, int CH, \
+                                                int p_l, int p_r, int8_t *Kernel, int8_t out_shift,     \
+                                                uint16_t out_mult, BN_T *kappa, BN_T *lambda,           \
+                                                int flag_relu, int flag_batch_norm,                     \
+                                                unsigned int *memory_chan)                              \
+  {                                                                                                     \
+    (void)memory_chan;                                                                                  \
+    depthwise_3x3_s1_entry<BN_T>(In_Img, Out_Img, R, C, CH, p_l, p_r, Kernel, out_shift, out_mult,      \
+                                 kappa, lambda, flag_relu, flag_batch_norm);                            \
+  }                                                                                                     \
+  extern "C" uint8_t *pulp_nn_matmul##SFX(const int8_t *pWeight, uint8_t *pInBuffer, uint16_t ch_out,   \
+                                          uint16_t num_col_im2col, uint16_t out_shift,                  \
+                                          uint16_t out_mult, BN_T *k, BN_T *lambda, const int8_t *bias, \
+                                          uint8_t *pOut, uint8_t *pOut2, int flag_relu,                 \
+                                          int flag_batch_norm)                                          \
+  {                                                                                                     \
+    matmul_entry<BN_T>(pWeight, pInBuffer, ch_out, num_col_im2col, out_shift, out_mult, k, lambda,      \
+                       bias, pOut, pOut2, flag_relu, flag_batch_norm);                                  \
+    return pOut ? pOut + 2 * (size_t)ch_out : pOut;      /* 32bit/src/pulp_nn_matmul.c:296-297 */       \
   }                                                                                                     \
   extern "C" void pulp_nn_linear##SFX(uint8_t *pInBuffer, int8_t *bias, uint8_t *pOutBuffer,            \
                                       int8_t *pWeights, BN_T *k, BN_T *lambda, uint16_t out_mult,       \

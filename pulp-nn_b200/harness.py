@@ -46,6 +46,10 @@ class GpuKernels:
         return t.cpu().numpy()
 
     @staticmethod
+    def _addr(t):
+        return int(t.ctypes.data) if isinstance(t, np.ndarray) else int(t.data_ptr())
+
+    @staticmethod
     def _bn(bits, k, lam):
         dt = np.int32 if bits == 32 else np.int64
         return (None if k is None else np.ascontiguousarray(k, dt),
@@ -102,6 +106,34 @@ class GpuKernels:
            self._in(lam), out_mult, out_shift, W, H, Cc, Wo, Ho, Cc, kx, ky, pt, pb, pl, pr, sx, sy,
            relu, bn)
         return self._np(out)
+
+    def depthwise_3x3_s1(self, bits, x, w, k, lam, *, out_mult=1, out_shift=0, relu=1, bn=1, p_l=1, p_r=1):
+        """x [B][CH][R][C] -> [B][R-2][C][CH]."""
+        B, CH, R, Cw = x.shape
+        k, lam = self._bn(bits, k, lam)
+        out = self._out((B, R - 2, Cw, CH), np.uint8)
+        api.set_batch(B)
+        api.pulp_nn_depthwise_3x3_s1(bits, self._in(x), out, R, Cw, CH, p_l, p_r, self._in(w), out_shift, out_mult,
+                                     self._in(k), self._in(lam), relu, bn)
+        return self._np(out)
+
+    def matmul(self, bits, x2, w, k, lam, *, bias=None, out_mult=1, out_shift=0, relu=1, bn=1, adjacent=True):
+        """x2 [2][K] (two im2col columns) -> [2][ch_out]; also checks the returned pointer."""
+        K = x2.shape[1]
+        N = w.shape[0]
+        k, lam = self._bn(bits, k, lam)
+        if adjacent:
+            out = self._out((2, N), np.uint8)
+            o1, o2 = self._addr(out), self._addr(out) + N
+        else:
+            out = self._out((3, N), np.uint8)          # rows 0 and 2: not adjacent
+            o1, o2 = self._addr(out), self._addr(out) + 2 * N
+        api.set_batch(1)
+        r = api.pulp_nn_matmul(bits, self._in(w), self._in(x2), N, K, out_shift, out_mult, self._in(k), self._in(lam),
+                               self._in(bias), o1, o2, relu, bn)
+        assert r == o1 + 2 * N, "pulp_nn_matmul must return pOut + 2*ch_out"
+        got = self._np(out)
+        return got if adjacent else got[[0, 2]]
 
     def linear(self, bits, x, w, k, lam, *, bias=None, out_mult=1, out_shift=0, relu=1, bn=1):
         B, K = x.shape

@@ -373,6 +373,42 @@ def test_slicing_variants_and_short_kernels(bits, gpu, restatement, reference32,
         same(gpu.depthwise(bits, c["x"], c["w"], c["k"], c["lam"], less_4_weights=True, **dw_kw(c)), want)
 
 
+@pytest.mark.parametrize("bits", [32, 64])
+@pytest.mark.parametrize("relu,bn", MODES)
+def test_depthwise_3x3_s1_and_matmul(bits, relu, bn, gpu, gpu_host, restatement, reference32, reference64):
+    """The last two symbols of the reference header through the C ABI, against the compiled
+    reference and the restatement: pulp_nn_depthwise_3x3_s1 (CHW in, no vertical padding) and
+    pulp_nn_matmul (two im2col columns; adjacent and separate output rows; device and host
+    buffers; the returned pointer is checked inside the harness)."""
+    ref = reference32 if bits == 32 else reference64
+    for (R, Cw, CH, B) in ((9, 12, 6, 3), (20, 32, 8, 2), (3, 2, 1, 1)):
+        c = wl.depthwise_case(64, R, Cw, CH, pads=(0, 0, 1, 1), batch=B, bits=bits, out_shift=6, out_mult=3,
+                              relu=relu, bn=bn)
+        kw = dict(out_mult=c["out_mult"], out_shift=c["out_shift"], relu=relu, bn=bn)
+        want = ref.depthwise_3x3_s1(bits, c["x"], c["w"], c["k"], c["lam"], **kw)
+        same(restatement.depthwise_3x3_s1(bits, c["x"], c["w"], c["k"], c["lam"], **kw), want)
+        same(gpu.depthwise_3x3_s1(bits, c["x"], c["w"], c["k"], c["lam"], **kw), want)
+    same(gpu_host.depthwise_3x3_s1(bits, c["x"], c["w"], c["k"], c["lam"], **kw), want)
+    for (K, N) in ((288, 64), (27, 7), (64, 1), (1024, 96)):
+        c = wl.linear_case(65, K, N, batch=2, bits=bits, out_shift=8, out_mult=3, relu=relu, bn=bn)
+        kw = dict(bias=c["bias"], out_mult=c["out_mult"], out_shift=c["out_shift"], relu=relu, bn=bn)
+        want = ref.matmul(bits, c["x"], c["w"], c["k"], c["lam"], **kw)
+        same(gpu.matmul(bits, c["x"], c["w"], c["k"], c["lam"], **kw), want)
+        same(gpu.matmul(bits, c["x"], c["w"], c["k"], c["lam"], adjacent=False, **kw), want)
+    same(gpu_host.matmul(bits, c["x"], c["w"], c["k"], c["lam"], **kw), want)
+    same(gpu_host.matmul(bits, c["x"], c["w"], c["k"], c["lam"], adjacent=False, **kw), want)
+
+
+def test_depthwise_3x3_s1_rejects_what_the_reference_gets_wrong(gpu):
+    """Without left/right padding flags, or with an odd width, the reference's row loop runs into
+    the next row (32bit/src/pulp_nn_depthwise_3x3_s1.c:140): rejected, nothing is enqueued."""
+    c = wl.depthwise_case(66, 9, 12, 4, pads=(0, 0, 1, 1), batch=1, out_shift=6)
+    for p_l, p_r, x in ((0, 1, c["x"]), (1, 0, c["x"]), (1, 1, c["x"][:, :, :, :11].copy())):
+        with pytest.raises(api.PulpNNError):
+            gpu.depthwise_3x3_s1(32, x, c["w"], c["k"], c["lam"], out_shift=6, p_l=p_l, p_r=p_r)
+    api.clear_error()
+
+
 def test_layout_change(gpu, gpu_host):
     """CHW <-> HWC against numpy's transpose: whole tiles, ragged tiles, sizes that rule out 32-bit
     accesses on either side, and the round trip."""

@@ -243,3 +243,30 @@ def test_depthwise_less_4_weights(kernel, pads, restatement, reference32, refere
         want = restatement.depthwise(bits, c["x"], c["w"], c["k"], c["lam"], **kw)
         assert np.count_nonzero(want) > want.size // 10
         assert np.array_equal(ref.depthwise(bits, c["x"], c["w"], c["k"], c["lam"], less4=True, **kw), want)
+
+
+@pytest.mark.parametrize("relu,bn", MODES)
+def test_depthwise_3x3_s1(relu, bn, restatement, reference32, reference64):
+    """pulp_nn_depthwise_3x3_s1 inside its defined domain (p_l = p_r = 1, even C) equals the 3x3
+    stride-1 depthwise convolution with horizontal padding only; its flags select the mode the
+    way the convolutions' do (flag_relu == 1 for the multiplier mode)."""
+    for bits, ref in ((32, reference32), (64, reference64)):
+        for (R, Cw, CH) in ((9, 12, 6), (3, 2, 1), (17, 30, 5)):
+            c = wl.depthwise_case(53, R, Cw, CH, pads=(0, 0, 1, 1), batch=2, bits=bits, out_shift=6, out_mult=3,
+                                  relu=relu, bn=bn)
+            kw = dict(out_mult=c["out_mult"], out_shift=c["out_shift"], relu=relu, bn=bn)
+            want = restatement.depthwise_3x3_s1(bits, c["x"], c["w"], c["k"], c["lam"], **kw)
+            assert want.shape == (2, R - 2, Cw, CH)
+            assert np.array_equal(ref.depthwise_3x3_s1(bits, c["x"], c["w"], c["k"], c["lam"], **kw), want)
+
+
+@pytest.mark.parametrize("relu,bn", MODES)
+def test_matmul_two_columns(relu, bn, restatement, reference32, reference64):
+    """pulp_nn_matmul: two im2col columns against all filters, with the channel tail (ch_out & 3)
+    and the reduction tail (K & 3) of the reference, and the returned pointer."""
+    for bits, ref in ((32, reference32), (64, reference64)):
+        for (K, N) in ((288, 64), (27, 7), (10, 3), (64, 1), (5, 9)):
+            c = wl.linear_case(54, K, N, batch=2, bits=bits, out_shift=8, out_mult=3, relu=relu, bn=bn)
+            kw = dict(bias=c["bias"], out_mult=c["out_mult"], out_shift=c["out_shift"], relu=relu, bn=bn)
+            want = restatement.matmul(bits, c["x"], c["w"], c["k"], c["lam"], **kw)
+            assert np.array_equal(ref.matmul(bits, c["x"], c["w"], c["k"], c["lam"], **kw), want)
