@@ -114,6 +114,66 @@ __global__ void __launch_bounds__(256) avgpool_kernel(const PoolProblem p, int C
   if (VEC) *reinterpret_cast<unsigned *>(dst) = o; else st_bytes(dst, o, nb);
 }
 
+// The same for 16 channels per thread (C a multiple of 16, 16-byte aligned tensors): 16-byte loads,
+// four of them in flight, so that a window of many pixels (a global pool) keeps HBM busy.
+__global__ void __launch_bounds__(256) avgpool16_kernel(const PoolProblem p, int CW, long long total)
+{
+  const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= total) return;
+  const int cw = (int)(t % CW);
+  long long r = t / CW;
+  const int ox = (int)(r % p.Wo); r /= p.Wo;
+  const int oy = (int)(r % p.Ho);
+  const int b = (int)(r / p.Ho);
+  const int c = cw * 16;
+  const int y0 = max(oy * p.sy - p.pb, 0), y1 = min(oy * p.sy - p.pt + p.ky, p.H);
+  const int x0 = max(ox * p.sx - p.pl, 0), x1 = min(ox * p.sx - p.pr + p.kx, p.W);
+  const uint8_t *img = p.in + (size_t)b * p.H * p.W * p.C + c;
+  unsigned s[16];
+#pragma unroll
+  for (int j = 0; j < 16; j++) s[j] = 0;
+  auto add16 = [&](const uint4 &v) {
+    const unsigned w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      s[4 * i + 0] += w[i] & 0xff; s[4 * i + 1] += (w[i] >> 8) & 0xff;
+      s[4 * i + 2] += (w[i] >> 16) & 0xff; s[4 * i + 3] += w[i] >> 24;
+    }
+  };
+  for (int y = y0; y < y1; y++) {
+    const uint8_t *row = img + (size_t)y * p.W * p.C;
+    int x = x0;
+    for (; x + 4 <= x1; x += 4) {
+      uint4 v[4];
+#pragma unroll
+      for (int i = 0; i < 4; i++) v[i] = __ldg(reinterpret_cast<const uint4 *>(row + (size_t)(x + i) * p.C));
+#pragma unroll
+      for (int i = 0; i < 4; i++) add16(v[i]);
+    }
+    for (; x < x1; x++) add16(__ldg(reinterpret_cast<const uint4 *>(row + (size_t)x * p.C)));
+  }
+  const unsigned ktot = (unsigned)(p.kx * p.ky);
+  unsigned o[4] = {0, 0, 0, 0};
+#pragma unroll
+  for (int j = 0; j < 16; j++) {
+    int res;
+    if (p.requant) {
+      if (p.bn_bits == 32) {
+        const unsigned tq = s[j] * (unsigned)(int)p.lambda / ktot + (unsigned)(int)p.out_add;
+        res = (int)(tq >> p.shift);
+      } else {
+        const long long tq = (long long)s[j] * p.lambda / (long long)ktot + p.out_add;
+        res = (int)(tq >> p.shift);
+      }
+    } else {
+      res = (int)(s[j] / ktot);
+    }
+    o[j >> 2] |= (unsigned)clip_u8(res) << (8 * (j & 3));
+  }
+  uint8_t *dst = p.out + (((size_t)b * p.Ho + oy) * p.Wo + ox) * p.C + c;
+  *reinterpret_cast<uint4 *>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
 // ---- residual add --------------------------------------------------------------------------
 // 32bit/src/pulp_nn_utils.c:47-60: uint32 sum of the two int16-scaled bytes, logical shift,
 // cut to 16 bits, then clamp to 255.
@@ -156,6 +216,14 @@ bool launch_maxpool(Context &c, const PoolProblem &p, uint8_t *clobber_in)
 {
   const bool vec = (p.C % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.in) & 3) == 0) &&
                    ((reinterpret_cast<uintptr_t>(p.out) & 3) == 0);
+  // windows of at least 16 pixels: fewer threads with more bytes in flight each
+  if (p.C % 16 == 0 && p.kx * p.ky >= 16 && ((reinterpret_cast<uintptr_t>(p.in) | reinterpret_cast<uintptr_t>(p.out)) & 15) == 0) {
+    const int CW16 = p.C / 16;
+    const long long total16 = (long long)p.B * p.Ho * p.Wo * CW16;
+    avgpool16_kernel<<<(unsigned)((total16 + 255) / 256), 256, 0, c.stream>>>(p, CW16, total16);
+    count_launch();
+    return cuda_ok(cudaGetLastError(), "avgpool launch");
+  }
   const int CW = vec ? p.C / 4 : p.C;
   const long long total = (long long)p.B * p.Ho * p.Wo * CW;
   const unsigned blocks = (unsigned)((total + 255) / 256);

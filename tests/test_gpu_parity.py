@@ -406,7 +406,6 @@ def test_depthwise_3x3_s1_rejects_what_the_reference_gets_wrong(gpu):
     for p_l, p_r, x in ((0, 1, c["x"]), (1, 0, c["x"]), (1, 1, c["x"][:, :, :, :11].copy())):
         with pytest.raises(api.PulpNNError):
             gpu.depthwise_3x3_s1(32, x, c["w"], c["k"], c["lam"], out_shift=6, p_l=p_l, p_r=p_r)
-    api.clear_error()
 
 
 def test_layout_change(gpu, gpu_host):
@@ -495,7 +494,8 @@ def test_avgpool(bits, requant, lam, add, shift, gpu, restatement):
     for C in (9, 32):
         x = rng.integers(0, 256, size=(2, 14, 14, C), dtype=np.uint8)
         for geom in (dict(kernel=(7, 7), strides=(7, 7), pads=(0, 0, 0, 0), out_hw=(2, 2)),
-                     dict(kernel=(3, 3), strides=(2, 2), pads=(1, 1, 1, 1), out_hw=(7, 7))):
+                     dict(kernel=(3, 3), strides=(2, 2), pads=(1, 1, 1, 1), out_hw=(7, 7)),
+                     dict(kernel=(5, 5), strides=(2, 2), pads=(2, 2, 2, 2), out_hw=(7, 7))):
             kw = dict(lam=lam, out_shift=shift, out_add=add, requant=requant, **geom)
             same(gpu.avgpool(bits, x, **kw), restatement.avgpool(bits, x, **kw))
 
