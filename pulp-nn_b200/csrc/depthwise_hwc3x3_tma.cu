@@ -240,6 +240,8 @@ __device__ __forceinline__ int taps3(const unsigned (&W)[9], int n)
 }
 
 template <int MODE, int S, int NGX, int CI>
+// (Capping the stride-1 kernel at 96 registers, which fits without spilling and lets a third CTA of
+// 224 threads onto an SM, was measured: 10-15 % slower on every stride-1 layer.)
 __global__ void __launch_bounds__(Geo<S, NGX, CI>::THREADS, 512 / Geo<S, NGX, CI>::THREADS)
 depthwise_hwc3x3_tma_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_constant__ CUtensorMap map_out,
                             const HwcTmaParams g)
