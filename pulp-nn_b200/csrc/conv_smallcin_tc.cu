@@ -100,6 +100,8 @@ conv_smallcin_tc_kernel(const __grid_constant__ CUtensorMap map_in, const SmallT
     mbar_fence_init();
   }
   if (warp == FIRST_MMA) tmem_alloc(tmem_slot, TMEM_COLS);
+  pdl_wait();                      // the set-up above may overlap the previous kernel's tail
+  if (tid == 0) pdl_launch_dependents();
   // the im2col ring starts as zeros: chunk 3 of every row (and what lies past a filter row's bytes)
   // is never written again
   for (int idx = tid; idx < NA * A_TILE_BYTES / 16; idx += THREADS) sts128(smem_u32(a_ring) + idx * 16, 0u, 0u, 0u, 0u);
@@ -337,9 +339,9 @@ bool launch_cfg(Context &c, const CUtensorMap &map, const SmallTcParams &g)
     return false;
   const int sms = c.sm_count > 0 ? c.sm_count : 148;
   const int grid = g.units < sms ? g.units : sms;
-  kern<<<grid, THREADS, smem, c.stream>>>(map, g);
+  const cudaError_t le = launch_pdl(kern, dim3(grid), dim3(THREADS), smem, c.stream, map, g);
   count_launch();
-  return cuda_ok(cudaGetLastError(), "conv_smallcin_tc launch");
+  return cuda_ok(le, "conv_smallcin_tc launch") && cuda_ok(cudaGetLastError(), "conv_smallcin_tc launch");
 }
 
 template <int MODE>

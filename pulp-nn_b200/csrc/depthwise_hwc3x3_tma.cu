@@ -287,6 +287,10 @@ depthwise_hwc3x3_tma_kernel(const __grid_constant__ CUtensorMap map_in, const __
     for (int s = 0; s < RING; s++) mbar_init(&full[s], 1);
     *abort_flag = 0;
     mbar_fence_init();
+  }
+  pdl_wait();                      // up to here the kernel may overlap the previous one's tail
+  if (tid == 0) {
+    pdl_launch_dependents();
     const int first = total < RING ? total : RING;
     for (int j = 0; j < first; j++) issue_next();
   }
@@ -538,6 +542,10 @@ depthwise_chw3x3_tma_kernel(const __grid_constant__ CUtensorMap map_in, const Ch
     for (int s = 0; s < RING; s++) mbar_init(&full[s], 1);
     *abort_flag = 0;
     mbar_fence_init();
+  }
+  pdl_wait();                      // up to here the kernel may overlap the previous one's tail
+  if (tid == 0) {
+    pdl_launch_dependents();
     const int first = ngroups < RING ? ngroups : RING;
     for (int j = 0; j < first; j++) {
       mbar_arrive_expect_tx(&full[j], stage);
@@ -782,9 +790,9 @@ bool launch_geo(Context &c, const DepthwiseProblem &p)
   CUtensorMap map_in, map_out;
   if (!encode_4d(&map_in, p.in, p.C, p.W, p.H, p.B, CI, G::WBOX, G::ROWS_IN)) return false;
   if (!encode_4d(&map_out, p.out, p.C, p.Wo, p.Ho, p.B, CI, G::WT, G::ROWS_OUT)) return false;
-  kern<<<(unsigned)total, G::THREADS, G::SMEM, c.stream>>>(map_in, map_out, g);
+  const cudaError_t le = launch_pdl(kern, dim3((unsigned)total), dim3(G::THREADS), G::SMEM, c.stream, map_in, map_out, g);
   count_launch();
-  return cuda_ok(cudaGetLastError(), "depthwise_hwc3x3_tma launch");
+  return cuda_ok(le, "depthwise_hwc3x3_tma launch") && cuda_ok(cudaGetLastError(), "depthwise_hwc3x3_tma launch");
 }
 
 // tile widths on offer: 28, 16 or 8 columns per column group of a warp's first lane ... in column
@@ -851,9 +859,9 @@ bool launch_chw_geo(Context &c, const DepthwiseProblem &p)
   // [B][C][H][W]: whole rows of 32 channels per box
   CUtensorMap map_in;
   if (!encode_4d(&map_in, p.in, p.W, p.H, p.C, p.B, p.W, G::ROWS_IN, G::CT)) return false;
-  kern<<<(unsigned)total, G::THREADS, smem, c.stream>>>(map_in, g);
+  const cudaError_t le = launch_pdl(kern, dim3((unsigned)total), dim3(G::THREADS), (size_t)smem, c.stream, map_in, g);
   count_launch();
-  return cuda_ok(cudaGetLastError(), "depthwise_chw3x3_tma launch");
+  return cuda_ok(le, "depthwise_chw3x3_tma launch") && cuda_ok(cudaGetLastError(), "depthwise_chw3x3_tma launch");
 }
 
 template <int MODE>

@@ -199,6 +199,9 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // everything above overlapped the tail of the previous kernel; nothing below may
+  pdl_wait();
+  if (threadIdx.x == 0) pdl_launch_dependents();
 
   const int units = g.m_tiles * g.n_tiles * g.k_slices;
   // stationary CTAs: n-tile and first m-tile of this CTA, distance between its m-tiles
@@ -699,9 +702,9 @@ bool launch_cfg(Context &c, const TcMaps &m, const TcParams &g, int grid)
   }
   // every configuration asks for more than half of an SM's shared memory, so exactly one CTA (and
   // its 512 tensor-memory columns) lives on an SM
-  kern<<<grid, NUM_THREADS, L::TOTAL, c.stream>>>(m.a, m.b, m.out, g);
+  const cudaError_t le = launch_pdl(kern, dim3(grid), dim3(NUM_THREADS), L::TOTAL, c.stream, m.a, m.b, m.out, g);
   count_launch();
-  return cuda_ok(cudaGetLastError(), "igemm_tc launch");
+  return cuda_ok(le, "igemm_tc launch") && cuda_ok(cudaGetLastError(), "igemm_tc launch");
 }
 
 template <int MODE, int BN_TILE, bool PARTIAL, bool TMA_OUT>

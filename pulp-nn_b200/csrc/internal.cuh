@@ -148,6 +148,29 @@ bool ensure_device(Context &c);
 void set_error(int code, const char *fmt, ...);
 bool cuda_ok(cudaError_t e, const char *what);
 void count_launch(unsigned n = 1);
+
+// Programmatic dependent launch. A kernel launched this way may become resident and run its
+// prologue while the previous kernel of the stream is still draining; it must execute pdl_wait()
+// before it reads anything an earlier kernel wrote or writes anything an earlier kernel may still
+// read (the wait returns once the earlier grids have completed and their writes are visible).
+// pdl_launch_dependents() lets the NEXT kernel of the stream do the same with respect to this one.
+// Both are no-ops in a kernel launched the ordinary way.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args &&...args)
+{
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#endif
 void *ctx_scratch(Context &c, size_t bytes);    // grow-only device scratch, nullptr on failure
 
 // Stages host buffers through device memory. Device pointers pass through untouched.

@@ -118,6 +118,8 @@ __global__ void __launch_bounds__(256) avgpool_kernel(const PoolProblem p, int C
 // four of them in flight, so that a window of many pixels (a global pool) keeps HBM busy.
 __global__ void __launch_bounds__(256) avgpool16_kernel(const PoolProblem p, int CW, long long total)
 {
+  pdl_wait();
+  pdl_launch_dependents();
   const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= total) return;
   const int cw = (int)(t % CW);
@@ -216,14 +218,6 @@ bool launch_maxpool(Context &c, const PoolProblem &p, uint8_t *clobber_in)
 {
   const bool vec = (p.C % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.in) & 3) == 0) &&
                    ((reinterpret_cast<uintptr_t>(p.out) & 3) == 0);
-  // windows of at least 16 pixels: fewer threads with more bytes in flight each
-  if (p.C % 16 == 0 && p.kx * p.ky >= 16 && ((reinterpret_cast<uintptr_t>(p.in) | reinterpret_cast<uintptr_t>(p.out)) & 15) == 0) {
-    const int CW16 = p.C / 16;
-    const long long total16 = (long long)p.B * p.Ho * p.Wo * CW16;
-    avgpool16_kernel<<<(unsigned)((total16 + 255) / 256), 256, 0, c.stream>>>(p, CW16, total16);
-    count_launch();
-    return cuda_ok(cudaGetLastError(), "avgpool launch");
-  }
   const int CW = vec ? p.C / 4 : p.C;
   const long long total = (long long)p.B * p.Ho * p.Wo * CW;
   const unsigned blocks = (unsigned)((total + 255) / 256);
@@ -251,6 +245,15 @@ bool launch_avgpool(Context &c, const PoolProblem &p)
 {
   const bool vec = (p.C % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.in) & 3) == 0) &&
                    ((reinterpret_cast<uintptr_t>(p.out) & 3) == 0);
+  // windows of at least 16 pixels: fewer threads with more bytes in flight each
+  if (p.C % 16 == 0 && p.kx * p.ky >= 16 && ((reinterpret_cast<uintptr_t>(p.in) | reinterpret_cast<uintptr_t>(p.out)) & 15) == 0) {
+    const int CW16 = p.C / 16;
+    const long long total16 = (long long)p.B * p.Ho * p.Wo * CW16;
+    const cudaError_t le = launch_pdl(avgpool16_kernel, dim3((unsigned)((total16 + 255) / 256)), dim3(256), 0, c.stream,
+                                      p, CW16, total16);
+    count_launch();
+    return cuda_ok(le, "avgpool launch") && cuda_ok(cudaGetLastError(), "avgpool launch");
+  }
   const int CW = vec ? p.C / 4 : p.C;
   const long long total = (long long)p.B * p.Ho * p.Wo * CW;
   const unsigned blocks = (unsigned)((total + 255) / 256);

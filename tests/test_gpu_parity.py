@@ -472,6 +472,8 @@ def test_linear_single_vector_and_odd_sizes(gpu, restatement):
     dict(kernel=(2, 2), strides=(2, 2), pads=(0, 0, 0, 0), out_hw=(7, 7)),
     dict(kernel=(3, 3), strides=(2, 2), pads=(1, 1, 1, 1), out_hw=(7, 7)),
     dict(kernel=(3, 2), strides=(3, 2), pads=(1, 0, 0, 0), out_hw=(5, 7)),
+    dict(kernel=(5, 5), strides=(3, 3), pads=(2, 2, 2, 2), out_hw=(5, 5)),     # a large window
+    dict(kernel=(7, 7), strides=(7, 7), pads=(0, 0, 0, 0), out_hw=(2, 2)),
 ])
 @pytest.mark.parametrize("C", [10, 64])
 def test_maxpool(geom, C, gpu, gpu_host, restatement):
