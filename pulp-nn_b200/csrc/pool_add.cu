@@ -142,17 +142,21 @@ __global__ void __launch_bounds__(256) avgpool16_kernel(const PoolProblem p, int
       s[4 * i + 2] += (w[i] >> 16) & 0xff; s[4 * i + 3] += w[i] >> 24;
     }
   };
-  for (int y = y0; y < y1; y++) {
-    const uint8_t *row = img + (size_t)y * p.W * p.C;
-    int x = x0;
-    for (; x + 4 <= x1; x += 4) {
-      uint4 v[4];
+  // the window's pixels in one sequence, eight loads in flight at a time
+  const int tot = (x1 > x0 && y1 > y0) ? (x1 - x0) * (y1 - y0) : 0;
+  int yy = y0, xx = x0;
+  for (int n = 0; n < tot; n += 8) {
+    uint4 v[8];
 #pragma unroll
-      for (int i = 0; i < 4; i++) v[i] = __ldg(reinterpret_cast<const uint4 *>(row + (size_t)(x + i) * p.C));
-#pragma unroll
-      for (int i = 0; i < 4; i++) add16(v[i]);
+    for (int i = 0; i < 8; i++) {
+      v[i] = make_uint4(0, 0, 0, 0);
+      if (n + i < tot) {
+        v[i] = __ldg(reinterpret_cast<const uint4 *>(img + ((size_t)yy * p.W + xx) * p.C));
+        if (++xx == x1) { xx = x0; yy++; }
+      }
     }
-    for (; x < x1; x++) add16(__ldg(reinterpret_cast<const uint4 *>(row + (size_t)x * p.C)));
+#pragma unroll
+    for (int i = 0; i < 8; i++) add16(v[i]);
   }
   const unsigned ktot = (unsigned)(p.kx * p.ky);
   unsigned o[4] = {0, 0, 0, 0};

@@ -459,6 +459,27 @@ def test_linear_out_32_config4_raw_accumulators(split_k, gpu, gpu_host, restatem
         same(gpu_host.linear_out_32(c["x"], c["w"], bias32=b32), want)
 
 
+@pytest.mark.parametrize("bits", [32, 64])
+@pytest.mark.parametrize("relu,bn", MODES)
+def test_linear_few_tiles_long_reduction(bits, relu, bn, gpu, gpu_host, restatement):
+    """Few output tiles and a long reduction (the shape of a fully connected layer at a small
+    batch): K split into partial sums or not, depending on the tile count; a K that is not a
+    multiple of the slab, filter counts that are not a multiple of 16, one and two row tiles, every
+    requantisation mode, and raw int32 output."""
+    for (K, N, B) in ((2048, 256, 5), (4096, 1000, 200), (2064, 48, 130), (3072, 520, 256), (4096, 4096, 256)):
+        c = wl.linear_case(26, K, N, batch=B, bits=bits, out_shift=wl.ceil_log2(K) + 4, out_mult=3,
+                           relu=relu, bn=bn, w_range=(-128, 127))
+        kw = dict(bias=c["bias"], out_mult=c["out_mult"], out_shift=c["out_shift"], relu=relu, bn=bn)
+        want = restatement.linear(bits, c["x"], c["w"], c["k"], c["lam"], **kw)
+        assert np.count_nonzero(want) > want.size // 20
+        same(gpu.linear(bits, c["x"], c["w"], c["k"], c["lam"], **kw), want)
+        if (relu, bn) == (1, 1):
+            same(gpu.linear_out_32(c["x"], c["w"], bias32=c["bias32"].view(np.int8), bits=bits),
+                 restatement.linear_out_32(c["x"], c["w"], bias32=c["bias32"].view(np.int8)))
+    same(gpu_host.linear(bits, c["x"], c["w"], c["k"], c["lam"], **kw), want)
+    assert api.device_status() == 0
+
+
 def test_linear_single_vector_and_odd_sizes(gpu, restatement):
     for (K, N, B) in ((4096, 4096, 1), (1024, 1000, 7), (77, 5, 1), (16, 16, 130)):
         c = wl.linear_case(43, K, N, batch=B, out_shift=wl.ceil_log2(K) + 2, relu=1, bn=1)
