@@ -190,6 +190,21 @@ void pulpnn_chw_to_hwc(const uint8_t *Im_in, uint8_t *Im_out, uint16_t dim_im_x,
 void pulpnn_hwc_to_chw(const uint8_t *Im_in, uint8_t *Im_out, uint16_t dim_im_x, uint16_t dim_im_y, uint16_t ch_im);
 
 /*
+ * Sub-byte unpack helpers of the reference as bulk device operations. Packed values sit
+ * little-endian in their bytes (element i of a byte = bits [w*i, w*i+w)).
+ *   pulp_nn_im2col_u4_to_u8, pulp_nn_im2col_u2_to_u8   32bit/include/pulp_nn_utils.h:65,67
+ *       (32bit/src/pulp_nn_utils.c:396-438): blockSize = number of uint8 results; it must be a
+ *       multiple of 2 (4): the reference's tail loops never end otherwise.
+ *   pulpnn_i4_to_i8, pulpnn_i2_to_i8                    the sign-extending counterparts, bulk forms of
+ *       pulp_nn_i4_to_i8 / pulp_nn_i2_to_i8 (pulp_nn_utils.c:255,289); n = number of int8 results.
+ * Device or host buffers; the batch setting does not apply.
+ */
+void pulp_nn_im2col_u4_to_u8(uint8_t *pInput, uint8_t *pOutput, unsigned int blockSize);
+void pulp_nn_im2col_u2_to_u8(uint8_t *pInput, uint8_t *pOutput, unsigned int blockSize);
+void pulpnn_i4_to_i8(const int8_t *pSrc, int8_t *pDst, unsigned int n);
+void pulpnn_i2_to_i8(const int8_t *pSrc, int8_t *pDst, unsigned int n);
+
+/*
  * pulpnn_linear_out_32_static_scratch -- no counterpart in the reference.
  *
  * The arithmetic of pulp_nn_linear_out_32 (int32 accumulators, bias read as int32 words, no

@@ -112,6 +112,19 @@ class Restatement:
                                   pt, pb, pl, pr, sx, sy, relu, bn, int(in_is_hwc), B, _ptr(acc))
         return (out, acc) if want_acc else out
 
+    @staticmethod
+    def unpack(packed, bits_per_value, signed):
+        """32bit/src/pulp_nn_utils.c:201-356: element i of a byte is bits [w*i, w*i+w), zero-extended
+        (bitextu) or sign-extended (bitext)."""
+        packed = np.ascontiguousarray(packed, np.uint8).ravel()
+        per = 8 // bits_per_value
+        mask = (1 << bits_per_value) - 1
+        v = np.stack([(packed >> (bits_per_value * i)) & mask for i in range(per)], axis=1).reshape(-1).astype(np.int16)
+        if signed:
+            v = np.where(v >= (1 << (bits_per_value - 1)), v - (1 << bits_per_value), v)
+            return v.astype(np.int8)
+        return v.astype(np.uint8)
+
     def depthwise_3x3_s1(self, bits, x, w, k, lam, *, out_mult=1, out_shift=0, relu=1, bn=1, p_l=1, p_r=1):
         """32bit/src/pulp_nn_depthwise_3x3_s1.c:28-210 inside its defined domain (p_l = p_r = 1, even
         C): the zero-padded 3x3 stride-1 depthwise convolution without vertical padding and without
@@ -190,7 +203,7 @@ class CompiledReference:
         self.threads = threads
         self.lib = C.CDLL(_REF_SO[bits])
         for name in ("refdrv_conv", "refdrv_depthwise", "refdrv_linear", "refdrv_maxpool",
-                     "refdrv_avgpool", "refdrv_add", "refdrv_depthwise_3x3_s1", "refdrv_matmul"):
+                     "refdrv_avgpool", "refdrv_add", "refdrv_depthwise_3x3_s1", "refdrv_matmul", "refdrv_unpack"):
             getattr(self.lib, name).restype = C.c_double
         self.lib.refdrv_init.argtypes = [C.c_size_t]
         assert self.lib.refdrv_bn_bits() == bits
@@ -276,6 +289,15 @@ class CompiledReference:
                                           _ptr(bias), _ptr(out), relu, bn, C.byref(off)))
         assert off.value == 2 * N
         return out
+
+    def unpack(self, packed, bits_per_value, signed):
+        """pulp_nn_im2col_u4_to_u8 / _u2_to_u8, pulp_nn_i4_to_i8 / _i2_to_i8 over a packed uint8 array."""
+        kind = {(4, False): 0, (2, False): 1, (4, True): 2, (2, True): 3}[(bits_per_value, bool(signed))]
+        packed = np.ascontiguousarray(packed, np.uint8)
+        n_out = packed.size * (8 // bits_per_value)
+        out = np.empty(n_out, np.uint8)
+        self._done(self.lib.refdrv_unpack(kind, _ptr(packed), _ptr(out), C.c_uint(n_out)))
+        return out.view(np.int8) if signed else out
 
     def linear(self, bits, x, w, k, lam, *, bias=None, out_mult=1, out_shift=0, relu=1, bn=1):
         assert bits == self.bits

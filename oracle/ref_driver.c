@@ -326,6 +326,36 @@ double refdrv_matmul(const int8_t *w, const uint8_t *in2, int ch_out, int K, int
   return dt;
 }
 
+/* ====================== sub-byte unpack helpers ============================ */
+/* the helpers live in pulp_nn_utils.c and are declared in pulp_nn_utils.h, which cannot be included
+ * here (it pulls in pmsis.h a second time through a different path); same signatures */
+void pulp_nn_im2col_u4_to_u8(uint8_t *pInput, uint8_t *pOutput, unsigned int blockSize);
+void pulp_nn_im2col_u2_to_u8(uint8_t *pInput, uint8_t *pOutput, unsigned int blockSize);
+void pulp_nn_i4_to_i8(int8_t *pSrc, int8_t *pDst);
+void pulp_nn_i2_to_i8(int8_t *pSrc, int8_t *pDst);
+
+/* kind: 0 u4, 1 u2, 2 i4, 3 i2. n_out = number of 8-bit results. The signed helpers widen one
+ * 32-bit word per call, so n_out must then be a multiple of 8 (i4) or 16 (i2). The helpers load
+ * whole words: the input copy is padded. */
+double refdrv_unpack(int kind, const uint8_t *in, uint8_t *out, unsigned int n_out)
+{
+  const unsigned per_byte = (kind == 0 || kind == 2) ? 2u : 4u;
+  const size_t n_in = n_out / per_byte;
+  bump_t b = { 0 };
+  uint8_t *s_in = bump(&b, n_in + 8), *s_out = bump(&b, (size_t)n_out + 16);
+  if (!s_in || !s_out) return -1.0;
+  memset(s_in, 0, n_in + 8);
+  memcpy(s_in, in, n_in);
+  double t0 = now_s();
+  if (kind == 0) pulp_nn_im2col_u4_to_u8(s_in, s_out, n_out);
+  else if (kind == 1) pulp_nn_im2col_u2_to_u8(s_in, s_out, n_out);
+  else if (kind == 2) for (size_t i = 0; i < n_in; i += 4) pulp_nn_i4_to_i8((int8_t *)s_in + i, (int8_t *)s_out + 2 * i);
+  else for (size_t i = 0; i < n_in; i += 4) pulp_nn_i2_to_i8((int8_t *)s_in + i, (int8_t *)s_out + 4 * i);
+  double dt = now_s() - t0;
+  memcpy(out, s_out, n_out);
+  return dt;
+}
+
 /* ============================== linear ==================================== */
 typedef struct {
   const uint8_t *in; const int8_t *bias; uint8_t *out8; int32_t *out32; const int8_t *w;

@@ -232,6 +232,21 @@ def pulp_nn_add(bits, Im_in_1, Im_in_2, Im_out, out_mult1, out_mult2, out_shift,
     _check()
 
 
+def _unpack(name):
+    def call(src, dst, n_out):
+        getattr(_lib.load_library(), name)(_ptr(src), _ptr(dst), C.c_uint(n_out))
+        _check()
+    call.__name__ = name
+    call.__doc__ = "%s(src, dst, number of 8-bit results): sub-byte values widened to bytes." % name
+    return call
+
+
+pulp_nn_im2col_u4_to_u8 = _unpack("pulp_nn_im2col_u4_to_u8")
+pulp_nn_im2col_u2_to_u8 = _unpack("pulp_nn_im2col_u2_to_u8")
+pulpnn_i4_to_i8 = _unpack("pulpnn_i4_to_i8")
+pulpnn_i2_to_i8 = _unpack("pulpnn_i2_to_i8")
+
+
 def pulpnn_chw_to_hwc(Im_in, Im_out, dim_im_x, dim_im_y, ch_im):
     """[batch][C][H][W] -> [batch][H][W][C] (no counterpart in the reference)."""
     _lib.load_library().pulpnn_chw_to_hwc(_ptr(Im_in), _ptr(Im_out), C.c_uint16(dim_im_x),

@@ -135,6 +135,16 @@ class GpuKernels:
         got = self._np(out)
         return got if adjacent else got[[0, 2]]
 
+    def unpack(self, packed, bits_per_value, signed):
+        """packed: uint8 array -> the 4- or 2-bit values widened to uint8 / int8."""
+        n_out = packed.size * (8 // bits_per_value)
+        fn = {(4, False): api.pulp_nn_im2col_u4_to_u8, (2, False): api.pulp_nn_im2col_u2_to_u8,
+              (4, True): api.pulpnn_i4_to_i8, (2, True): api.pulpnn_i2_to_i8}[(bits_per_value, bool(signed))]
+        out = self._out((n_out,), np.uint8)
+        fn(self._in(packed), out, n_out)
+        got = self._np(out)
+        return got.view(np.int8) if signed else got
+
     def linear(self, bits, x, w, k, lam, *, bias=None, out_mult=1, out_shift=0, relu=1, bn=1):
         B, K = x.shape
         N = w.shape[0]

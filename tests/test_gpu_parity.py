@@ -408,6 +408,25 @@ def test_depthwise_3x3_s1_rejects_what_the_reference_gets_wrong(gpu):
             gpu.depthwise_3x3_s1(32, x, c["w"], c["k"], c["lam"], out_shift=6, p_l=p_l, p_r=p_r)
 
 
+@pytest.mark.parametrize("bits_per_value,signed", [(4, False), (2, False), (4, True), (2, True)])
+def test_subbyte_unpack(bits_per_value, signed, gpu, gpu_host, restatement, reference32):
+    """pulp_nn_im2col_u4_to_u8 / _u2_to_u8 and their sign-extending counterparts: whole words, a
+    byte-wise tail, host buffers; an element count that is not a whole number of bytes is refused
+    (the reference's tail loop would never end)."""
+    rng = np.random.default_rng(67)
+    for n_in in (4, 64, 1001, 1 << 20):
+        packed = rng.integers(0, 256, size=n_in, dtype=np.uint8)
+        want = restatement.unpack(packed, bits_per_value, signed)
+        if n_in % 4 == 0:
+            same(reference32.unpack(packed, bits_per_value, signed), want)
+        same(gpu.unpack(packed, bits_per_value, signed), want)
+    same(gpu_host.unpack(packed[:1001], bits_per_value, signed), restatement.unpack(packed[:1001], bits_per_value, signed))
+    fn = {(4, False): api.pulp_nn_im2col_u4_to_u8, (2, False): api.pulp_nn_im2col_u2_to_u8,
+          (4, True): api.pulpnn_i4_to_i8, (2, True): api.pulpnn_i2_to_i8}[(bits_per_value, signed)]
+    with pytest.raises(api.PulpNNError):
+        fn(packed, np.zeros(16, np.uint8), 8 // bits_per_value + 1)
+
+
 def test_layout_change(gpu, gpu_host):
     """CHW <-> HWC against numpy's transpose: whole tiles, ragged tiles, sizes that rule out 32-bit
     accesses on either side, and the round trip."""

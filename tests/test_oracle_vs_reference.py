@@ -270,3 +270,14 @@ def test_matmul_two_columns(relu, bn, restatement, reference32, reference64):
             kw = dict(bias=c["bias"], out_mult=c["out_mult"], out_shift=c["out_shift"], relu=relu, bn=bn)
             want = restatement.matmul(bits, c["x"], c["w"], c["k"], c["lam"], **kw)
             assert np.array_equal(ref.matmul(bits, c["x"], c["w"], c["k"], c["lam"], **kw), want)
+
+
+@pytest.mark.parametrize("bits_per_value,signed", [(4, False), (2, False), (4, True), (2, True)])
+def test_subbyte_unpack(bits_per_value, signed, restatement, reference32):
+    """The sub-byte unpack helpers: whole words and (unsigned block forms) the byte-wise tail."""
+    rng = np.random.default_rng(55)
+    for n_in in (4, 64, 1000) + (() if signed else (1, 7, 1001)):
+        packed = rng.integers(0, 256, size=n_in, dtype=np.uint8)
+        want = restatement.unpack(packed, bits_per_value, signed)
+        assert want.size == n_in * (8 // bits_per_value)
+        assert np.array_equal(reference32.unpack(packed, bits_per_value, signed), want)
