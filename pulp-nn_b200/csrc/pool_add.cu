@@ -48,6 +48,43 @@ __global__ void __launch_bounds__(256) maxpool_kernel(const PoolProblem p, int C
   if (VEC) *reinterpret_cast<unsigned *>(o) = m; else st_bytes(o, m, nb);
 }
 
+// The same for 16 channels per thread (C a multiple of 16, 16-byte aligned tensors, fewer than 2^31
+// threads): 16-byte accesses and 32-bit index arithmetic. The four-channel kernel above spends its
+// time on 64-bit divisions; this one reaches the memory system.
+__global__ void __launch_bounds__(256) maxpool16_kernel(const PoolProblem p, int CW, unsigned total)
+{
+  const unsigned t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= total) return;
+  const unsigned cw = t % (unsigned)CW;
+  unsigned r = t / (unsigned)CW;
+  const int ox = (int)(r % (unsigned)p.Wo); r /= (unsigned)p.Wo;
+  const int oy = (int)(r % (unsigned)p.Ho);
+  const int b = (int)(r / (unsigned)p.Ho);
+  const int y0 = max(oy * p.sy - p.pt, 0), y1 = min(oy * p.sy - p.pt + p.ky, p.H);
+  const int x0 = max(ox * p.sx - p.pl, 0), x1 = min(ox * p.sx - p.pl + p.kx, p.W);
+  const uint8_t *img = p.in + (size_t)b * p.H * p.W * p.C + cw * 16;
+  uint4 m = make_uint4(0, 0, 0, 0);
+  // the window's pixels in one sequence, four loads in flight at a time (a 2x2 window: all of it)
+  const int tot = (x1 > x0 && y1 > y0) ? (x1 - x0) * (y1 - y0) : 0;
+  int yy = y0, xx = x0;
+  for (int n = 0; n < tot; n += 4) {
+    uint4 v[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      v[i] = make_uint4(0, 0, 0, 0);
+      if (n + i < tot) {
+        v[i] = __ldg(reinterpret_cast<const uint4 *>(img + ((size_t)yy * p.W + xx) * p.C));
+        if (++xx == x1) { xx = x0; yy++; }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      m.x = __vmaxu4(m.x, v[i].x); m.y = __vmaxu4(m.y, v[i].y); m.z = __vmaxu4(m.z, v[i].z); m.w = __vmaxu4(m.w, v[i].w);
+    }
+  }
+  *reinterpret_cast<uint4 *>(p.out + (((size_t)b * p.Ho + oy) * p.Wo + ox) * p.C + cw * 16) = m;
+}
+
 // Reproduces what the reference leaves in Im_in: after its x pass, column ox of every input row
 // holds the maximum over that row's window for output column ox (pulp_nn_maxpool.c:63,85-92).
 // Reads the untouched input copy `src` and writes into `dst` (the caller's Im_in).
@@ -225,7 +262,11 @@ bool launch_maxpool(Context &c, const PoolProblem &p, uint8_t *clobber_in)
   const int CW = vec ? p.C / 4 : p.C;
   const long long total = (long long)p.B * p.Ho * p.Wo * CW;
   const unsigned blocks = (unsigned)((total + 255) / 256);
-  if (vec) maxpool_kernel<true><<<blocks, 256, 0, c.stream>>>(p, CW, total);
+  const long long total16 = (long long)p.B * p.Ho * p.Wo * (p.C / 16);
+  if (p.C % 16 == 0 && total16 < 0x7fffffffLL &&
+      ((reinterpret_cast<uintptr_t>(p.in) | reinterpret_cast<uintptr_t>(p.out)) & 15) == 0)
+    maxpool16_kernel<<<(unsigned)((total16 + 255) / 256), 256, 0, c.stream>>>(p, p.C / 16, (unsigned)total16);
+  else if (vec) maxpool_kernel<true><<<blocks, 256, 0, c.stream>>>(p, CW, total);
   else     maxpool_kernel<false><<<blocks, 256, 0, c.stream>>>(p, CW, total);
   count_launch();
   if (!cuda_ok(cudaGetLastError(), "maxpool launch")) return false;

@@ -98,6 +98,23 @@ def build_case(name, B, pkg):
         x, w, o = dev(c["x"]), dev(c["w"]), out((B, 1000), torch.int32)
         fn = lambda: api.pulp_nn_linear_out_32(32, x, None, o, w, 1024, 1000)  # noqa: E731
         return fn, 2.0 * B * 1024 * 1000, B * (1024 + 4000) + 1024 * 1000, (x, w, o)
+    if name in ("add", "maxpool", "avgpool"):
+        # the byte movers on a 56x56x128 tensor (3 bytes per element for add; 2x2 stride-2 max pool;
+        # the network's 7x7 global average pool on 7x7x1024)
+        if name == "add":
+            a = torch.randint(0, 256, (B, 56, 56, 128), dtype=torch.uint8, device="cuda")
+            b = torch.randint(0, 256, (B, 56, 56, 128), dtype=torch.uint8, device="cuda")
+            o = torch.empty_like(a)
+            return (lambda: api.pulp_nn_add(32, a, b, o, 37, 91, 6, 56, 56, 128)), 0.0, 3 * a.numel(), (a, b, o)
+        if name == "maxpool":
+            x = torch.randint(0, 256, (B, 56, 56, 128), dtype=torch.uint8, device="cuda")
+            o = torch.empty((B, 28, 28, 128), dtype=torch.uint8, device="cuda")
+            return ((lambda: api.pulp_nn_maxpool(32, x, o, 56, 56, 128, 28, 28, 2, 2, 0, 0, 0, 0, 2, 2)), 0.0,
+                    x.numel() + o.numel(), (x, o))
+        x = torch.randint(0, 256, (B, 7, 7, 1024), dtype=torch.uint8, device="cuda")
+        o = torch.empty((B, 1, 1, 1024), dtype=torch.uint8, device="cuda")
+        return ((lambda: api.pulp_nn_avgpool(32, x, o, 0, 0, 0, 7, 7, 1024, 1, 1, 7, 7, 0, 0, 0, 0, 7, 7, 0)), 0.0,
+                x.numel() + o.numel(), (x, o))
     if name in ("chw_to_hwc", "hwc_to_chw"):
         # the layout change a reference-style chain needs before every depthwise call: dw2's tensor
         H, C = 112, 64
