@@ -61,6 +61,76 @@ __global__ void __launch_bounds__(256) transpose_u8_kernel(const uint8_t *in, ui
   }
 }
 
+// The fast path: 128 x 128 byte tiles. Phase 1: 16-byte loads along the input's rows, the words
+// stored in shared memory at word position w ^ ((r >> 2) ^ (r & 3)) of row r. Phase 2: a lane takes
+// four consecutive rows of one word column (four conflict-free 32-bit loads thanks to the swizzle),
+// transposes the 4 x 4 bytes with byte permutes and writes one word to each of four output rows;
+// the lanes of a warp cover 128 consecutive bytes of an output row. Needs cols % 16 == 0,
+// rows % 4 == 0 and aligned buffers; tiles at the edges are clipped chunk-wise.
+constexpr int TB = 128;
+
+__device__ __forceinline__ unsigned prmt(unsigned a, unsigned b, unsigned sel)
+{
+  unsigned d;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+  return d;
+}
+
+__global__ void __launch_bounds__(256) transpose_u8_fast_kernel(const uint8_t *in, uint8_t *out, int rows, int cols,
+                                                                int tiles_r, int tiles_c)
+{
+  __shared__ unsigned tile[TB][TB / 4];
+  int t = blockIdx.x;
+  const int tc = t % tiles_c; t /= tiles_c;
+  const int tr = t % tiles_r;
+  const int b = t / tiles_r;
+  const int r0 = tr * TB, c0 = tc * TB;
+  const uint8_t *src = in + (size_t)b * rows * cols;
+  uint8_t *dst = out + (size_t)b * rows * cols;
+  const int tid = threadIdx.x;
+  // phase 1: thread -> (row, 16-byte chunk): 8 chunks per row, 32 rows per pass, 4 passes
+  {
+    const int ch = tid & 7, rl = tid >> 3;
+    uint4 v[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const int r = r0 + rl + 32 * i, c = c0 + 16 * ch;
+      v[i] = make_uint4(0, 0, 0, 0);
+      if (r < rows && c < cols) v[i] = __ldg(reinterpret_cast<const uint4 *>(src + (size_t)r * cols + c));
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const int r = rl + 32 * i;
+      const int f = ((r >> 2) ^ (r & 3)) & 31;
+      tile[r][(4 * ch + 0) ^ f] = v[i].x; tile[r][(4 * ch + 1) ^ f] = v[i].y;
+      tile[r][(4 * ch + 2) ^ f] = v[i].z; tile[r][(4 * ch + 3) ^ f] = v[i].w;
+    }
+  }
+  __syncthreads();
+  // phase 2: lane = group of four rows, warp = word column (four of them per warp)
+  const int rg = tid & 31, warp = tid >> 5;
+  const int r = r0 + 4 * rg;
+#pragma unroll
+  for (int k = 0; k < 4; k++) {
+    const int cg = warp + 8 * k;
+    unsigned m[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) m[i] = tile[4 * rg + i][cg ^ ((rg ^ i) & 31)];
+    // 4 x 4 byte transpose: w[j] = byte j of m[0..3]
+    const unsigned a = prmt(m[0], m[1], 0x5140), bb = prmt(m[0], m[1], 0x7362);
+    const unsigned cc = prmt(m[2], m[3], 0x5140), d = prmt(m[2], m[3], 0x7362);
+    const unsigned w0 = prmt(a, cc, 0x5410), w1 = prmt(a, cc, 0x7632);
+    const unsigned w2 = prmt(bb, d, 0x5410), w3 = prmt(bb, d, 0x7632);
+    const int c = c0 + 4 * cg;
+    if (r < rows) {
+      if (c + 0 < cols) *reinterpret_cast<unsigned *>(dst + (size_t)(c + 0) * rows + r) = w0;
+      if (c + 1 < cols) *reinterpret_cast<unsigned *>(dst + (size_t)(c + 1) * rows + r) = w1;
+      if (c + 2 < cols) *reinterpret_cast<unsigned *>(dst + (size_t)(c + 2) * rows + r) = w2;
+      if (c + 3 < cols) *reinterpret_cast<unsigned *>(dst + (size_t)(c + 3) * rows + r) = w3;
+    }
+  }
+}
+
 void layout_entry(const char *who, const uint8_t *in, uint8_t *out, int dim_x, int dim_y, int ch, bool to_hwc)
 {
   Context &c = ctx();
@@ -74,6 +144,18 @@ void layout_entry(const char *who, const uint8_t *in, uint8_t *out, int dim_x, i
   if (!st.ok()) return;
   const int hw = dim_x * dim_y;
   const int rows = to_hwc ? ch : hw, cols = to_hwc ? hw : ch;
+  if (cols % 16 == 0 && rows % 4 == 0 && (reinterpret_cast<uintptr_t>(din) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(dout) & 3) == 0) {
+    const int fr = (rows + TB - 1) / TB, fc = (cols + TB - 1) / TB;
+    const long long ftotal = (long long)c.batch * fr * fc;
+    if (ftotal <= 0x7fffffffLL) {
+      transpose_u8_fast_kernel<<<(unsigned)ftotal, 256, 0, c.stream>>>(din, dout, rows, cols, fr, fc);
+      count_launch();
+      if (!cuda_ok(cudaGetLastError(), "transpose launch")) return;
+      st.finish();
+      return;
+    }
+  }
   const int tiles_r = (rows + TS - 1) / TS, tiles_c = (cols + TS - 1) / TS;
   const long long total = (long long)c.batch * tiles_r * tiles_c;
   if (total > 0x7fffffffLL) { set_error(PULPNN_ERR_UNSUPPORTED, "%s: too many tiles", who); return; }

@@ -431,7 +431,8 @@ def test_layout_change(gpu, gpu_host):
     """CHW <-> HWC against numpy's transpose: whole tiles, ragged tiles, sizes that rule out 32-bit
     accesses on either side, and the round trip."""
     rng = np.random.default_rng(63)
-    for (B, Cc, H, W) in ((2, 64, 8, 16), (3, 5, 7, 9), (1, 130, 3, 67), (2, 32, 56, 56), (1, 3, 224, 224)):
+    for (B, Cc, H, W) in ((2, 64, 8, 16), (3, 5, 7, 9), (1, 130, 3, 67), (2, 32, 56, 56), (1, 3, 224, 224),
+                          (2, 144, 20, 20), (1, 256, 16, 24), (3, 64, 112, 112)):
         x = rng.integers(0, 256, size=(B, Cc, H, W), dtype=np.uint8)
         hwc = gpu.chw_to_hwc(x)
         same(hwc, np.ascontiguousarray(x.transpose(0, 2, 3, 1)))
