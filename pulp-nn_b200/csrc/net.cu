@@ -179,7 +179,7 @@ int run_impl(pulpnn_net *net, const uint8_t *input, void *output, int n, int n_l
     int sizes[64];
     int n_slices = 0;
     {
-      const int want = 4;        // measured at batch 1024: 3 or 5 slices lose 2 %, 6 lose 5 %, 8 lose 7 %
+      const int want = 4;        // measured at batch 1024: 5 slices lose 2 %, 6 lose 5 %, 8 lose 7 %
       const int part = (n + want - 1) / want;
       int slice = micro < part ? micro : part;
       while (slice < n && slice * want < n) slice += micro;
