@@ -1,33 +1,44 @@
 // igemm_tc.cu -- u8 x s8 -> s32 GEMM on the sm_100a tensor cores with the requantisation fused
-// into the epilogue. It carries pointwise convolution and the fully connected layers:
+// into the epilogue. It carries the convolutions and the fully connected layers:
 //
 //     D[m][n] = bias[n] + sum_k A[m][k] * W[n][k]      A: activations, [M][K] uint8, K contiguous
 //                                                       W: weights,     [N][K] int8,  K contiguous
 //
-// (the im2col matrix of a 1x1 convolution is the HWC activation tensor itself, and the reference
-// keeps weights as [ch_out][K], 32bit/src/pulp_nn_matmul.c:55-59, so both operands are K-major
-// exactly as they lie in memory).
+// The im2col matrix of a 1x1 convolution is the HWC activation tensor itself, and the reference
+// keeps weights as [ch_out][ky][kx][ch_in] = [ch_out][K] (32bit/src/pulp_nn_matmul.c:55-59), so both
+// operands are K-major exactly as they lie in memory. For a spatial kernel on a multiple of 32
+// input channels the im2col matrix is never built: an m-tile is a patch of TH x TW = 128 output
+// pixels, a K-slab is (filter tap, chunk of ch_in), and its A operand is one 4-D TMA box of the
+// input image (element strides = the convolution's strides, out-of-range fill = the zero padding
+// of 32bit/src/pulp_nn_conv_Ho_parallel.c:80-164).
 //
-// Structure of one CTA (22 warps, persistent over work units = (m-tile, n-tile, k-slice)):
+// Structure of one CTA (24 warps, persistent over work units = (m-tile, n-tile, k-slice)):
 //   warps 0..3, one lane each   TMA producers: a 128-row tile of A and a BN-row tile of W per
 //                      pipeline stage, BKB bytes of K wide (32, 64 or 128, matching swizzle),
 //                      completion on an mbarrier (no multicast). TMA fetches the whole box from L2
 //                      even where it lies outside the tensor, so the box is never wider than K
-//                      needs. When one n-tile covers all of W and it is small, W is loaded ONCE per
-//                      CTA and stays in shared memory; the ring then carries A only. The four
-//                      warps take turns slab by slab: getting one load on its way costs a thread
-//                      several hundred cycles, more than a short-K tile has to spare.
-//   warps 4..5, one lane each   issue tcgen05.mma.kind::i8 (M=128, N=BN, K=32 per instruction),
+//                      needs. When the CTA's n-tile of W fits beside four stages of A it is loaded
+//                      ONCE per CTA and stays in shared memory; the CTA then keeps that n-tile and
+//                      walks down the m-tiles, and the ring carries A only. A stage is always
+//                      refilled by the same warp (stage % 4): getting one load on its way costs a
+//                      thread several hundred cycles, more than a short-K tile has to spare.
+//   warps 4..7, one lane each   issue tcgen05.mma.kind::i8 (M=128, N=BN, K=32 per instruction),
 //                      operands from shared-memory descriptors, accumulator in tensor memory;
-//                      commits free the stage and publish the accumulator. They alternate tiles.
-//   warps 6..21        epilogue, two groups of eight that alternate tiles: tcgen05.ld the
-//                      accumulator (lane = output row), add bias, requantise with per-channel
-//                      k/lambda held in shared memory, pack to bytes and store 32 bytes at a time
-//                      into the HWC output
-// All 512 columns of tensor memory are used as a ring of 512/BN accumulators, so the MMA issuer runs
+//                      commits free the stage and publish the accumulator. They alternate tiles
+//                      (at most one warp per accumulator), ordered by a "tiles landed" counter.
+//   warps 8..23        epilogue: tcgen05.ld the accumulator (lane = output row), requantise with
+//                      per-channel k / lambda' (bias folded in) held in shared memory, pack to
+//                      bytes. 128- and 256-column tiles go through a swizzled staging tile and
+//                      leave with TMA stores (one, or two rounds of 128 columns; 4-D boxes for a
+//                      convolution's patch); 64-column tiles, raw int32 output and partial sums are
+//                      stored from registers. 64- and 128-column tiles are drained by two groups of
+//                      eight warps that alternate tiles, 256-column tiles by all sixteen.
+// All 512 columns of tensor memory are used as a ring of 512/BN accumulators, so the MMA issuers run
 // several tiles ahead of the epilogue. Integer accumulation is associative, so splitting K over
-// several CTAs (used when a problem has too few tiles to fill the GPU) gives bit-identical sums;
-// partial sums then go to a scratch buffer and a second kernel adds them and requantises.
+// several CTAs (used when a problem has very few tiles) gives bit-identical sums; partial sums then
+// go to a scratch buffer and a second kernel adds them and requantises. Rows of a short reduction
+// (K <= 64, N <= 64) are folded two or more to a GEMM row against a block-diagonal copy of W (see
+// launch_igemm_tc).
 //
 // Every wait on an mbarrier is bounded: after about a second the waiting thread raises a flag in
 // shared memory, records a code in a global status word and all roles fall through to the common
