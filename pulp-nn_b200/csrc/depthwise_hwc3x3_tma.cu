@@ -18,7 +18,12 @@
 //
 // Synchronisation per group of rows: one mbarrier wait (data landed), one __syncthreads (all
 // threads finished reading the group and writing the output tile), after which thread 0 issues the
-// store of the tile and the load that refills the group. Every wait is bounded.
+// store of the tile and the load that refills the group. Every wait is bounded. When there are more
+// whole-image columns than CTAs fit on the GPU at once, a CTA works through several consecutive
+// images and its ring of row groups runs on from one image to the next.
+//
+// The second kernel of this file, depthwise_chw3x3_tma_kernel, does the same for the reference's own
+// CHW input layout (see the comment above it): same accumulate / requantise code, different feeding.
 #include <type_traits>
 
 #include "internal.cuh"
