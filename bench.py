@@ -5,10 +5,13 @@
   python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
   python bench.py --impl reference          # the reference's own C code on the host cores
 
-A step is one pass of the 29-call layer stack over one batch of synthetic images (1024 per GPU;
-weak scaling: every GPU keeps 1024 images as N grows, nothing is exchanged but the final logits
-gather). `value` is measured with the batch already resident in HBM; `e2e` is the same metric
-through the C ABI with host buffers (pinned input copied in, logits copied out, every step).
+A step is one pass of the 29-call layer stack over one batch of 1024 synthetic images, sharded by
+batch over the GPUs (strong scaling: 1024/N images per GPU; nothing is exchanged but the final
+logits gather). With N > 1 the weak-scaling figure (1024 images per GPU) is measured in the same run
+and reported under "weak". `value` is measured with the batch already resident in HBM; `e2e` is the
+same metric through the C ABI with host buffers (pinned input copied in, logits copied out, every
+step). At N = 1 the line also carries configurations 1-4, the box's int8 GEMM and pinned-copy rates,
+a sustained run and a parity check of the timed network against the CPU checker.
 Prints ONE JSON line on rank 0.
 """
 import argparse
@@ -41,7 +44,7 @@ def peaks():
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
     Q = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
-        "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+        "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap,power.draw"
 
     def __init__(self, index):
         self.index, self.proc, self.lines = index, None, []
@@ -59,9 +62,9 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.time(), line.strip()))
 
-    def stop(self):
+    def stop(self, keep_samples=False):
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -71,7 +74,8 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
+        trace = []
+        for ts, ln in self.lines:
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 6:
                 continue
@@ -82,9 +86,17 @@ class ClockSampler:
             for n, v in zip(names, f[2:6]):
                 if v.lower().startswith("active"):
                     reasons.add(n)
-        return {"sm_mhz": statistics.median(sm) if sm else None,
-                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
-                "samples": len(sm)}
+            try:
+                watts = float(f[6]) if len(f) > 6 else None
+            except ValueError:
+                watts = None
+            trace.append((ts, sm[-1], watts))
+        out = {"sm_mhz": statistics.median(sm) if sm else None,
+               "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
+               "samples": len(sm)}
+        if keep_samples:
+            out["trace"] = trace
+        return out
 
 
 # ---- CPU arm -----------------------------------------------------------------------------------
@@ -182,7 +194,7 @@ def run_reference_arm(args):
     base["value"] = value
     line = {"impl": "reference", "metric": "MobileNetV1-int8 images/s", "value": value, "unit": "images/s",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": 1000.0 * secs / args.steps, "higher_is_better": True, "scaling": "weak",
+            "ms_per_step": 1000.0 * secs / args.steps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "u8*s8->s32", "data": "synthetic",
             "config": {"workload": WORKLOAD, "per_step": "bounded sample of <=256 images on the host cores"},
             "cpu_baseline": base,
@@ -191,7 +203,49 @@ def run_reference_arm(args):
 
 
 # ---- GPU arm -----------------------------------------------------------------------------------
+def _event_ms(torch, fn, reps):
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(reps):
+        fn()
+    ev1.record()
+    torch.cuda.synchronize()
+    return ev0.elapsed_time(ev1) / reps
+
+
+def measured_traffic_ratio(kernel):
+    """DRAM bytes moved / algorithmic bytes of one launch, from an ncu capture of that kernel at the
+    benchmark's batch (dram__bytes_read.sum + dram__bytes_write.sum); None when no capture is on file."""
+    p = os.path.join(ROOT, "profiles", "dram_traffic_measured.json")
+    if not os.path.exists(p):
+        return None
+    try:
+        return json.load(open(p)).get(kernel)
+    except Exception:
+        return None
+
+
+def single_layer_configs(pkg, torch, hbm_peak, int8_library_pops):
+    """Configurations 1-4 with their literal parameters on device buffers: 200 back-to-back C-ABI
+    calls between two CUDA events, and a CUDA-graph replay of the same 200 calls (calls shorter than
+    about 15 us are paced by the Python call, not by the GPU)."""
+    import layer_bench
+    out = []
+    for name, batch in (("c1", 1), ("c2", 64), ("c3", 64), ("c4", 256), ("c4_out32", 256)):
+        r = layer_bench.run_case(name, batch, 200, pkg, graph=False)
+        g = layer_bench.run_case(name, batch, 200, pkg, graph=True)
+        us = g["ms_per_call"] * 1e3
+        tops = g["GOPs"] / 1e3
+        out.append({"name": name, "batch": batch, "us": round(us, 2), "us_python_calls": round(r["ms_per_call"] * 1e3, 2),
+                    "GOPs": g["GOPs"], "GBs": g["GBs"], "hbm_frac": round(g["GBs"] / hbm_peak, 3),
+                    "tc_frac_nominal": round(tops / 4500.0, 3),
+                    "tc_frac_library": round(tops / int8_library_pops / 1e3, 3) if int8_library_pops else None,
+                    "algorithmic_bytes": g["algorithmic_bytes"]})
+    return out
+
+
 def run_gpu_arm(args):
+    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # peer stores only, no NVLS binding
     import torch
     import torch.distributed as dist
 
@@ -202,88 +256,131 @@ def run_gpu_arm(args):
         raise SystemExit("bench.py needs a CUDA device: this framework has no CPU path "
                          "(use --impl reference for the CPU arm)")
     torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        dist.init_process_group("nccl", device_id=dev)
     pkg = entry.load_package()
     api, wl = pkg.api, pkg.workloads
     api.set_device(local)
     api.set_stream(None)
-
     sharding = __import__("importlib").import_module("pulpnn_b200.sharding")
-    if args.scaling == "strong":      # one batch of --batch images cut into per-rank slices
-        first, last = sharding.shard_bounds(args.batch, rank, world)
-        B, global_batch = last - first, args.batch
-    else:                             # weak: every GPU keeps --batch images
-        B, global_batch = args.batch, args.batch * world
     params = wl.mobilenet_params(seed=4, bits=32, shift_bias=11)
-    net = api.build_mobilenet_v1(params, bits=32, max_batch=B, micro_batch=args.micro)
-    x_host = torch.from_numpy(wl.mobilenet_input(100 + rank, B)).pin_memory()
-    x_dev = x_host.cuda()
-    logits = torch.zeros((B, 1000), dtype=torch.int32, device="cuda")
-    logits_host = torch.zeros((B, 1000), dtype=torch.int32).pin_memory()
-
-    def step():
-        net.run(x_dev, logits, B)
-        if world > 1:   # the only exchange of the whole path: the final logits gather
-            sharding.gather_rows(logits, global_batch)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
+    def make_gather(n_total):
+        if world == 1:
+            return None
+        if args.gather in ("auto", "peer"):
+            try:
+                return sharding.PeerLogits(n_total, 1000, torch.int32, rank, world, dev)
+            except Exception as exc:      # no symmetric memory on this box
+                if args.gather == "peer":
+                    raise
+                print("peer-mapped logits unavailable (%s): NCCL all-gather on a side stream" % exc)
+        return sharding.OverlappedGather(n_total, 1000, torch.int32, rank, world, dev)
+
+    class Job:
+        """One scaling mode: this rank's slice of a global batch, its network and its buffers."""
+
+        def __init__(self, global_batch):
+            first, last = sharding.shard_bounds(global_batch, rank, world)
+            self.B, self.global_batch = last - first, global_batch
+            self.net = api.build_mobilenet_v1(params, bits=32, max_batch=self.B, micro_batch=args.micro)
+            seed = 100 if world == 1 else 100 + rank
+            self.x_host = torch.from_numpy(wl.mobilenet_input(seed, self.B)).pin_memory()
+            self.x_dev = self.x_host.cuda()
+            self.logits = torch.zeros((self.B, 1000), dtype=torch.int32, device="cuda")
+            self.logits_host = torch.zeros((self.B, 1000), dtype=torch.int32).pin_memory()
+            self.gather = make_gather(global_batch)
+
+        def step(self):
+            if self.gather is None:
+                self.net.run(self.x_dev, self.logits, self.B)
+            else:   # the only exchange of the whole path: the final logits gather
+                self.net.run(self.x_dev, self.gather.target(), self.B)
+                self.gather.publish()
+
+        def step_e2e(self):
+            self.net.run(self.x_host, self.logits_host, self.B)
+
+        def timed(self, fn, steps):
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            barrier()
+            ev0.record()
+            for _ in range(steps):
+                fn()
+            if self.gather is not None and fn == self.step:
+                self.gather.finish()
+            ev1.record()
+            barrier()
+            ms = ev0.elapsed_time(ev1)
+            if world > 1:
+                t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ms = float(t.item())
+            return ms
+
+    strong = args.scaling == "strong"
+    job = Job(args.batch if strong else args.batch * world)
+    B, global_batch = job.B, job.global_batch
+    warm = max(args.warmup, 3)
+
     # the clock sampler needs a moment to come up: start it before the warm-up and keep the GPU
     # busy until its first samples are in, so that the timed region is covered
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    for _ in range(max(args.warmup, 3)):
-        step()
+    for _ in range(warm):
+        job.step()
     if world == 1:
         t_wait = time.time()
         while len(sampler.lines) < 2 and time.time() - t_wait < 3.0:
-            step()
+            job.step()
     else:
-        for _ in range(200):        # same count on every rank: the step contains a collective
-            step()
+        for _ in range(200):        # same count on every rank
+            job.step()
     barrier()
     launches0 = api.launch_count()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    ev0.record()
-    for _ in range(args.steps):
-        step()
-    ev1.record()
-    barrier()
-    ms = ev0.elapsed_time(ev1)
+    ms = job.timed(job.step, args.steps)
     launches = api.launch_count() - launches0
     clocks = sampler.stop() if rank == 0 else None
 
     # end to end through the C ABI with host buffers
     for _ in range(2):
-        net.run(x_host, logits_host, B)
-    barrier()
-    ev0.record()
-    for _ in range(args.steps):
-        net.run(x_host, logits_host, B)
-    ev1.record()
-    barrier()
-    ms_e2e = ev0.elapsed_time(ev1)
+        job.step_e2e()
+    ms_e2e = job.timed(job.step_e2e, args.steps)
 
     # per-layer times (events between layer calls), averaged over a few runs
-    layer_ms = np.zeros(net.num_layers())
+    layer_ms = np.zeros(job.net.num_layers())
     reps = max(3, min(args.steps, 10))
     for _ in range(reps):
-        layer_ms += np.array(net.run_timed(x_dev, logits, B))
+        layer_ms += np.array(job.net.run_timed(job.x_dev, job.logits, B))
     layer_ms /= reps
     assert api.device_status() == 0, "a bounded wait inside a tensor-core kernel ran out"
 
-    if world > 1:
-        t = torch.tensor([ms, ms_e2e], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, ms_e2e = t.tolist()
+    # the other scaling mode, in the same run (N > 1 only; at N = 1 the two coincide)
+    other = None
+    if world > 1 and not args.no_extras:
+        job2 = Job(args.batch * world if strong else args.batch)
+        for _ in range(warm + 20):
+            job2.step()
+        ms2 = job2.timed(job2.step, args.steps)
+        for _ in range(2):
+            job2.step_e2e()
+        ms2_e2e = job2.timed(job2.step_e2e, args.steps)
+        other = {"scaling": "weak" if strong else "strong", "per_gpu_batch": job2.B, "global_batch": job2.global_batch,
+                 "value": round(job2.global_batch * args.steps / (ms2 / 1e3), 1), "unit": "images/s",
+                 "ms_per_step": round(ms2 / args.steps, 4),
+                 "e2e_value": round(job2.global_batch * args.steps / (ms2_e2e / 1e3), 1)}
+        del job2
+
     if rank != 0:
         if world > 1:
+            barrier()
             dist.destroy_process_group()
         return
 
@@ -296,7 +393,8 @@ def run_gpu_arm(args):
         gop = r["ops"] * B / 1e9
         per_layer.append({"layer": L["name"], "ms": round(float(t_ms), 4),
                           "GOPs": round(gop / (t_ms / 1e3), 1), "GBs": round(gb / (t_ms / 1e3), 1),
-                          "hbm_frac": round(gb / (t_ms / 1e3) / hbm_peak, 3)})
+                          "hbm_frac": round(gb / (t_ms / 1e3) / hbm_peak, 3),
+                          "tc_frac_nominal": round(gop / (t_ms / 1e3) / 4.5e6, 3)})
         kname = {"conv": "conv_smallcin_tc_kernel", "depthwise": "depthwise_hwc3x3_tma_kernel",
                  "pointwise": "igemm_tc_kernel", "avgpool": "avgpool_kernel",
                  "linear32": "igemm_tc_kernel"}[L["op"]]
@@ -305,17 +403,14 @@ def run_gpu_arm(args):
     top = max(by_kernel, key=lambda n: by_kernel[n]["ms"])
     tk = by_kernel[top]
     achieved = tk["bytes"] / 1e9 / (tk["ms"] / 1e3)
-    # DRAM bytes per launch. The ncu captures (profiles/*_ncu_full.md, batch 128/256 because a
-    # batch-1024 capture is too large to profile safely) show dram__bytes_read equal to the input
-    # operand to within 0.1 % for all three kernels; their outputs at batch 1024 are several times
-    # L2 and are written once, so traffic scales with the batch and equals the algorithmic bytes.
-    dram_over_algorithmic = {"igemm_tc_kernel": 1.001, "depthwise_hwc3x3_tma_kernel": 1.000,
-                             "conv_smallcin_tc_kernel": 1.002}
-    traffic = None
-    if top in dram_over_algorithmic:
-        traffic = int(dram_over_algorithmic[top] * tk["bytes"] / tk["launches"])
+    traffic, traffic_src = None, None
+    m = measured_traffic_ratio(top)
+    if m:
+        traffic = int(m["dram_over_algorithmic"] * tk["bytes"] / tk["launches"])
+        traffic_src = m.get("source")
     roofline = {"bound": "hbm", "kernel": top, "achieved": round(achieved, 1), "peak": hbm_peak,
                 "unit": "GB/s", "frac": round(achieved / hbm_peak, 4), "traffic": traffic,
+                "traffic_source": traffic_src,
                 "peak_source": "of %s" % peak_kind,
                 "launches_per_step": tk["launches"], "avg_launch_ms": round(tk["ms"] / tk["launches"], 4),
                 "algorithmic_bytes_per_launch": int(tk["bytes"] / tk["launches"]),
@@ -323,19 +418,67 @@ def run_gpu_arm(args):
 
     images = global_batch * args.steps
     value = images / (ms / 1e3)
+    gather_kind = job.gather.kind if job.gather is not None else "none (one GPU)"
     line = {"metric": "MobileNetV1-int8 images/s", "value": round(value, 1), "unit": "images/s",
-            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "n_gpus": world, "steps": args.steps, "warmup": warm,
             "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True, "scaling": args.scaling,
             "vs_baseline": None, "dtype": "u8*s8->s32", "data": "synthetic",
             "config": {"workload": WORKLOAD, "per_gpu_batch": B, "global_batch": global_batch,
-                       "micro_batch": args.micro, "parallelism": "batch-sharded x%d, logits all-gather" % world,
-                       "l2": "inputs larger than L2 (154 MB of images per step)"},
+                       "micro_batch": args.micro, "parallelism": "batch-sharded x%d" % world,
+                       "logits_gather": gather_kind,
+                       "l2": "inputs larger than L2 (154 MB of images per step)" if B * 150528 > 126e6 else
+                             "per-GPU input %.0f MB: the first layer's input is re-read from HBM every step "
+                             "(the 29 layers between two reads of it move %.0f MB)" % (B * 0.150528, B * 10.24)},
             "clocks": clocks,
             "e2e": {"value": round(images / (ms_e2e / 1e3), 1), "unit": "images/s",
-                    "h2d_bytes_per_step": int(x_host.numel()), "d2h_bytes_per_step": int(logits_host.numel() * 4)},
+                    "h2d_bytes_per_step": int(job.x_host.numel()), "d2h_bytes_per_step": int(job.logits_host.numel() * 4)},
             "gpu_launches": int(launches),
             "roofline": roofline,
             "per_layer": per_layer}
+    if other:
+        line[other["scaling"]] = other
+
+    if world == 1 and not args.no_extras:
+        import layer_bench
+        # the box's practical int8 tensor peak and its pinned host-to-device copy rate: the
+        # denominators of the tensor-bound layers and of the end-to-end figure
+        ip = layer_bench.int8_peak(5)
+        line["int8_peak"] = {"nominal_pops": 4.5, "library_pops": round(ip["TOPs"] / 1e3, 3), "how": ip["how"]}
+        best = min(_event_ms(torch, lambda: job.x_dev.copy_(job.x_host, non_blocking=True), 1) for _ in range(5))
+        h2d_gbs = job.x_host.numel() / best / 1e6
+        e2e_ms = ms_e2e / args.steps
+        line["e2e"].update({"h2d_gbs_measured": round(h2d_gbs, 2), "h2d_copy_ms": round(best, 4),
+                            "ms_per_step": round(e2e_ms, 4), "frac_of_copy": round(best / e2e_ms, 3)})
+        for pl in per_layer:
+            pl["tc_frac_library"] = round(pl["GOPs"] / 1e3 / ip["TOPs"], 3)
+        line["configs"] = single_layer_configs(pkg, torch, hbm_peak, ip["TOPs"] / 1e3)
+        api.set_batch(1)
+
+        # sustained: the same step in blocks for >= 3 s, with the clocks sampled meanwhile
+        s2 = ClockSampler(local)
+        s2.start()
+        blocks, t_end = [], time.time() + args.sustain
+        per_block = max(1, int(0.25 / (ms / args.steps / 1e3)))
+        while time.time() < t_end:
+            t0 = time.time()
+            bms = _event_ms(torch, job.step, per_block) * per_block
+            blocks.append((t0, time.time(), B * per_block / (bms / 1e3)))
+        clk = s2.stop(keep_samples=True)
+        out_blocks = []
+        for (t0, t1, ips) in blocks:
+            mhz = [v for (ts, v, _) in clk.get("trace", []) if t0 <= ts <= t1]
+            out_blocks.append([round(ips, 1), statistics.median(mhz) if mhz else None])
+        tail = [b for b in blocks if b[1] >= blocks[-1][1] - 1.0]
+        pw = [w for (_, _, w) in clk.get("trace", []) if w is not None]
+        line["sustained"] = {"seconds": round(blocks[-1][1] - blocks[0][0], 2),
+                             "value": round(sum(b[2] for b in tail) / len(tail), 1), "unit": "images/s",
+                             "sm_mhz_median": clk["sm_mhz"], "power_w_max": max(pw) if pw else None,
+                             "reasons": clk["reasons"], "blocks": out_blocks[:: max(1, len(out_blocks) // 16)]}
+
+        # what was timed is also what is checked: the same layer stack at the same batch, with
+        # live requantisation parameters, against the CPU checker on sampled images
+        line["parity_checked"] = parity_check(pkg, torch, job, params, args)
+
     if world == 1 and not args.no_cpu:
         # in a process of its own: the reference harness wants a low-address arena, and a process
         # that has CUDA loaded may already have that address range mapped
@@ -349,7 +492,69 @@ def run_gpu_arm(args):
                                     "sample": "CPU baseline run failed: " + (r.stderr.strip().splitlines() or ["?"])[-1][:200]}
     print(json.dumps(line), flush=True)
     if world > 1:
+        barrier()
         dist.destroy_process_group()
+
+
+PARITY_SAMPLE = [0, 1, 255, 256, 511, 512, 767, 768, 1022, 1023]
+
+
+def parity_check(pkg, torch, job, timed_params, args):
+    """Runs the benchmark's layer stack once more at the benchmark's batch -- with the literal
+    parameters (the timed network object itself) and with live ones (same shapes, so the same
+    kernels and branches) -- and compares sampled images' logits with the CPU checker, which runs
+    in a child process (`--impl parity-oracle`)."""
+    import tempfile
+    api, wl = pkg.api, pkg.workloads
+    B = job.B
+    sample = sorted({i for i in PARITY_SAMPLE if i < B} | {B - 1})
+    res = {"images": 0, "equal": None}
+    with tempfile.TemporaryDirectory() as tmp:
+        got = {}
+        job.net.run(job.x_dev, job.logits, B)
+        api.synchronize()
+        got["literal"] = job.logits.cpu().numpy()[sample]
+        live = wl.mobilenet_params(seed=4, bits=32, shift_bias=1)
+        net = api.build_mobilenet_v1(live, bits=32, max_batch=B, micro_batch=args.micro)
+        net.run(job.x_dev, job.logits, B)
+        api.synchronize()
+        got["live"] = job.logits.cpu().numpy()[sample]
+        host_logits = np.zeros((B, 1000), np.int32)
+        net.run(job.x_host, host_logits, B)
+        got["live_host_input"] = host_logits[sample]
+        net.close()
+        np.save(os.path.join(tmp, "x.npy"), job.x_host.numpy()[sample])
+        r = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "parity-oracle", "--tmp", tmp],
+                           capture_output=True, text=True, timeout=600)
+        if r.returncode != 0:
+            res["error"] = (r.stderr.strip().splitlines() or ["?"])[-1][:200]
+            return res
+        want_lit, want_live = np.load(os.path.join(tmp, "literal.npy")), np.load(os.path.join(tmp, "live.npy"))
+        eq = {"literal": bool(np.array_equal(got["literal"], want_lit)),
+              "live": bool(np.array_equal(got["live"], want_live)),
+              "live_host_input": bool(np.array_equal(got["live_host_input"], want_live))}
+        res = {"images": len(sample), "image_indices": sample, "batch": B, "equal": all(eq.values()), "cases": eq,
+               "distinct_logit_values_live": int(len(np.unique(want_live))),
+               "checker": r.stdout.strip().splitlines()[-1] if r.stdout.strip() else "?"}
+    return res
+
+
+def run_parity_oracle(args):
+    """Child of parity_check: the CPU checker's logits for the sampled images (the compiled
+    reference when it was built on this machine, else the C restatement)."""
+    from oracle import bindings
+    from oracle.netref import mobilenet_chain
+    pkg = entry.load_package()
+    wl = pkg.workloads
+    x = np.load(os.path.join(args.tmp, "x.npy"))
+    if bindings.have_reference(32):
+        impl, kind = bindings.CompiledReference(32, arena_mb=256, threads=os.cpu_count() or 1), "compiled reference"
+    else:
+        impl, kind = bindings.Restatement(), "C restatement"
+    for name, sb in (("literal", 11), ("live", 1)):
+        params = wl.mobilenet_params(seed=4, bits=32, shift_bias=sb)
+        np.save(os.path.join(args.tmp, name + ".npy"), mobilenet_chain(impl, params, x)[-1])
+    print(kind)
 
 
 def main():
@@ -357,10 +562,19 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--batch", type=int, default=1024, help="images per GPU")
-    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
-                    help="weak: --batch images per GPU; strong: --batch images in total, sliced over the GPUs")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "parity-oracle"])
+    ap.add_argument("--batch", type=int, default=1024, help="images: in total (strong scaling) or per GPU (weak)")
+    ap.add_argument("--scaling", default="strong", choices=["weak", "strong"],
+                    help="strong (the configuration the metric is quoted on): --batch images in total, sliced over "
+                         "the GPUs; weak: --batch images per GPU. With more than one GPU the other mode is measured "
+                         "too and reported under its own key.")
+    ap.add_argument("--gather", default="auto", choices=["auto", "peer", "nccl"],
+                    help="final logits gather: stores into the root's peer-mapped buffer, or an NCCL all-gather "
+                         "on a side stream")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the single-layer configurations, the sustained run and the parity check")
+    ap.add_argument("--sustain", type=float, default=3.0, help="seconds of the sustained run")
+    ap.add_argument("--tmp", default="", help="(internal) exchange directory of the parity check")
     ap.add_argument("--micro", type=int, default=0, help="images per pass through the stack (0 = all)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--budget", type=float, default=0.0, help="reference arm: seconds of CPU work per step")
@@ -379,6 +593,8 @@ def main():
     try:
         if args.impl == "reference":
             run_reference_arm(args)
+        elif args.impl == "parity-oracle":
+            run_parity_oracle(args)
         else:
             run_gpu_arm(args)
     finally:

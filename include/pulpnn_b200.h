@@ -216,8 +216,9 @@ void pulpnn_i2_to_i8(const int8_t *pSrc, int8_t *pDst, unsigned int n);
  * library image (every GPU that loads the library holds it until the process exits), and the
  * call uses no cudaMalloc, cudaFree or any other allocating routine.
  *
- *  - All four buffers must be DEVICE memory, 16-byte aligned (host buffers would need staging
- *    memory); bias may be NULL; dim_vec must be a multiple of 16.
+ *  - All four buffers must be device (or managed) memory of the context's GPU -- host buffers
+ *    would need staging memory; pInBuffer and pWeights 16-byte aligned, pOutBuffer and bias
+ *    4-byte aligned; bias may be NULL; dim_vec must be a multiple of 16.
  *  - Limit: k_slices * n_vectors * num_o_neurons <= 1048576 partial sums (k_slices >= 2, and
  *    dim_vec long enough to split); anything larger is refused with PULPNN_ERR_UNSUPPORTED.
  *  - The first call on a device looks up the array's device address; make that first call
@@ -226,10 +227,25 @@ void pulpnn_i2_to_i8(const int8_t *pSrc, int8_t *pDst, unsigned int n);
  *    has to start at zero (each call writes every partial sum it later reads), but two calls
  *    whose kernels overlap on the GPU -- different streams, different host threads -- race.
  *  - Enqueues on the calling thread's stream and returns a status (PULPNN_OK or an error code).
+ *  - A bounded wait that runs out inside its kernel is recorded in a status word that is built
+ *    into the library as well, and shows up in pulpnn_device_status() like any other.
  */
 int pulpnn_linear_out_32_static_scratch(const uint8_t *pInBuffer, const int32_t *bias,
                                         int32_t *pOutBuffer, const int8_t *pWeights, int dim_vec,
                                         int num_o_neurons, int n_vectors, int k_slices);
+
+/*
+ * pulpnn_selftest_wait_timeout -- diagnostic, no counterpart in the reference.
+ *
+ * Every wait inside the TMA / tensor-core kernels is bounded: when it runs out the kernel leaves
+ * through its ordinary exit and records a code in the device status word. This call exercises
+ * exactly that path without disturbing anything: a one-warp kernel waits, with the given limit
+ * (microseconds, clamped to 1..100000), on a barrier that nothing will ever complete. After it,
+ * pulpnn_device_status() returns a non-zero code (and clears it) and pulpnn_last_error() is
+ * PULPNN_ERR_DEVICE_WAIT; the GPU and the context stay usable. Returns PULPNN_OK when the
+ * kernel was enqueued.
+ */
+int pulpnn_selftest_wait_timeout(unsigned int limit_us);
 
 /* ---- sequential network runner --------------------------------------------
  * The reference is a kernel library; its user chains the calls. This runner is
@@ -283,6 +299,8 @@ int  pulpnn_net_run_timed(pulpnn_net_t *net, const uint8_t *input, void *output,
                           float *layer_ms);
 int  pulpnn_net_num_layers(const pulpnn_net_t *net);
 size_t pulpnn_net_layer_output_bytes(const pulpnn_net_t *net, int layer);   /* per image */
+/* Kernel launches the most recent pulpnn_net_run / _run_prefix / _run_timed of this network made
+ * (0 before the first run). n_images is ignored. */
 unsigned long long pulpnn_net_launches_per_run(const pulpnn_net_t *net, int n_images);
 void pulpnn_net_destroy(pulpnn_net_t *net);
 

@@ -2,13 +2,13 @@
 """Single-kernel measurements: the four single-layer benchmark configurations and the layer shapes
 of MobileNetV1, one C-ABI call each, timed with CUDA events on device-resident buffers.
 
-    python pulp-nn_b200/layer_bench.py --case c2            # pointwise 56x56x128 -> 256, batch 64
-    python pulp-nn_b200/layer_bench.py --case pw1 --batch 128 --reps 3
-    python pulp-nn_b200/layer_bench.py --all
+    python layer_bench.py --case c2            # pointwise 56x56x128 -> 256, batch 64
+    python layer_bench.py --case pw1 --batch 128 --reps 3
+    python layer_bench.py --all
 
 Prints one JSON line per case: milliseconds per call, GOP/s, algorithmic GB/s and the fraction of
-the measured HBM bandwidth (MEASURED_PEAKS.json beside the repository root, if present). Also the
-command used for the ncu captures summarised under profiles/ (small batch, few repetitions).
+the measured HBM bandwidth (MEASURED_PEAKS.json at the repository root, if present). With a small
+batch and few repetitions it is also the command to profile one kernel in isolation.
 """
 import argparse
 import json
@@ -17,7 +17,7 @@ import sys
 
 import numpy as np
 
-ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 import __graft_entry__ as entry  # noqa: E402
 

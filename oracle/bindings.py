@@ -26,11 +26,22 @@ _u8p = C.POINTER(C.c_uint8)
 _vp = C.c_void_p
 
 
+def reference_dir():
+    """Where the PULP-NN tree lies: $PULPNN_REF_DIR, else a directory `reference` beside the
+    repository. None when neither holds the sources (then only the restatement is built)."""
+    cands = [os.environ.get("PULPNN_REF_DIR"),
+             os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")]
+    for d in cands:
+        if d and os.path.isdir(os.path.join(d, "32bit", "src")):
+            return d
+    return None
+
+
 def build(ref_dir=None):
     """Compile the restatement, and the reference harness when the tree is there."""
     subprocess.run(["make", "-s", "-C", HERE, "oracle"], check=True)
-    ref_dir = ref_dir or os.environ.get("PULPNN_REF_DIR", "/root/reference")
-    if os.path.isdir(os.path.join(ref_dir, "32bit", "src")):
+    ref_dir = ref_dir or reference_dir()
+    if ref_dir:
         subprocess.run(["make", "-s", "-C", HERE, "ref", "PULPNN_REF_DIR=" + ref_dir], check=True)
 
 

@@ -1,4 +1,4 @@
-"""The MobileNetV1 call chain on a CPU checker: conv1, 13 x (depthwise, pointwise), avgpool, fc.
+"""TEST INFRASTRUCTURE ONLY. The MobileNetV1 call chain on a CPU checker: conv1, 13 x (depthwise, pointwise), avgpool, fc.
 
 Returns every layer's output so the GPU runner can be compared layer by layer. Depthwise layers
 are evaluated on HWC input (the checker's arithmetic is layout-independent; the compiled

@@ -46,6 +46,30 @@ def smoke():
         assert np.array_equal(gpu.depthwise(64, c["x"], c["w"], c["k"], c["lam"], **kw),
                               cpu.depthwise(64, c["x"], c["w"], c["k"], c["lam"], **kw)), "depthwise differs"
 
+    # a three-layer network through the runner: depthwise 3x3 -> pointwise -> global average pool
+    rng = np.random.default_rng(104)
+    B, H, Cc, Co = 4, 14, 64, 128
+    x = rng.integers(0, 256, size=(B, H, H, Cc), dtype=np.uint8)
+    dw = wl.depthwise_case(105, H, H, Cc, batch=1, bits=32, out_shift=9, hwc=True)
+    pw = wl.pointwise_case(106, H, H, Cc, Co, batch=1, bits=32, out_shift=10)
+    net = api.Net(32, B)
+    net.add_layer(api.LAYER_DEPTHWISE, dim_in=(H, H), ch_in=Cc, dim_out=(H, H), ch_out=Cc, kernel=(3, 3),
+                  pads=(1, 1, 1, 1), out_shift=9, weights=dw["w"], k=dw["k"], lam=dw["lam"])
+    net.add_layer(api.LAYER_POINTWISE, dim_in=(H, H), ch_in=Cc, dim_out=(H, H), ch_out=Co, out_shift=10,
+                  weights=pw["w"], k=pw["k"], lam=pw["lam"])
+    net.add_layer(api.LAYER_AVGPOOL, dim_in=(H, H), ch_in=Co, dim_out=(1, 1), ch_out=Co, kernel=(H, H), strides=(H, H))
+    net.finalize()
+    got = np.zeros((B, 1, 1, Co), np.uint8)
+    net.run(x, got, B)
+    net.close()
+    t = cpu.depthwise(32, x, dw["w"], dw["k"], dw["lam"], out_shift=9, out_hw=(H, H), kernel=(3, 3),
+                      pads=(1, 1, 1, 1), strides=(1, 1), in_is_hwc=True)
+    t = cpu.pointwise(32, t, pw["w"], pw["k"], pw["lam"], out_shift=10)
+    t = cpu.avgpool(32, t, out_hw=(1, 1), kernel=(H, H), pads=(0, 0, 0, 0), strides=(H, H))
+    assert np.array_equal(got, t), "the network runner differs from the chain of checker calls"
+    assert np.count_nonzero(t) > t.size // 4
+    assert api.device_status() == 0, "a bounded wait inside a kernel ran out"
+
     assert api.launch_count() > launches0, "no kernel of this library was launched"
     print("smoke ok: %d kernel launches, outputs identical to the CPU checker"
           % (api.launch_count() - launches0))

@@ -16,7 +16,14 @@ Context &ctx()
   return c;
 }
 
-void count_launch(unsigned n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+static thread_local unsigned long long t_launches = 0;
+
+void count_launch(unsigned n)
+{
+  g_launches.fetch_add(n, std::memory_order_relaxed);
+  t_launches += n;
+}
+unsigned long long thread_launch_count() { return t_launches; }
 
 void set_error(int code, const char *fmt, ...)
 {
@@ -209,14 +216,18 @@ int pulpnn_device_status(void)
 {
   Context &c = ctx();
   if (!ensure_device(c)) return -1;
-  if (!c.status_word) return 0;
-  int v = 0;
   if (!cuda_ok(cudaStreamSynchronize(c.stream), "cudaStreamSynchronize")) return -1;
-  if (!cuda_ok(cudaMemcpy(&v, c.status_word, sizeof(int), cudaMemcpyDeviceToHost), "status read")) return -1;
-  if (v != 0) {
-    cudaMemset(c.status_word, 0, sizeof(int));
-    set_error(PULPNN_ERR_DEVICE_WAIT, "a bounded wait inside a tensor-core kernel ran out (code 0x%x)", v);
+  int v = 0;
+  if (c.status_word) {
+    if (!cuda_ok(cudaMemcpy(&v, c.status_word, sizeof(int), cudaMemcpyDeviceToHost), "status read")) return -1;
+    if (v != 0) cudaMemset(c.status_word, 0, sizeof(int));
   }
+  // the entry point that must not allocate keeps its own word inside the library image
+  const int s = static_scratch_status_take(c);
+  if (s < 0) return -1;
+  v |= s;
+  if (v != 0)
+    set_error(PULPNN_ERR_DEVICE_WAIT, "a bounded wait inside a tensor-core kernel ran out (code 0x%x)", v);
   return v;
 }
 

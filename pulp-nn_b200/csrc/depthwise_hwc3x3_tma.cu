@@ -760,7 +760,8 @@ bool launch_geo(Context &c, const DepthwiseProblem &p)
   g.status = ctx_status_word(c);
   if (!g.status) return false;
   auto kern = depthwise_hwc3x3_tma_kernel<MODE, S, NGX, CI>;
-  static thread_local int resident = 0;     // CTAs of this instantiation that fit on one SM
+  static PerDeviceInt resident_on;          // CTAs of this instantiation that fit on one SM, per device
+  int resident = resident_on.get(c.device);
   if (resident == 0) {
     if (!cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM),
                  "cudaFuncSetAttribute(depthwise_hwc3x3_tma)"))
@@ -768,6 +769,7 @@ bool launch_geo(Context &c, const DepthwiseProblem &p)
     int n = 0;
     if (!cuda_ok(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, G::THREADS, G::SMEM), "occupancy query")) return false;
     resident = n > 0 ? n : 1;
+    resident_on.set(c.device, resident);
   }
   // Strips down the height only when whole columns leave the GPU short of CTAs (small batches): a
   // strip boundary costs one extra group of input rows.
@@ -841,12 +843,12 @@ bool launch_chw_geo(Context &c, const DepthwiseProblem &p)
   if (!g.status) return false;
   const int smem = 128 + G::HEADER + RING * g.stage_bytes + 2 * G::TILE_BYTES;
   auto kern = depthwise_chw3x3_tma_kernel<MODE, S, LPQ>;
-  static thread_local int smem_set = 0;
-  if (smem > smem_set) {
+  static PerDeviceInt smem_set;             // largest dynamic shared memory asked for so far, per device
+  if (smem > smem_set.get(c.device)) {
     if (!cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
                  "cudaFuncSetAttribute(depthwise_chw3x3_tma)"))
       return false;
-    smem_set = smem;
+    smem_set.set(c.device, smem);
   }
   int resident = 0;
   if (!cuda_ok(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, kern, G::THREADS, smem), "occupancy query")) return false;

@@ -704,12 +704,12 @@ bool launch_cfg(Context &c, const TcMaps &m, const TcParams &g, int grid)
 {
   using L = SmemLayout<BN_TILE, TMA_OUT>;
   auto kern = igemm_tc_kernel<MODE, BN_TILE, BKB, PARTIAL, TMA_OUT>;
-  static bool attr_set = false;     // per instantiation
-  if (!attr_set) {
+  static PerDeviceInt attr_set;     // per instantiation and device
+  if (!attr_set.get(c.device)) {
     if (!cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL),
                  "cudaFuncSetAttribute(igemm_tc)"))
       return false;
-    attr_set = true;
+    attr_set.set(c.device, 1);
   }
   // every configuration asks for more than half of an SM's shared memory, so exactly one CTA (and
   // its 512 tensor-memory columns) lives on an SM
@@ -809,11 +809,24 @@ bool launch_igemm_tc(Context &c, const ConvProblem &p)
     }
     if (fold > 1) {
       const size_t wbytes = (size_t)g.N * fold * g.K * fold;
-      int8_t *wf = static_cast<int8_t *>(ctx_scratch(c, wbytes));
-      if (!wf) return false;
-      fold_weights_kernel<<<(unsigned)((wbytes / 16 + 255) / 256), 256, 0, c.stream>>>(p.w, wf, g.N, g.K, fold);
-      count_launch();
-      if (!cuda_ok(cudaGetLastError(), "fold_weights launch")) return false;
+      int slot = 0;
+      while ((1 << slot) < fold) slot++;
+      int8_t *wf = p.folded ? p.folded->w[slot] : nullptr;
+      if (!wf) {
+        // a layer of a network keeps its folded copy (constant weights: folded once); a one-off
+        // call folds into the context's scratch every time
+        if (p.folded) {
+          void *mem = nullptr;
+          if (!cuda_ok(cudaMalloc(&mem, wbytes), "cudaMalloc(folded weights)")) return false;
+          wf = p.folded->w[slot] = static_cast<int8_t *>(mem);
+        } else {
+          wf = static_cast<int8_t *>(ctx_scratch(c, wbytes));
+          if (!wf) return false;
+        }
+        fold_weights_kernel<<<(unsigned)((wbytes / 16 + 255) / 256), 256, 0, c.stream>>>(p.w, wf, g.N, g.K, fold);
+        count_launch();
+        if (!cuda_ok(cudaGetLastError(), "fold_weights launch")) return false;
+      }
       w_used = wf;
       g.M /= fold; g.N *= fold; g.K *= fold;
     }
@@ -931,27 +944,50 @@ bool launch_igemm_tc(Context &c, const ConvProblem &p)
 // uses it touches no allocator at all.
 constexpr size_t STATIC_SCRATCH_INTS = 1u << 20;                      // 4 MiB of int32 partial sums
 static __device__ __align__(256) int g_static_partials[STATIC_SCRATCH_INTS];
+// The ordinary paths report a bounded wait that ran out through a status word obtained with
+// cudaMalloc; this path has its own, built into the library image like the array above.
+static __device__ int g_static_status;
 
 namespace {
-constexpr int MAX_DEVICES = 64;
-int *g_static_partials_dev[MAX_DEVICES] = {};     // device address of the array, per device
+std::atomic<int *> g_static_partials_dev[MAX_DEVICES];    // device address of the array, per device
+std::atomic<int *> g_static_status_dev[MAX_DEVICES];      // device address of the status word
 
-// In host code the name g_static_partials is only a handle for the runtime; the address a kernel
-// can use has to be asked for, once per device, with that device current.
-int *static_partials_for_current_device(Context &c)
+// In host code the names g_static_partials / g_static_status are only handles for the runtime; the
+// addresses a kernel can use have to be asked for, once per device, with that device current.
+bool static_symbols_for_current_device(Context &c, int **partials, int **status)
 {
   if (c.device < 0 || c.device >= MAX_DEVICES) {
     set_error(PULPNN_ERR_INVALID_ARG, "device index %d outside 0..%d", c.device, MAX_DEVICES - 1);
-    return nullptr;
+    return false;
   }
-  if (!g_static_partials_dev[c.device]) {
-    void *p = nullptr;
-    if (!cuda_ok(cudaGetSymbolAddress(&p, g_static_partials), "cudaGetSymbolAddress(static scratch)")) return nullptr;
-    g_static_partials_dev[c.device] = static_cast<int *>(p);
+  int *pp = g_static_partials_dev[c.device].load(std::memory_order_acquire);
+  int *ps = g_static_status_dev[c.device].load(std::memory_order_acquire);
+  if (!pp || !ps) {
+    void *a = nullptr, *b = nullptr;
+    if (!cuda_ok(cudaGetSymbolAddress(&a, g_static_partials), "cudaGetSymbolAddress(static scratch)")) return false;
+    if (!cuda_ok(cudaGetSymbolAddress(&b, g_static_status), "cudaGetSymbolAddress(static status)")) return false;
+    pp = static_cast<int *>(a); ps = static_cast<int *>(b);
+    // a module's __device__ variables start at zero, so the status word needs no clearing here
+    g_static_status_dev[c.device].store(ps, std::memory_order_release);
+    g_static_partials_dev[c.device].store(pp, std::memory_order_release);
   }
-  return g_static_partials_dev[c.device];
+  *partials = pp; *status = ps;
+  return true;
 }
 }  // namespace
+
+// Status word of the entry point below on the context's device: 0 if that entry point was never
+// used there. Reads and clears it (after the caller has synchronised the stream).
+int static_scratch_status_take(Context &c)
+{
+  if (c.device < 0 || c.device >= MAX_DEVICES) return 0;
+  int *ps = g_static_status_dev[c.device].load(std::memory_order_acquire);
+  if (!ps) return 0;
+  int v = 0;
+  if (!cuda_ok(cudaMemcpy(&v, ps, sizeof(int), cudaMemcpyDeviceToHost), "static status read")) return -1;
+  if (v != 0) cudaMemset(ps, 0, sizeof(int));
+  return v;
+}
 
 }  // namespace pulpnn
 
@@ -969,7 +1005,8 @@ extern "C" int pulpnn_linear_out_32_static_scratch(const uint8_t *pInBuffer, con
     set_error(PULPNN_ERR_INVALID_ARG, "%s: NULL pointer, empty dimension or fewer than 2 K slices", who);
     return c.err;
   }
-  // host buffers would have to be staged through allocated device memory: refuse them
+  // host buffers would have to be staged through allocated device memory: refuse them; so is a
+  // buffer that lives on another GPU than the context's (the tensor maps are made for this one)
   const void *ptrs[4] = {pInBuffer, pWeights, pOutBuffer, bias};
   for (const void *q : ptrs) {
     if (!q) continue;
@@ -977,7 +1014,12 @@ extern "C" int pulpnn_linear_out_32_static_scratch(const uint8_t *pInBuffer, con
     if (cudaPointerGetAttributes(&a, q) != cudaSuccess ||
         (a.type != cudaMemoryTypeDevice && a.type != cudaMemoryTypeManaged)) {
       cudaGetLastError();
-      set_error(PULPNN_ERR_INVALID_ARG, "%s: every buffer must be device memory", who);
+      set_error(PULPNN_ERR_INVALID_ARG, "%s: every buffer must be device (or managed) memory", who);
+      return c.err;
+    }
+    if (a.type == cudaMemoryTypeDevice && a.device != c.device) {
+      set_error(PULPNN_ERR_INVALID_ARG, "%s: a buffer lives on device %d, the context is bound to device %d", who,
+                a.device, c.device);
       return c.err;
     }
   }
@@ -987,7 +1029,8 @@ extern "C" int pulpnn_linear_out_32_static_scratch(const uint8_t *pInBuffer, con
   p.ky = p.kx = 1; p.pt = p.pl = 0; p.sy = p.sx = 1;
   p.epi.k = p.epi.lambda = nullptr; p.epi.bias = bias; p.epi.mode = EPI_RAW32; p.epi.out_mult = 0; p.epi.shift = 0;
   if (!igemm_tc_supported(c, p) || (reinterpret_cast<uintptr_t>(pOutBuffer) & 3) || (reinterpret_cast<uintptr_t>(bias) & 3)) {
-    set_error(PULPNN_ERR_UNSUPPORTED, "%s: needs dim_vec a multiple of 16 and 16-byte aligned device pointers", who);
+    set_error(PULPNN_ERR_UNSUPPORTED, "%s: needs dim_vec a multiple of 16, pInBuffer and pWeights 16-byte aligned, "
+              "pOutBuffer and bias 4-byte aligned", who);
     return c.err;
   }
 
@@ -1020,14 +1063,14 @@ extern "C" int pulpnn_linear_out_32_static_scratch(const uint8_t *pInBuffer, con
               who, g.k_slices, g.M, g.N, need, (size_t)STATIC_SCRATCH_INTS);
     return c.err;
   }
-  int *partials = static_partials_for_current_device(c);
-  if (!partials) return c.err;
+  int *partials = nullptr, *status = nullptr;
+  if (!static_symbols_for_current_device(c, &partials, &status)) return c.err;
 
   g.w_resident = 0;
   g.stationary = 0;
   g.n_stages = PIPE_BYTES / (BM * bkb + bn * bkb);
   if (g.n_stages > MAX_STAGES) g.n_stages = MAX_STAGES;
-  g.status = nullptr;                      // the status word of the ordinary path is allocated; do without
+  g.status = status;                       // built into the library too; read by pulpnn_device_status()
   g.out = partials;
   g.vec_store = (g.N % 4 == 0);
   TcMaps maps;

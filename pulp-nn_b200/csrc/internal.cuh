@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stddef.h>
+#include <atomic>
 
 #include "../../include/pulpnn_b200.h"
 
@@ -96,12 +97,17 @@ __device__ __forceinline__ int dp4a_us(unsigned a_u8x4, int b_s8x4, int c)
 // Problem descriptions handed from the entry points to the launchers (all pointers are device
 // pointers by then).
 // ---------------------------------------------------------------------------------------------
+// Block-diagonal copies of a layer's weights (see launch_igemm_tc), made once and kept by whoever
+// owns the layer; slot i holds the copy for 2^i pixels per GEMM row. Device memory, freed by the owner.
+struct FoldedWeights { int8_t *w[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr}; };
+
 struct ConvProblem {
   const uint8_t *in;     // [B][H][W][Cin]
   const int8_t *w;       // [Cout][ky][kx][Cin]
   void *out;             // [B][Ho][Wo][Cout] uint8 (int32 for EPI_RAW32)
   int B, H, W, Cin, Ho, Wo, Cout, ky, kx, pt, pl, sy, sx;
   Epilogue epi;
+  FoldedWeights *folded = nullptr;   // optional: where constant weights keep their folded copies
 };
 
 struct DepthwiseProblem {
@@ -148,6 +154,7 @@ bool ensure_device(Context &c);
 void set_error(int code, const char *fmt, ...);
 bool cuda_ok(cudaError_t e, const char *what);
 void count_launch(unsigned n = 1);
+unsigned long long thread_launch_count();       // launches made by the calling thread so far
 
 // Programmatic dependent launch. A kernel launched this way may become resident and run its
 // prologue while the previous kernel of the stream is still draining; it must execute pdl_wait()
@@ -172,6 +179,17 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 #endif
 void *ctx_scratch(Context &c, size_t bytes);    // grow-only device scratch, nullptr on failure
+
+// A per-kernel setting that belongs to a device (cudaFuncSetAttribute, an occupancy figure) is
+// cached per device, not per process or per thread: one process may drive several GPUs, from one
+// thread that rebinds its context or from a thread per GPU.
+constexpr int MAX_DEVICES = 64;
+struct PerDeviceInt {
+  std::atomic<int> v[MAX_DEVICES];
+  PerDeviceInt() { for (auto &x : v) x.store(0, std::memory_order_relaxed); }
+  int get(int dev) const { return (dev >= 0 && dev < MAX_DEVICES) ? v[dev].load(std::memory_order_acquire) : 0; }
+  void set(int dev, int val) { if (dev >= 0 && dev < MAX_DEVICES) v[dev].store(val, std::memory_order_release); }
+};
 
 // Stages host buffers through device memory. Device pointers pass through untouched.
 class Stager {
@@ -212,6 +230,7 @@ bool launch_depthwise_chw3x3_tma(Context &c, const DepthwiseProblem &p);
 bool depthwise_chw3x3_supported(const DepthwiseProblem &p);
 bool launch_depthwise_chw3x3(Context &c, const DepthwiseProblem &p);
 int *ctx_status_word(Context &c);               // allocated on first use; nullptr on failure
+int static_scratch_status_take(Context &c);     // status of the no-allocation entry point (0: unused or fine)
 bool launch_maxpool(Context &c, const PoolProblem &p, uint8_t *clobber_in);
 bool launch_avgpool(Context &c, const PoolProblem &p);
 bool launch_add(Context &c, const uint8_t *a, const uint8_t *b, uint8_t *out, size_t n, int m1,

@@ -18,6 +18,7 @@ struct Layer {
   const void *bias = nullptr, *k = nullptr, *lambda = nullptr;
   size_t in_bytes = 0, out_bytes = 0;      // per image
   int mode = EPI_NONE;
+  FoldedWeights folded;                    // device copies owned by the network
 };
 
 bool is_device_ptr(const void *p)
@@ -39,6 +40,7 @@ struct pulpnn_net {
   uint8_t *stage_in = nullptr; size_t stage_in_cap = 0;
   uint8_t *stage_out = nullptr; size_t stage_out_cap = 0;
   cudaStream_t copy_stream = nullptr;
+  unsigned long long launches_last_run = 0;
   cudaEvent_t ev_in[2] = {nullptr, nullptr}, ev_done[2] = {nullptr, nullptr};
 };
 
@@ -55,7 +57,7 @@ const void *upload(pulpnn_net *net, const void *src, size_t bytes)
   return dev;
 }
 
-bool run_layer(Context &c, const pulpnn_net *net, const Layer &L, const uint8_t *in, void *out, int n)
+bool run_layer(Context &c, const pulpnn_net *net, Layer &L, const uint8_t *in, void *out, int n)
 {
   const pulpnn_layer_desc_t &d = L.d;
   Epilogue e;
@@ -66,7 +68,7 @@ bool run_layer(Context &c, const pulpnn_net *net, const Layer &L, const uint8_t 
     case PULPNN_LAYER_POINTWISE:
     case PULPNN_LAYER_LINEAR_OUT_32: {
       ConvProblem p;
-      p.in = in; p.w = L.w; p.out = out; p.epi = e;
+      p.in = in; p.w = L.w; p.out = out; p.epi = e; p.folded = &L.folded;
       p.B = n; p.H = d.dim_in_y; p.W = d.dim_in_x; p.Cin = d.ch_in; p.Ho = d.dim_out_y; p.Wo = d.dim_out_x;
       p.Cout = d.ch_out;
       if (d.type == PULPNN_LAYER_CONV) {
@@ -145,6 +147,7 @@ int run_impl(pulpnn_net *net, const uint8_t *input, void *output, int n, int n_l
   const size_t in_b = net->layers.front().in_bytes * n;
   const size_t out_b = net->layers[n_layers - 1].out_bytes * n;
   const bool in_dev = is_device_ptr(input), out_dev = is_device_ptr(output);
+  const unsigned long long launches0 = thread_launch_count();
   const uint8_t *din = input;
   uint8_t *dout = static_cast<uint8_t *>(output);
   if (!in_dev) {
@@ -200,6 +203,7 @@ int run_impl(pulpnn_net *net, const uint8_t *input, void *output, int n, int n_l
       i0 += nb;
     }
   }
+  net->launches_last_run = thread_launch_count() - launches0;
   if (!out_dev) {
     if (!cuda_ok(cudaMemcpyAsync(output, dout, out_b, cudaMemcpyDeviceToHost, c.stream), "D2H copy")) return c.err;
   }
@@ -359,8 +363,11 @@ int pulpnn_net_run_timed(pulpnn_net_t *net, const uint8_t *input, void *output, 
   }
   const int nl = (int)net->layers.size();
   std::vector<cudaEvent_t> marks;
-  const bool ok = run_device(c, net, input, static_cast<uint8_t *>(output), n_images, nl, &marks);
-  if (ok && cuda_ok(cudaStreamSynchronize(c.stream), "cudaStreamSynchronize")) {
+  const unsigned long long launches0 = thread_launch_count();
+  bool ok = run_device(c, net, input, static_cast<uint8_t *>(output), n_images, nl, &marks);
+  net->launches_last_run = thread_launch_count() - launches0;
+  ok = ok && cuda_ok(cudaStreamSynchronize(c.stream), "cudaStreamSynchronize");
+  if (ok) {
     for (int l = 0; l < nl; l++) layer_ms[l] = 0.f;
     // marks: one event before every layer call of every micro-batch, plus one at the very end
     for (size_t i = 0; i + 1 < marks.size(); i++) {
@@ -370,7 +377,8 @@ int pulpnn_net_run_timed(pulpnn_net_t *net, const uint8_t *input, void *output, 
     }
   }
   for (cudaEvent_t ev : marks) cudaEventDestroy(ev);
-  return c.err == PULPNN_OK && ok ? PULPNN_OK : (c.err ? c.err : PULPNN_ERR_CUDA);
+  // only this call's own failures count: an error left on the thread by an earlier call is not ours
+  return ok ? PULPNN_OK : (c.err ? c.err : PULPNN_ERR_CUDA);
 }
 
 int pulpnn_net_num_layers(const pulpnn_net_t *net) { return net ? (int)net->layers.size() : 0; }
@@ -383,10 +391,8 @@ size_t pulpnn_net_layer_output_bytes(const pulpnn_net_t *net, int layer)
 
 unsigned long long pulpnn_net_launches_per_run(const pulpnn_net_t *net, int n_images)
 {
-  if (!net || !net->finalized) return 0;
-  const int micro = net->micro > 0 ? net->micro : n_images;
-  const unsigned long long chunks = (unsigned long long)((n_images + micro - 1) / micro);
-  return chunks * net->layers.size();
+  (void)n_images;
+  return net ? net->launches_last_run : 0;
 }
 
 void pulpnn_net_destroy(pulpnn_net_t *net)
@@ -394,6 +400,8 @@ void pulpnn_net_destroy(pulpnn_net_t *net)
   if (!net) return;
   cudaDeviceSynchronize();
   for (void *p : net->owned) cudaFree(p);
+  for (Layer &L : net->layers)
+    for (int8_t *wf : L.folded.w) if (wf) cudaFree(wf);
   for (int i = 0; i < 2; i++) {
     if (net->act[i]) cudaFree(net->act[i]);
     if (net->ev_in[i]) cudaEventDestroy(net->ev_in[i]);

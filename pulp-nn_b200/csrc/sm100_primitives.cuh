@@ -55,7 +55,7 @@ __device__ __forceinline__ unsigned long long global_ns()
 }
 // Bounded wait. The clock is first read once a wait has lasted 256 polls.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
-                                          int *status, int code)
+                                          int *status, int code, unsigned long long limit_ns = WAIT_LIMIT_NS)
 {
   unsigned long long t0 = 0;
   for (unsigned spin = 1;; spin++) {
@@ -64,7 +64,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
     if ((spin & 255u) == 0) {
       if (*abort_flag) return false;
       if (t0 == 0) t0 = global_ns();
-      else if (global_ns() - t0 > WAIT_LIMIT_NS) {
+      else if (global_ns() - t0 > limit_ns) {
         *abort_flag = 1;
         if (status) atomicOr(status, code);
         return false;

@@ -23,6 +23,7 @@ class GpuKernels:
         torch.cuda.set_device(self.dev)
         api.set_device(device)
         api.set_stream(None)
+        self._guarded = {}
 
     # -- buffers ---------------------------------------------------------------------------
     def _in(self, a, dtype=None):
@@ -33,16 +34,40 @@ class GpuKernels:
             return a
         return self.torch.from_numpy(a).to(self.dev)
 
+    GUARD = 256            # bytes of canary on either side of every output buffer
+    CANARY = 0xA5
+
     def _out(self, shape, dtype):
+        """A zero-filled output buffer with GUARD canary bytes before and after it (checked by
+        ``_np``): a kernel that stores one row or one vector past its output is caught here,
+        where no memory checker runs."""
+        nbytes = int(np.prod(shape)) * np.dtype(dtype).itemsize
         if self.host:
-            return np.zeros(shape, dtype)
-        tdt = {np.uint8: self.torch.uint8, np.int32: self.torch.int32}[dtype]
-        return self.torch.zeros(shape, dtype=tdt, device=self.dev)
+            base = np.full(nbytes + 2 * self.GUARD, self.CANARY, np.uint8)
+            mid = base[self.GUARD:self.GUARD + nbytes]
+            mid[:] = 0
+            out = mid.view(dtype).reshape(shape)
+        else:
+            tdt = {np.uint8: self.torch.uint8, np.int32: self.torch.int32}[dtype]
+            base = self.torch.full((nbytes + 2 * self.GUARD,), self.CANARY, dtype=self.torch.uint8, device=self.dev)
+            mid = base[self.GUARD:self.GUARD + nbytes]
+            mid.zero_()
+            out = mid.view(tdt).reshape(shape)
+        self._guarded[id(out)] = (base, nbytes)
+        return out
 
     def _np(self, t):
+        if not self.host:
+            api.synchronize()
+        entry = self._guarded.pop(id(t), None)
+        if entry is not None:
+            base, nbytes = entry
+            flat = base if self.host else base.cpu().numpy()
+            lo, hi = flat[:self.GUARD], flat[self.GUARD + nbytes:]
+            assert (lo == self.CANARY).all(), "a kernel wrote BEFORE its output buffer (%d bytes changed)" % int((lo != self.CANARY).sum())
+            assert (hi == self.CANARY).all(), "a kernel wrote PAST its output buffer (%d bytes changed)" % int((hi != self.CANARY).sum())
         if self.host:
-            return t
-        api.synchronize()
+            return np.array(t)
         return t.cpu().numpy()
 
     @staticmethod

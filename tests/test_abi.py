@@ -66,6 +66,30 @@ def test_no_gpu_means_error_not_fallback():
         pulpnn.GpuKernels()
 
 
+def test_dropin_header_compiles_and_links_as_documented(tmp_path):
+    """INTEGRATION.md's two-line switch: a C file that includes pulpnn_b200_dropin.h and uses the
+    reference's names is compiled and linked with the documented line, then run. Without a GPU the
+    call must record PULPNN_ERR_NO_DEVICE and leave the output alone; with one it must compute
+    pulp_nn_add (32bit/src/pulp_nn_add.c:54-60)."""
+    import subprocess
+    pulpnn.build_library()
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    libdir = os.path.join(root, "pulp-nn_b200", "lib")
+    exe = str(tmp_path / "dropin_app")
+    subprocess.run(["cc", os.path.join(root, "tests", "data", "dropin_app.c"), "-I" + os.path.join(root, "include"),
+                    "-L" + libdir, "-lpulpnn_b200_32", "-lpulpnn_b200", "-Wl,-rpath," + libdir, "-o", exe],
+                   check=True)
+    out = subprocess.run([exe], check=True, capture_output=True, text=True).stdout.split()
+    assert out[0] == "status"
+    if _has_gpu():
+        a = (np.arange(256) * 7).astype(np.uint8).astype(np.uint32)
+        b = (255 - np.arange(256)).astype(np.uint8).astype(np.uint32)
+        want = np.minimum(((a * 3 + b * 5) >> 2) & 0xffff, 255)
+        assert out[1] == "0" and int(out[3]) == int(want.sum())
+    else:
+        assert int(out[1]) == pulpnn.api.ERR_NO_DEVICE
+
+
 def test_product_does_not_reach_the_checkers():
     """Nothing under the package or include/ may import, link or name the oracle."""
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))

@@ -3,7 +3,7 @@ import numpy as np
 import pytest
 
 from conftest import pulpnn
-from netref import mobilenet_chain
+from oracle.netref import mobilenet_chain
 
 pytestmark = pytest.mark.gpu
 wl = pulpnn.workloads
@@ -54,4 +54,62 @@ def test_batch_split_gives_identical_logits(restatement):
     parts = [_device_run(net, np.ascontiguousarray(x[i:i + 2]), (2, 1000), np.int32) for i in (0, 2, 4)]
     assert np.array_equal(full, np.concatenate(parts))
     assert np.array_equal(full[:1], mobilenet_chain(restatement, params, x[:1])[-1])
+    net.close()
+
+
+def test_mobilenet_at_the_benchmark_batch(restatement):
+    """MobileNetV1 at batch 1024 -- the benchmark's own shape, where every kernel takes its
+    large-batch branch (several images per depthwise CTA, full waves of GEMM tiles) -- with live
+    parameters, from device memory and through the sliced host-input path. The logits of sampled
+    images (first, last, the boundaries of the four host-input slices) must equal the CPU
+    checker's, and every image's logits must equal the same image's logits in a batch of 8."""
+    import torch
+    pulpnn.GpuKernels()
+    B = 1024
+    params = wl.mobilenet_params(seed=4, bits=32, shift_bias=1)
+    x = wl.mobilenet_input(9, B)
+    net = api.build_mobilenet_v1(params, bits=32, max_batch=B)
+    dx = torch.from_numpy(x).cuda()
+    dout = torch.zeros((B, 1000), dtype=torch.int32, device="cuda")
+    net.run(dx, dout, B)
+    api.synchronize()
+    dev_logits = dout.cpu().numpy()
+    host_logits = np.zeros((B, 1000), np.int32)
+    net.run(x, host_logits, B)
+    assert api.device_status() == 0
+    assert np.array_equal(dev_logits, host_logits), "host-input path differs from the device-input path"
+    sample = [0, 1, 127, 128, 255, 256, 257, 511, 512, 513, 767, 768, 769, 1000, 1022, 1023]
+    want = mobilenet_chain(restatement, params, np.ascontiguousarray(x[sample]))[-1]
+    assert len(np.unique(want)) > 100
+    assert np.array_equal(dev_logits[sample], want), "batch-1024 logits differ from the CPU checker"
+    # batch invariance: the same images in a small batch
+    small = np.ascontiguousarray(x[504:512])
+    dsmall = torch.zeros((8, 1000), dtype=torch.int32, device="cuda")
+    net.run(torch.from_numpy(small).cuda(), dsmall, 8)
+    api.synchronize()
+    assert np.array_equal(dsmall.cpu().numpy(), dev_logits[504:512])
+    net.close()
+
+
+def test_mobilenet_prefixes_at_a_large_batch(restatement):
+    """Layer-by-layer outputs at batch 160 (large enough for the several-images-per-CTA branch of
+    the late depthwise layers) for four sampled images against the CPU checker."""
+    import torch
+    pulpnn.GpuKernels()
+    B = 160
+    params = wl.mobilenet_params(seed=4, bits=32, shift_bias=1)
+    x = wl.mobilenet_input(10, B)
+    sample = [0, 79, 80, 159]
+    want = mobilenet_chain(restatement, params, np.ascontiguousarray(x[sample]))
+    net = api.build_mobilenet_v1(params, bits=32, max_batch=B)
+    dx = torch.from_numpy(x).cuda()
+    for l in (0, 1, 2, 3, 4, 6, 8, 10, 12, 14, 16, 24, 26, 27, 28):
+        w = want[l]
+        dout = torch.zeros((B,) + w.shape[1:], dtype={np.uint8: torch.uint8, np.int32: torch.int32}[w.dtype.type],
+                           device="cuda")
+        net.run(dx, dout, B, l + 1)
+        api.synchronize()
+        got = dout.cpu().numpy()[sample]
+        assert np.array_equal(got, w), "layer %d (%s) differs at batch %d" % (l, params[l]["name"], B)
+    assert api.device_status() == 0
     net.close()

@@ -54,6 +54,54 @@ def same(a, b):
                              % (len(bad), a.size, tuple(bad[0]), a[tuple(bad[0])], b[tuple(bad[0])]))
 
 
+# ---- the five configurations against both checkers ----------------------------------------------
+@pytest.fixture(params=["restatement", "reference"])
+def checker(request, restatement):
+    """The CPU side of a comparison: our restatement, or the reference's own code compiled in
+    place (skipped where that library was not built)."""
+    if request.param == "restatement":
+        return lambda bits: restatement
+    r32, r64 = request.getfixturevalue("reference32"), request.getfixturevalue("reference64")
+    return lambda bits: r32 if bits == 32 else r64
+
+
+def test_configurations_against_both_checkers(checker, gpu):
+    """Configurations 1-4 (literal and live requantisation) and the pooling / add kernels, GPU
+    against the restatement AND against the compiled reference, in the GPU run itself."""
+    for shift in (None, 12):
+        c = wl.conv_case(0, 32, 32, 32, 64, bits=32, out_shift=shift, batch=2)
+        same(gpu.conv(32, c["x"], c["w"], c["k"], c["lam"], **conv_kw(c)),
+             checker(32).conv(32, c["x"], c["w"], c["k"], c["lam"], **conv_kw(c)))
+    for shift in (None, 10):
+        c = wl.pointwise_case(1, 56, 56, 128, 256, batch=3, bits=32, out_shift=shift)
+        same(gpu.pointwise(32, c["x"], c["w"], c["k"], c["lam"], **pw_kw(c)),
+             checker(32).pointwise(32, c["x"], c["w"], c["k"], c["lam"], **pw_kw(c)))
+    c = wl.config_c3(batch=3)
+    same(gpu.depthwise(64, c["x"], c["w"], c["k"], c["lam"], **dw_kw(c)),
+         checker(64).depthwise(64, c["x"], c["w"], c["k"], c["lam"], **dw_kw(c)))
+    c = wl.config_c4(batch=6)
+    for shift in (c["out_shift"], 14):
+        kw = dict(bias=c["bias"], out_mult=c["out_mult"], out_shift=shift, relu=c["relu"], bn=c["bn"])
+        same(gpu.linear(32, c["x"], c["w"], c["k"], c["lam"], **kw),
+             checker(32).linear(32, c["x"], c["w"], c["k"], c["lam"], **kw))
+    same(gpu.linear_out_32(c["x"], c["w"], bias32=c["bias32"]),
+         checker(32).linear_out_32(c["x"], c["w"], bias32=c["bias32"]))
+    # MobileNet's own pair shapes with live parameters
+    c = wl.depthwise_case(61, 28, 28, 256, batch=5, bits=32, out_shift=9, hwc=True)
+    same(gpu.depthwise(32, c["x"], c["w"], c["k"], c["lam"], **dw_kw(c)),
+         checker(32).depthwise(32, c["x"], c["w"], c["k"], c["lam"], **dw_kw(c)))
+    c = wl.pointwise_case(62, 14, 14, 512, 512, batch=4, bits=32, out_shift=12)
+    same(gpu.pointwise(32, c["x"], c["w"], c["k"], c["lam"], **pw_kw(c)),
+         checker(32).pointwise(32, c["x"], c["w"], c["k"], c["lam"], **pw_kw(c)))
+    rng = np.random.default_rng(63)
+    x = rng.integers(0, 256, size=(3, 7, 7, 1024), dtype=np.uint8)
+    pk = dict(out_hw=(1, 1), kernel=(7, 7), pads=(0, 0, 0, 0), strides=(7, 7))
+    same(gpu.avgpool(32, x, **pk), checker(32).avgpool(32, x, **pk))
+    a = rng.integers(0, 256, size=(2, 9, 9, 48), dtype=np.uint8)
+    b = rng.integers(0, 256, size=(2, 9, 9, 48), dtype=np.uint8)
+    same(gpu.add(a, b, m1=37, m2=91, out_shift=6), checker(32).add(a, b, m1=37, m2=91, out_shift=6))
+
+
 # ---- standard convolution ------------------------------------------------------------------
 @pytest.mark.parametrize("variant", ["Ho", "HoWo"])
 def test_conv_config1_literal(variant, gpu, restatement):
@@ -335,6 +383,36 @@ def test_depthwise_hwc_tma_small_batch_strips(gpu, restatement):
         want = restatement.depthwise(32, c["x"], c["w"], c["k"], c["lam"], **dw_kw(c))
         same(gpu.depthwise(32, c["x"], c["w"], c["k"], c["lam"], **dw_kw(c)), want)
     assert api.device_status() == 0
+
+
+@pytest.mark.parametrize("H,C,s,B", [(14, 512, 1, 256), (7, 1024, 1, 250), (28, 256, 2, 128), (112, 32, 1, 67),
+                                     (56, 128, 1, 131), (14, 512, 2, 301), (28, 256, 1, 203), (112, 64, 2, 75)])
+def test_depthwise_hwc_tma_several_images_per_cta(H, C, s, B, gpu, restatement):
+    """Large batches: more whole-image columns than CTAs fit on the GPU at once, so a CTA works
+    through several consecutive images with its ring of row groups running on from one image to
+    the next (the branch every depthwise layer of the batch-1024 benchmark takes). Batches that
+    do not divide by the images per CTA leave the last CTA short."""
+    c = wl.depthwise_case(41, H, H, C, strides=(s, s), batch=B, bits=32, out_shift=9, hwc=True)
+    want = restatement.depthwise(32, c["x"], c["w"], c["k"], c["lam"], **dw_kw(c))
+    assert np.count_nonzero(want) > want.size // 4
+    same(gpu.depthwise(32, c["x"], c["w"], c["k"], c["lam"], **dw_kw(c)), want)
+    assert api.device_status() == 0
+
+
+@pytest.mark.parametrize("bits", [32, 64])
+@pytest.mark.parametrize("relu,bn", MODES)
+def test_depthwise_hwc_tma_several_images_per_cta_modes(bits, relu, bn, gpu, restatement, reference32, reference64):
+    """The same branch in every epilogue mode and both trees; the first and the last images are
+    also held to the compiled reference itself."""
+    c = wl.depthwise_case(42, 14, 14, 512, batch=250, bits=bits, out_shift=9, with_bias=True, out_mult=3,
+                          relu=relu, bn=bn, hwc=True)
+    want = restatement.depthwise(bits, c["x"], c["w"], c["k"], c["lam"], **dw_kw(c))
+    got = gpu.depthwise(bits, c["x"], c["w"], c["k"], c["lam"], **dw_kw(c))
+    same(got, want)
+    ref = reference32 if bits == 32 else reference64
+    for sl in (slice(0, 2), slice(248, 250)):
+        r = ref.depthwise(bits, np.ascontiguousarray(c["x"][sl]), c["w"], c["k"], c["lam"], **dw_kw(c))
+        same(got[sl], r)
 
 
 def test_depthwise_mobilenet_shapes(gpu, restatement):

@@ -24,18 +24,20 @@ def _dev(a):
     return torch.from_numpy(np.ascontiguousarray(a)).cuda()
 
 
-def test_static_scratch_linear_matches_the_allocating_entry_point():
+def test_static_scratch_linear_matches_the_allocating_entry_point(restatement):
     import torch
     pulpnn.GpuKernels()                       # binds the device
     K, N = 4096, 4096
     rng = np.random.default_rng(77)
-    w = _dev(rng.integers(-128, 128, size=(N, K)).astype(np.int8))
-    bias = _dev(rng.integers(-2 ** 20, 2 ** 20, size=N).astype(np.int32))
+    w_np = rng.integers(-128, 128, size=(N, K)).astype(np.int8)
+    bias_np = rng.integers(-2 ** 20, 2 ** 20, size=N).astype(np.int32)
+    w, bias = _dev(w_np), _dev(bias_np)
     results = []
     # two calls in a row with different inputs and shapes: 32 vectors x 4 slices, then
     # 16 vectors x 8 slices (both 524288 partial sums, half of the built-in array)
     for call, (B, slices) in enumerate(((32, 4), (16, 8))):
-        x = _dev(rng.integers(0, 256, size=(B, K), dtype=np.uint8))
+        x_np = rng.integers(0, 256, size=(B, K), dtype=np.uint8)
+        x = _dev(x_np)
         want = torch.zeros((B, N), dtype=torch.int32, device="cuda")
         api.set_batch(B)
         api.set_option(api.OPT_SPLIT_K, 1)        # the existing entry point, no split, no scratch
@@ -44,22 +46,31 @@ def test_static_scratch_linear_matches_the_allocating_entry_point():
         finally:
             api.set_option(api.OPT_SPLIT_K, 0)
         got = torch.full((B, N), -1, dtype=torch.int32, device="cuda")
+        api.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
         api.pulpnn_linear_out_32_static_scratch(x, bias, got, w, K, N, B, slices)
         api.synchronize()
-        assert api.device_status() == 0
+        if call > 0:      # the first call on a device may make the driver load the module's data
+            assert torch.cuda.mem_get_info()[0] == free_before, "the call changed the free device memory"
+        assert api.device_status() == 0       # covers this entry point's own status word too
         assert torch.equal(got, want), "call %d differs from pulp_nn_linear_out_32" % call
+        # ... and both equal the CPU checker (32bit/src/pulp_nn_linear_out_32.c:48-80)
+        cpu = restatement.linear_out_32(x_np, w_np, bias32=bias_np)
+        assert np.array_equal(got.cpu().numpy(), cpu), "call %d differs from the CPU checker" % call
         results.append(int(want.abs().max()))
     assert min(results) > 0
-    # without a bias, and a neuron count that is not a multiple of the tile width
-    x = _dev(rng.integers(0, 256, size=(8, 1024), dtype=np.uint8))
-    w2 = _dev(rng.integers(-16, 16, size=(1000, 1024)).astype(np.int8))
-    want = torch.zeros((8, 1000), dtype=torch.int32, device="cuda")
-    got = torch.zeros_like(want)
-    api.set_batch(8)
-    api.pulp_nn_linear_out_32(32, x, None, want, w2, 1024, 1000)
-    api.pulpnn_linear_out_32_static_scratch(x, None, got, w2, 1024, 1000, 8, 2)
-    api.synchronize()
-    assert torch.equal(got, want)
+    # without a bias; neuron counts that are not a multiple of the tile width (1000) or of the
+    # 16-byte store (1001: scalar stores of the partial sums); a reduction length that leaves the
+    # last K slab partly empty (144 = 128 + 16)
+    for (B, K2, N2, slices) in ((8, 1024, 1000, 2), (5, 1024, 1001, 4), (7, 144, 72, 2)):
+        x_np = rng.integers(0, 256, size=(B, K2), dtype=np.uint8)
+        w2_np = rng.integers(-16, 16, size=(N2, K2)).astype(np.int8)
+        x, w2 = _dev(x_np), _dev(w2_np)
+        got = torch.full((B, N2), -1, dtype=torch.int32, device="cuda")
+        api.pulpnn_linear_out_32_static_scratch(x, None, got, w2, K2, N2, B, slices)
+        api.synchronize()
+        assert api.device_status() == 0
+        assert np.array_equal(got.cpu().numpy(), restatement.linear_out_32(x_np, w2_np)), (B, K2, N2)
 
 
 def test_static_scratch_linear_refuses_what_does_not_fit():
