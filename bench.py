@@ -388,18 +388,36 @@ def run_gpu_arm(args):
     rows = wl.mobilenet_ops_bytes()
     per_layer = []
     by_kernel = {}
-    for L, r, t_ms in zip(params, rows, layer_ms):
-        gb = r["bytes"] * B / 1e9
-        gop = r["ops"] * B / 1e9
-        per_layer.append({"layer": L["name"], "ms": round(float(t_ms), 4),
-                          "GOPs": round(gop / (t_ms / 1e3), 1), "GBs": round(gb / (t_ms / 1e3), 1),
-                          "hbm_frac": round(gb / (t_ms / 1e3) / hbm_peak, 3),
-                          "tc_frac_nominal": round(gop / (t_ms / 1e3) / 4.5e6, 3)})
+    roles = [job.net.layer_role(l) for l in range(job.net.num_layers())]
+    idx = 0
+    while idx < len(params):
+        L, r, t_ms = params[idx], rows[idx], float(layer_ms[idx])
+        name, ops, nbytes = L["name"], r["ops"], r["bytes"]
         kname = {"conv": "conv_smallcin_tc_kernel", "depthwise": "depthwise_hwc3x3_tma_kernel",
                  "pointwise": "igemm_tc_kernel", "avgpool": "avgpool_kernel",
                  "linear32": "igemm_tc_kernel"}[L["op"]]
+        step = 1
+        if roles[idx] == 1:
+            # a depthwise + pointwise pair run as one kernel: one entry, the pair's operations, and as
+            # algorithmic bytes what the fused kernel has to move (the pair's input and output; the
+            # intermediate tensor is not traffic any more)
+            r2 = rows[idx + 1]
+            name = L["name"] + "+" + params[idx + 1]["name"]
+            t_ms += float(layer_ms[idx + 1])
+            ops += r2["ops"]
+            nbytes = L["H"] * L["W"] * L["Cin"] + params[idx + 1]["Ho"] * params[idx + 1]["Wo"] * params[idx + 1]["Cout"]
+            kname, step = "dwpw_fused_kernel", 2
+        gb, gop = nbytes * B / 1e9, ops * B / 1e9
+        entry_ = {"layer": name, "ms": round(t_ms, 4),
+                  "GOPs": round(gop / (t_ms / 1e3), 1), "GBs": round(gb / (t_ms / 1e3), 1),
+                  "hbm_frac": round(gb / (t_ms / 1e3) / hbm_peak, 3),
+                  "tc_frac_nominal": round(gop / (t_ms / 1e3) / 4.5e6, 3), "kernel": kname}
+        if step == 2:
+            entry_["unfused_bytes_frac"] = round((r["bytes"] + rows[idx + 1]["bytes"]) * B / 1e9 / (t_ms / 1e3) / hbm_peak, 3)
+        per_layer.append(entry_)
         k = by_kernel.setdefault(kname, {"ms": 0.0, "bytes": 0.0, "launches": 0})
-        k["ms"] += float(t_ms); k["bytes"] += r["bytes"] * B; k["launches"] += 1
+        k["ms"] += t_ms; k["bytes"] += nbytes * B; k["launches"] += 1
+        idx += step
     top = max(by_kernel, key=lambda n: by_kernel[n]["ms"])
     tk = by_kernel[top]
     achieved = tk["bytes"] / 1e9 / (tk["ms"] / 1e3)

@@ -69,7 +69,10 @@ int  pulpnn_device_status(void);
 enum {
   PULPNN_OPT_FORCE_GENERIC = 1,   /* route contractions to the generic CUDA-core kernel      */
   PULPNN_OPT_MAXPOOL_CLOBBER = 2, /* also reproduce the reference's overwrite of Im_in       */
-  PULPNN_OPT_SPLIT_K = 3          /* 0 = choose automatically, n > 0 = force n K-slices      */
+  PULPNN_OPT_SPLIT_K = 3,         /* 0 = choose automatically, n > 0 = force n K-slices      */
+  PULPNN_OPT_FUSE_DWPW = 4        /* network runner: run a 3x3 stride-1 depthwise layer and   */
+                                  /* the pointwise layer behind it as ONE kernel where a      */
+                                  /* fused kernel exists (default 1); results are identical   */
 };
 int  pulpnn_set_option(int option, int value);
 int  pulpnn_get_option(int option);
@@ -299,6 +302,9 @@ int  pulpnn_net_run_timed(pulpnn_net_t *net, const uint8_t *input, void *output,
                           float *layer_ms);
 int  pulpnn_net_num_layers(const pulpnn_net_t *net);
 size_t pulpnn_net_layer_output_bytes(const pulpnn_net_t *net, int layer);   /* per image */
+/* How layer `layer` ran in the most recent run: 0 = a kernel of its own, 1 / 2 = the first /
+ * second layer of a pair executed as one fused kernel (PULPNN_OPT_FUSE_DWPW); -1 = no such layer. */
+int  pulpnn_net_layer_role(const pulpnn_net_t *net, int layer);
 /* Kernel launches the most recent pulpnn_net_run / _run_prefix / _run_timed of this network made
  * (0 before the first run). n_images is ignored. */
 unsigned long long pulpnn_net_launches_per_run(const pulpnn_net_t *net, int n_images);

@@ -67,6 +67,24 @@ def build_case(name, B, pkg):
         fn = lambda: call(bits, x, None, None, o, w, None, k, lam, 1, c["out_shift"], H, H, C, Ho, Ho, C,  # noqa: E731
                           3, 3, 1, 1, 1, 1, s, s, 1, 1)
         return fn, 2.0 * B * Ho * Ho * C * 9, B * C * (H * H + Ho * Ho), (x, w, k, lam, o)
+    if name.startswith("dwpw"):
+        # a depthwise layer and the pointwise layer behind it through the network runner: one fused
+        # kernel where the library has one (PULPNN_OPT_FUSE_DWPW), else two kernels
+        idx = name[4:]
+        H, C, s = DEPTHWISE["dw" + idx]
+        Hp, cin, cout = POINTWISE["pw" + idx]
+        dw = wl.depthwise_case(2, H, H, C, strides=(s, s), batch=1, bits=32, hwc=True)
+        pw = wl.pointwise_case(1, Hp, Hp, cin, cout, batch=1, bits=32)
+        net = api.Net(32, B)
+        net.add_layer(api.LAYER_DEPTHWISE, dim_in=(H, H), ch_in=C, dim_out=(Hp, Hp), ch_out=C, kernel=(3, 3),
+                      pads=(1, 1, 1, 1), strides=(s, s), out_shift=dw["out_shift"], weights=dw["w"], k=dw["k"], lam=dw["lam"])
+        net.add_layer(api.LAYER_POINTWISE, dim_in=(Hp, Hp), ch_in=cin, dim_out=(Hp, Hp), ch_out=cout,
+                      out_shift=pw["out_shift"], weights=pw["w"], k=pw["k"], lam=pw["lam"])
+        net.finalize()
+        x = torch.randint(0, 256, (B, H, H, C), dtype=torch.uint8, device="cuda")
+        o = out((B, Hp, Hp, cout))
+        ops = 2.0 * B * Hp * Hp * C * 9 + 2.0 * B * Hp * Hp * cin * cout
+        return (lambda: net.run(x, o, B)), ops, B * (H * H * C + Hp * Hp * cout), (net, x, o)
     if name in ("c1", "conv1"):
         if name == "c1":
             c = wl.config_c1(batch=B)
@@ -196,6 +214,7 @@ def main():
     ap.add_argument("--all", action="store_true")
     ap.add_argument("--graph", action="store_true", help="capture the repetitions in one CUDA graph and time its replay")
     ap.add_argument("--split-k", type=int, default=0, help="force this many K-slices in the GEMM (0 = automatic)")
+    ap.add_argument("--no-fuse", action="store_true", help="dwpwN cases: two kernels instead of the fused one")
     args = ap.parse_args()
     import torch
     if not torch.cuda.is_available():
@@ -204,6 +223,8 @@ def main():
     pkg.api.set_device(0)
     if args.split_k:
         pkg.api.set_option(3, args.split_k)      # PULPNN_OPT_SPLIT_K
+    if args.no_fuse:
+        pkg.api.set_option(pkg.api.OPT_FUSE_DWPW, 0)
     names = [args.case]
     if args.all:
         names = list(dict.fromkeys(["c1", "c2", "c3", "c4", "c4_out32", "conv1"] + sorted(POINTWISE) + sorted(DEPTHWISE)))

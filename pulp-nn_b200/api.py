@@ -13,7 +13,7 @@ import numpy as np
 from . import _lib
 
 OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_CUDA, ERR_NO_DEVICE, ERR_DEVICE_WAIT = range(6)
-OPT_FORCE_GENERIC, OPT_MAXPOOL_CLOBBER, OPT_SPLIT_K = 1, 2, 3
+OPT_FORCE_GENERIC, OPT_MAXPOOL_CLOBBER, OPT_SPLIT_K, OPT_FUSE_DWPW = 1, 2, 3, 4
 LAYER_CONV, LAYER_POINTWISE, LAYER_DEPTHWISE, LAYER_AVGPOOL, LAYER_MAXPOOL, LAYER_LINEAR_OUT_32 = range(6)
 
 
@@ -341,6 +341,10 @@ class Net:
 
     def num_layers(self):
         return self.lib.pulpnn_net_num_layers(self.handle)
+
+    def layer_role(self, layer):
+        """0: own kernel; 1 / 2: first / second layer of a fused pair (in the most recent run)."""
+        return int(self.lib.pulpnn_net_layer_role(self.handle, int(layer)))
 
     def layer_output_bytes(self, layer):
         return int(self.lib.pulpnn_net_layer_output_bytes(self.handle, int(layer)))

@@ -238,6 +238,7 @@ int pulpnn_set_option(int option, int value)
     case PULPNN_OPT_FORCE_GENERIC: c.opt_force_generic = value != 0; return PULPNN_OK;
     case PULPNN_OPT_MAXPOOL_CLOBBER: c.opt_maxpool_clobber = value != 0; return PULPNN_OK;
     case PULPNN_OPT_SPLIT_K: c.opt_split_k = value < 0 ? 0 : value; return PULPNN_OK;
+    case PULPNN_OPT_FUSE_DWPW: c.opt_fuse_dwpw = value != 0; return PULPNN_OK;
     default: set_error(PULPNN_ERR_INVALID_ARG, "unknown option %d", option); return c.err;
   }
 }
@@ -249,6 +250,7 @@ int pulpnn_get_option(int option)
     case PULPNN_OPT_FORCE_GENERIC: return c.opt_force_generic;
     case PULPNN_OPT_MAXPOOL_CLOBBER: return c.opt_maxpool_clobber;
     case PULPNN_OPT_SPLIT_K: return c.opt_split_k;
+    case PULPNN_OPT_FUSE_DWPW: return c.opt_fuse_dwpw;
     default: return -1;
   }
 }

@@ -142,6 +142,7 @@ struct Context {
   int opt_force_generic = 0;
   int opt_maxpool_clobber = 0;
   int opt_split_k = 0;
+  int opt_fuse_dwpw = 1;          // the network runner pairs depthwise + pointwise layers into one kernel
   StageSlot slots[8];
   // device scratch owned by the context (split-K partial sums, status word)
   void *scratch = nullptr; size_t scratch_cap = 0;
@@ -227,6 +228,9 @@ bool depthwise_hwc3x3_tma_supported(const DepthwiseProblem &p);
 bool launch_depthwise_hwc3x3_tma(Context &c, const DepthwiseProblem &p);
 bool depthwise_chw3x3_tma_supported(const DepthwiseProblem &p);
 bool launch_depthwise_chw3x3_tma(Context &c, const DepthwiseProblem &p);
+// a 3x3 stride-1 depthwise layer and the pointwise layer behind it in one kernel (dwpw_fused.cu)
+bool dwpw_fused_supported(const DepthwiseProblem &dw, const ConvProblem &pw);
+bool launch_dwpw_fused(Context &c, const DepthwiseProblem &dw, const ConvProblem &pw);
 bool depthwise_chw3x3_supported(const DepthwiseProblem &p);
 bool launch_depthwise_chw3x3(Context &c, const DepthwiseProblem &p);
 int *ctx_status_word(Context &c);               // allocated on first use; nullptr on failure

@@ -41,6 +41,7 @@ struct pulpnn_net {
   uint8_t *stage_out = nullptr; size_t stage_out_cap = 0;
   cudaStream_t copy_stream = nullptr;
   unsigned long long launches_last_run = 0;
+  std::vector<char> role_last_run;         // per layer: 0 own kernel, 1 / 2 first / second layer of a fused pair
   cudaEvent_t ev_in[2] = {nullptr, nullptr}, ev_done[2] = {nullptr, nullptr};
 };
 
@@ -57,36 +58,51 @@ const void *upload(pulpnn_net *net, const void *src, size_t bytes)
   return dev;
 }
 
+Epilogue layer_epilogue(const Layer &L)
+{
+  Epilogue e;
+  e.k = L.k; e.lambda = L.lambda; e.bias = L.bias; e.mode = L.mode;
+  e.out_mult = (int)(int16_t)(uint16_t)L.d.out_mult; e.shift = L.d.out_shift;
+  return e;
+}
+
+ConvProblem conv_problem(Layer &L, const uint8_t *in, void *out, int n)
+{
+  const pulpnn_layer_desc_t &d = L.d;
+  ConvProblem p;
+  p.in = in; p.w = L.w; p.out = out; p.epi = layer_epilogue(L); p.folded = &L.folded;
+  p.B = n; p.H = d.dim_in_y; p.W = d.dim_in_x; p.Cin = d.ch_in; p.Ho = d.dim_out_y; p.Wo = d.dim_out_x;
+  p.Cout = d.ch_out;
+  if (d.type == PULPNN_LAYER_CONV) {
+    p.ky = d.dim_kernel_y; p.kx = d.dim_kernel_x; p.pt = d.padding_y_top; p.pl = d.padding_x_left;
+    p.sy = d.stride_y; p.sx = d.stride_x;
+  } else {
+    p.ky = p.kx = 1; p.pt = p.pl = 0; p.sy = p.sx = 1;
+  }
+  return p;
+}
+
+DepthwiseProblem depthwise_problem(const Layer &L, const uint8_t *in, void *out, int n)
+{
+  const pulpnn_layer_desc_t &d = L.d;
+  DepthwiseProblem p;
+  p.in = in; p.w = L.w; p.out = static_cast<uint8_t *>(out); p.epi = layer_epilogue(L);
+  p.B = n; p.H = d.dim_in_y; p.W = d.dim_in_x; p.C = d.ch_in; p.Ho = d.dim_out_y; p.Wo = d.dim_out_x;
+  p.ky = d.dim_kernel_y; p.kx = d.dim_kernel_x; p.pt = d.padding_y_top; p.pl = d.padding_x_left;
+  p.sy = d.stride_y; p.sx = d.stride_x; p.in_is_hwc = true;
+  return p;
+}
+
 bool run_layer(Context &c, const pulpnn_net *net, Layer &L, const uint8_t *in, void *out, int n)
 {
   const pulpnn_layer_desc_t &d = L.d;
-  Epilogue e;
-  e.k = L.k; e.lambda = L.lambda; e.bias = L.bias; e.mode = L.mode;
-  e.out_mult = (int)(int16_t)(uint16_t)d.out_mult; e.shift = d.out_shift;
   switch (d.type) {
     case PULPNN_LAYER_CONV:
     case PULPNN_LAYER_POINTWISE:
-    case PULPNN_LAYER_LINEAR_OUT_32: {
-      ConvProblem p;
-      p.in = in; p.w = L.w; p.out = out; p.epi = e; p.folded = &L.folded;
-      p.B = n; p.H = d.dim_in_y; p.W = d.dim_in_x; p.Cin = d.ch_in; p.Ho = d.dim_out_y; p.Wo = d.dim_out_x;
-      p.Cout = d.ch_out;
-      if (d.type == PULPNN_LAYER_CONV) {
-        p.ky = d.dim_kernel_y; p.kx = d.dim_kernel_x; p.pt = d.padding_y_top; p.pl = d.padding_x_left;
-        p.sy = d.stride_y; p.sx = d.stride_x;
-      } else {
-        p.ky = p.kx = 1; p.pt = p.pl = 0; p.sy = p.sx = 1;
-      }
-      return launch_conv(c, p);
-    }
-    case PULPNN_LAYER_DEPTHWISE: {
-      DepthwiseProblem p;
-      p.in = in; p.w = L.w; p.out = static_cast<uint8_t *>(out); p.epi = e;
-      p.B = n; p.H = d.dim_in_y; p.W = d.dim_in_x; p.C = d.ch_in; p.Ho = d.dim_out_y; p.Wo = d.dim_out_x;
-      p.ky = d.dim_kernel_y; p.kx = d.dim_kernel_x; p.pt = d.padding_y_top; p.pl = d.padding_x_left;
-      p.sy = d.stride_y; p.sx = d.stride_x; p.in_is_hwc = true;
-      return launch_depthwise(c, p);
-    }
+    case PULPNN_LAYER_LINEAR_OUT_32:
+      return launch_conv(c, conv_problem(L, in, out, n));
+    case PULPNN_LAYER_DEPTHWISE:
+      return launch_depthwise(c, depthwise_problem(L, in, out, n));
     case PULPNN_LAYER_AVGPOOL:
     case PULPNN_LAYER_MAXPOOL: {
       PoolProblem p{};
@@ -103,6 +119,16 @@ bool run_layer(Context &c, const pulpnn_net *net, Layer &L, const uint8_t *in, v
   }
 }
 
+// Layers l (depthwise) and l+1 (pointwise) as one kernel, the depthwise output never leaving the
+// SM? Only where a fused kernel exists for the pair's shape and both layers requantise the same way.
+bool pair_is_fusable(Context &c, pulpnn_net *net, int l, int n_layers, const uint8_t *in, void *out, int n)
+{
+  if (!c.opt_fuse_dwpw || l + 1 >= n_layers) return false;
+  Layer &A = net->layers[l], &B = net->layers[l + 1];
+  if (A.d.type != PULPNN_LAYER_DEPTHWISE || B.d.type != PULPNN_LAYER_POINTWISE) return false;
+  return dwpw_fused_supported(depthwise_problem(A, in, nullptr, n), conv_problem(B, nullptr, out, n));
+}
+
 // pushes images [0, n) that already sit in device memory through layers [0, n_layers)
 bool run_device(Context &c, pulpnn_net *net, const uint8_t *din, uint8_t *dout, int n, int n_layers,
                 std::vector<cudaEvent_t> *marks = nullptr)
@@ -113,15 +139,39 @@ bool run_device(Context &c, pulpnn_net *net, const uint8_t *din, uint8_t *dout, 
   for (int i0 = 0; i0 < n; i0 += micro) {
     const int nb = n - i0 < micro ? n - i0 : micro;
     const uint8_t *cur = din + (size_t)i0 * in_b;
+    int cur_buf = -1;                      // which ping-pong buffer holds `cur` (-1: the caller's input)
     for (int l = 0; l < n_layers; l++) {
-      void *dst = (l == n_layers - 1) ? static_cast<void *>(dout + (size_t)i0 * out_b)
-                                      : static_cast<void *>(net->act[l & 1]);
-      if (marks) {
+      auto mark = [&]() {
+        if (!marks) return true;
         cudaEvent_t ev;
         if (!cuda_ok(cudaEventCreate(&ev), "cudaEventCreate")) return false;
         cudaEventRecord(ev, c.stream);
         marks->push_back(ev);
+        return true;
+      };
+      // where the output of layer `last` goes: the caller's buffer for the final layer, else the
+      // ping-pong buffer that does not hold the current input
+      const int other = cur_buf == 0 ? 1 : 0;
+      auto dest = [&](int last) -> void * {
+        if (last == n_layers - 1) return static_cast<void *>(dout + (size_t)i0 * out_b);
+        return static_cast<void *>(net->act[other]);
+      };
+      if (!mark()) return false;
+      if (pair_is_fusable(c, net, l, n_layers, cur, dest(l + 1), nb)) {
+        void *dst = dest(l + 1);
+        if (!launch_dwpw_fused(c, depthwise_problem(net->layers[l], cur, nullptr, nb),
+                               conv_problem(net->layers[l + 1], nullptr, dst, nb)))
+          return false;
+        cur = static_cast<const uint8_t *>(dst);
+        cur_buf = other;
+        net->role_last_run[l] = 1; net->role_last_run[l + 1] = 2;
+        l++;
+        if (!mark()) return false;         // the pair's time is booked on the depthwise layer, none on the pointwise
+        continue;
       }
+      cur_buf = other;
+      net->role_last_run[l] = 0;
+      void *dst = dest(l);
       if (!run_layer(c, net, net->layers[l], cur, dst, nb)) return false;
       cur = static_cast<const uint8_t *>(dst);
     }
@@ -335,6 +385,7 @@ int pulpnn_net_finalize(pulpnn_net_t *net, int micro_batch)
     if (!cuda_ok(cudaEventCreateWithFlags(&net->ev_done[i], cudaEventDisableTiming), "cudaEventCreate")) return c.err;
   }
   if (!cuda_ok(cudaStreamCreateWithFlags(&net->copy_stream, cudaStreamNonBlocking), "cudaStreamCreate")) return c.err;
+  net->role_last_run.assign(net->layers.size(), 0);
   net->finalized = true;
   return PULPNN_OK;
 }
@@ -387,6 +438,12 @@ size_t pulpnn_net_layer_output_bytes(const pulpnn_net_t *net, int layer)
 {
   if (!net || layer < 0 || layer >= (int)net->layers.size()) return 0;
   return net->layers[layer].out_bytes;
+}
+
+int pulpnn_net_layer_role(const pulpnn_net_t *net, int layer)
+{
+  if (!net || layer < 0 || layer >= (int)net->role_last_run.size()) return -1;
+  return net->role_last_run[layer];
 }
 
 unsigned long long pulpnn_net_launches_per_run(const pulpnn_net_t *net, int n_images)
