@@ -70,9 +70,12 @@ enum {
   PULPNN_OPT_FORCE_GENERIC = 1,   /* route contractions to the generic CUDA-core kernel      */
   PULPNN_OPT_MAXPOOL_CLOBBER = 2, /* also reproduce the reference's overwrite of Im_in       */
   PULPNN_OPT_SPLIT_K = 3,         /* 0 = choose automatically, n > 0 = force n K-slices      */
-  PULPNN_OPT_FUSE_DWPW = 4        /* network runner: run a 3x3 stride-1 depthwise layer and   */
+  PULPNN_OPT_FUSE_DWPW = 4,       /* network runner: run a 3x3 stride-1 depthwise layer and   */
                                   /* the pointwise layer behind it as ONE kernel where a      */
                                   /* fused kernel exists (default 1); results are identical   */
+  PULPNN_OPT_TUNE = 5             /* measurement switch: a bit mask that selects alternative   */
+                                  /* launch configurations of some kernels (0 = the defaults); */
+                                  /* never changes a result                                     */
 };
 int  pulpnn_set_option(int option, int value);
 int  pulpnn_get_option(int option);

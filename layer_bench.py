@@ -215,6 +215,7 @@ def main():
     ap.add_argument("--graph", action="store_true", help="capture the repetitions in one CUDA graph and time its replay")
     ap.add_argument("--split-k", type=int, default=0, help="force this many K-slices in the GEMM (0 = automatic)")
     ap.add_argument("--no-fuse", action="store_true", help="dwpwN cases: two kernels instead of the fused one")
+    ap.add_argument("--tune", type=int, default=0, help="experimental kernel configurations (bit mask)")
     args = ap.parse_args()
     import torch
     if not torch.cuda.is_available():
@@ -223,6 +224,8 @@ def main():
     pkg.api.set_device(0)
     if args.split_k:
         pkg.api.set_option(3, args.split_k)      # PULPNN_OPT_SPLIT_K
+    if args.tune:
+        pkg.api.set_option(pkg.api.OPT_TUNE, args.tune)
     if args.no_fuse:
         pkg.api.set_option(pkg.api.OPT_FUSE_DWPW, 0)
     names = [args.case]

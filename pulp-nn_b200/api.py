@@ -13,7 +13,7 @@ import numpy as np
 from . import _lib
 
 OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_CUDA, ERR_NO_DEVICE, ERR_DEVICE_WAIT = range(6)
-OPT_FORCE_GENERIC, OPT_MAXPOOL_CLOBBER, OPT_SPLIT_K, OPT_FUSE_DWPW = 1, 2, 3, 4
+OPT_FORCE_GENERIC, OPT_MAXPOOL_CLOBBER, OPT_SPLIT_K, OPT_FUSE_DWPW, OPT_TUNE = 1, 2, 3, 4, 5
 LAYER_CONV, LAYER_POINTWISE, LAYER_DEPTHWISE, LAYER_AVGPOOL, LAYER_MAXPOOL, LAYER_LINEAR_OUT_32 = range(6)
 
 

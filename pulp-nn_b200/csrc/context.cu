@@ -239,6 +239,7 @@ int pulpnn_set_option(int option, int value)
     case PULPNN_OPT_MAXPOOL_CLOBBER: c.opt_maxpool_clobber = value != 0; return PULPNN_OK;
     case PULPNN_OPT_SPLIT_K: c.opt_split_k = value < 0 ? 0 : value; return PULPNN_OK;
     case PULPNN_OPT_FUSE_DWPW: c.opt_fuse_dwpw = value != 0; return PULPNN_OK;
+    case PULPNN_OPT_TUNE: c.opt_tune = value; return PULPNN_OK;
     default: set_error(PULPNN_ERR_INVALID_ARG, "unknown option %d", option); return c.err;
   }
 }
@@ -251,6 +252,7 @@ int pulpnn_get_option(int option)
     case PULPNN_OPT_MAXPOOL_CLOBBER: return c.opt_maxpool_clobber;
     case PULPNN_OPT_SPLIT_K: return c.opt_split_k;
     case PULPNN_OPT_FUSE_DWPW: return c.opt_fuse_dwpw;
+    case PULPNN_OPT_TUNE: return c.opt_tune;
     default: return -1;
   }
 }

@@ -150,12 +150,6 @@ depthwise_hwc3x3_tma_kernel(const __grid_constant__ CUtensorMap map_in, const __
     *abort_flag = 0;
     mbar_fence_init();
   }
-  pdl_wait();                      // up to here the kernel may overlap the previous one's tail
-  if (tid == 0) {
-    pdl_launch_dependents();
-    const int first = total < RING ? total : RING;
-    for (int j = 0; j < first; j++) issue_next();
-  }
 
   // the thread's four channels: weights as [w0,w1,w2,0] and [0,w0,w1,w2] per filter row, and the
   // requantisation parameters (fetched while the first loads are in flight)
@@ -193,6 +187,14 @@ depthwise_hwc3x3_tma_kernel(const __grid_constant__ CUtensorMap map_in, const __
                            (unsigned long long)__ldg(reinterpret_cast<const long long *>(e.lambda) + c + j));
       k32 = k32 && (k == (long long)(int)k);
     }
+  }
+  // The filter taps and requantisation parameters above are constants, fetched while the previous
+  // kernel may still be running; its output is touched only from here on.
+  pdl_wait();
+  if (tid == 0) {
+    pdl_launch_dependents();
+    const int first = total < RING ? total : RING;
+    for (int j = 0; j < first; j++) issue_next();
   }
   __syncthreads();                                   // the barriers are initialised
 

@@ -194,6 +194,11 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
+  // stationary CTAs: n-tile and first m-tile of this CTA, distance between its m-tiles
+  const int nt0 = g.stationary ? (int)(blockIdx.x % (unsigned)g.n_tiles) : 0;
+  const int m0 = g.stationary ? (int)(blockIdx.x / (unsigned)g.n_tiles) : 0;
+  const int m_step = g.stationary ? (int)(gridDim.x / (unsigned)g.n_tiles) : 0;
+
   if (threadIdx.x == 0) {
     for (int s = 0; s < MAX_STAGES; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
     // an accumulator is free again once every warp that drains it has arrived (see the epilogue)
@@ -204,6 +209,14 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     for (int s = 0; s < MAX_STAGES; s++) issued_parity[s] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    // The resident slice of W is fetched right away, before the wait on the previous kernel:
+    // weights are constants that no kernel of this library writes after the layer was set up (a
+    // block-diagonal copy is made by an ordinary launch, which this kernel cannot overtake), so the
+    // fetch may overlap the previous kernel's tail.
+    if (g.w_resident) {
+      mbar_arrive_expect_tx(wres_bar, (uint32_t)wres_bytes);
+      for (int s = 0; s < g.total_slabs; s++) tma_load_2d(smem + s * B_BYTES, &map_b, wres_bar, s * BKB, nt0 * BN_TILE);
+    }
   }
   if (warp == NPROD) tmem_alloc(tmem_slot, TMEM_COLS);
   tc_fence_before();
@@ -215,10 +228,6 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   if (threadIdx.x == 0) pdl_launch_dependents();
 
   const int units = g.m_tiles * g.n_tiles * g.k_slices;
-  // stationary CTAs: n-tile and first m-tile of this CTA, distance between its m-tiles
-  const int nt0 = g.stationary ? (int)(blockIdx.x % (unsigned)g.n_tiles) : 0;
-  const int m0 = g.stationary ? (int)(blockIdx.x / (unsigned)g.n_tiles) : 0;
-  const int m_step = g.stationary ? (int)(gridDim.x / (unsigned)g.n_tiles) : 0;
 
   if (warp < NPROD) {
     // ------------------------------ TMA producers -------------------------------------------
@@ -228,10 +237,6 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     if (lane == 0) {
       int st = 0; uint32_t ph = 0;           // ring position of the current slab
       bool ok = true;
-      if (warp == 0 && g.w_resident) {
-        mbar_arrive_expect_tx(wres_bar, (uint32_t)wres_bytes);
-        for (int s = 0; s < g.total_slabs; s++) tma_load_2d(smem + s * B_BYTES, &map_b, wres_bar, s * BKB, nt0 * BN_TILE);
-      }
       for (int i = 0; ok; i++) {
         int nt, mt, ks;
         if (!unit_at(g, i, units, nt0, m0, m_step, nt, mt, ks)) break;

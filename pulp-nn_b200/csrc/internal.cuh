@@ -142,6 +142,7 @@ struct Context {
   int opt_force_generic = 0;
   int opt_maxpool_clobber = 0;
   int opt_split_k = 0;
+  int opt_tune = 0;               // experiment switch: alternative kernel configurations (bit mask)
   int opt_fuse_dwpw = 1;          // the network runner pairs depthwise + pointwise layers into one kernel
   StageSlot slots[8];
   // device scratch owned by the context (split-K partial sums, status word)

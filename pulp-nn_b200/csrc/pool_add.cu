@@ -217,6 +217,75 @@ __global__ void __launch_bounds__(256) avgpool16_kernel(const PoolProblem p, int
   *reinterpret_cast<uint4 *>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
 }
 
+// Large windows (a global pool): one thread per window would leave most of the GPU idle and make
+// every thread walk the whole window alone. Here a block takes one output pixel and 128 channels:
+// lane = four channels (a warp reads 128 contiguous bytes of a pixel), the block's eight warps share
+// out the window's pixels, and shared memory adds up the eight partial sums. Same arithmetic.
+__global__ void __launch_bounds__(256) avgpool_window_kernel(const PoolProblem p, int chunks)
+{
+  __shared__ unsigned part[8][32][4];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  unsigned t = blockIdx.x;
+  const int chunk = (int)(t % (unsigned)chunks); t /= (unsigned)chunks;
+  const int ox = (int)(t % (unsigned)p.Wo); t /= (unsigned)p.Wo;
+  const int oy = (int)(t % (unsigned)p.Ho);
+  const int b = (int)(t / (unsigned)p.Ho);
+  const int c = chunk * 128 + lane * 4;
+  const bool on = c < p.C;
+  const int y0 = max(oy * p.sy - p.pb, 0), y1 = min(oy * p.sy - p.pt + p.ky, p.H);
+  const int x0 = max(ox * p.sx - p.pl, 0), x1 = min(ox * p.sx - p.pr + p.kx, p.W);
+  const int wx = x1 - x0, tot = (wx > 0 && y1 > y0) ? wx * (y1 - y0) : 0;
+  const uint8_t *img = p.in + (size_t)b * p.H * p.W * p.C + (on ? c : 0);
+  unsigned s[4] = {0, 0, 0, 0};
+  // a window as wide as the image (a global pool) is one contiguous run of pixels: no division
+  const bool run = wx == p.W;
+  for (int n = warp; n < tot; n += 32) {          // four loads in flight per thread
+    unsigned v[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const int q = n + 8 * i;
+      v[i] = 0;
+      if (q < tot && on) {
+        const size_t pix = run ? (size_t)y0 * p.W + q : (size_t)(y0 + q / wx) * p.W + x0 + q % wx;
+        v[i] = __ldg(reinterpret_cast<const unsigned *>(img + pix * p.C));
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      s[0] += v[i] & 0xff; s[1] += (v[i] >> 8) & 0xff; s[2] += (v[i] >> 16) & 0xff; s[3] += v[i] >> 24;
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 4; j++) part[warp][lane][j] = s[j];
+  __syncthreads();
+  if (warp != 0 || !on) return;
+#pragma unroll
+  for (int w = 1; w < 8; w++)
+#pragma unroll
+    for (int j = 0; j < 4; j++) s[j] += part[w][lane][j];
+  const unsigned ktot = (unsigned)(p.kx * p.ky);
+  unsigned o = 0;
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    int res;
+    if (p.requant) {
+      if (p.bn_bits == 32) {
+        const unsigned tq = s[j] * (unsigned)(int)p.lambda / ktot + (unsigned)(int)p.out_add;
+        res = (int)(tq >> p.shift);
+      } else {
+        const long long tq = (long long)s[j] * p.lambda / (long long)ktot + p.out_add;
+        res = (int)(tq >> p.shift);
+      }
+    } else {
+      res = (int)(s[j] / ktot);
+    }
+    o |= (unsigned)clip_u8(res) << (8 * j);
+  }
+  *reinterpret_cast<unsigned *>(p.out + (((size_t)b * p.Ho + oy) * p.Wo + ox) * p.C + c) = o;
+}
+
 // ---- residual add --------------------------------------------------------------------------
 // 32bit/src/pulp_nn_utils.c:47-60: uint32 sum of the two int16-scaled bytes, logical shift,
 // cut to 16 bits, then clamp to 255.
@@ -290,6 +359,16 @@ bool launch_avgpool(Context &c, const PoolProblem &p)
 {
   const bool vec = (p.C % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.in) & 3) == 0) &&
                    ((reinterpret_cast<uintptr_t>(p.out) & 3) == 0);
+  // windows of at least 32 pixels: a block per output pixel and 128 channels
+  const int chunks = (p.C + 127) / 128;
+  const long long blocks_w = (long long)p.B * p.Ho * p.Wo * chunks;
+  const long long threads16 = (long long)p.B * p.Ho * p.Wo * (p.C / 16);
+  const bool fills_gpu = p.C % 16 == 0 && threads16 >= 256LL * 2 * (c.sm_count > 0 ? c.sm_count : 148);
+  if (vec && p.kx * p.ky >= 32 && blocks_w < 0x7fffffffLL && !fills_gpu) {
+    const cudaError_t le = launch_pdl(avgpool_window_kernel, dim3((unsigned)blocks_w), dim3(256), 0, c.stream, p, chunks);
+    count_launch();
+    return cuda_ok(le, "avgpool launch") && cuda_ok(cudaGetLastError(), "avgpool launch");
+  }
   // windows of at least 16 pixels: fewer threads with more bytes in flight each
   if (p.C % 16 == 0 && p.kx * p.ky >= 16 && ((reinterpret_cast<uintptr_t>(p.in) | reinterpret_cast<uintptr_t>(p.out)) & 15) == 0) {
     const int CW16 = p.C / 16;

@@ -626,6 +626,14 @@ def test_avgpool_mobilenet_tail(gpu, restatement):
     x = rng.integers(0, 256, size=(5, 7, 7, 1024), dtype=np.uint8)
     kw = dict(kernel=(7, 7), strides=(7, 7), pads=(0, 0, 0, 0), out_hw=(1, 1))
     same(gpu.avgpool(32, x, **kw), restatement.avgpool(32, x, **kw))
+    # windows of 32 pixels and more share a window among the warps of a block: a channel count that
+    # leaves the last 128-channel chunk ragged, overlapping padded windows, both requantised forms
+    x = rng.integers(0, 256, size=(3, 13, 12, 200), dtype=np.uint8)
+    for bits in (32, 64):
+        for requant in (0, 1):
+            kw = dict(kernel=(6, 7), strides=(3, 4), pads=(2, 2, 3, 3), out_hw=(4, 3), lam=-77, out_shift=5,
+                      out_add=1000, requant=requant)
+            same(gpu.avgpool(bits, x, **kw), restatement.avgpool(bits, x, **kw))
 
 
 @pytest.mark.parametrize("m1,m2,shift", [(37, 91, 6), (1, 1, 0), (65535, 3, 4), (300, 500, 1)])
