@@ -211,6 +211,35 @@ void pulpnn_i4_to_i8(const int8_t *pSrc, int8_t *pDst, unsigned int n);
 void pulpnn_i2_to_i8(const int8_t *pSrc, int8_t *pDst, unsigned int n);
 
 /*
+ * The scalar requantisers of pulp_nn_utils.h as element-wise bulk device operations: n int32
+ * accumulators in, one result byte each out (not packed); element i takes the parameters of channel
+ * i % channels; bits = 8, 4 or 2 selects the clip range 255 / 15 / 3. Device or host buffers.
+ *   pulpnn_bn_quant_bulk     pulp_nn_bn_quant_u8 / _u4 / _u2   32bit/include/pulp_nn_utils.h:23,29,41
+ *                            (32bit/src/pulp_nn_utils.c:35-45,158-167,180-189): clip((k*phi + lambda) >> d),
+ *                            int32 wrap-around in the 32-bit tree, int64 in the 64-bit tree
+ *   pulpnn_quant_bulk        pulp_nn_quant_u8 / _u4 / _u2      pulp_nn_utils.h:25,31,43
+ *                            (pulp_nn_utils.c:148-156,169-178,191-199): clip((m*phi) >> d); the shifted
+ *                            value is cut to int16 for 8 bits in both trees and for 4 / 2 bits in the
+ *                            64-bit tree only (64bit/src/pulp_nn_utils.c:153,175,197)
+ *   pulpnn_threshold_quant_bulk   pulp_nn_i4_quant / pulp_nn_i2_quant   pulp_nn_utils.h:69,71
+ *                            (pulp_nn_utils.c:438-540): the signed 4- or 2-bit level of each input among a
+ *                            channel's thresholds (int16; 16 per channel of which 15 are read for 4
+ *                            bits, 4 per channel of which 3 are read for 2 bits), one int8 out
+ *   pulp_nn_avg_and_replace_int8   pulp_nn_utils.h:39 (pulp_nn_utils.c:95-115), the reference's own
+ *                            signature: base[i] = (base[i] + target[i]) >> 1 on signed bytes, for
+ *                            length >> 2 whole words; the batch setting does not apply
+ */
+void pulpnn_bn_quant_bulk_bn32(const int32_t *phi, const int32_t *k, const int32_t *lambda, int8_t d, uint8_t *out,
+                               unsigned int n, unsigned int channels, int bits);
+void pulpnn_bn_quant_bulk_bn64(const int32_t *phi, const int64_t *k, const int64_t *lambda, int8_t d, uint8_t *out,
+                               unsigned int n, unsigned int channels, int bits);
+void pulpnn_quant_bulk_bn32(const int32_t *phi, int16_t m, int8_t d, uint8_t *out, unsigned int n, int bits);
+void pulpnn_quant_bulk_bn64(const int32_t *phi, int16_t m, int8_t d, uint8_t *out, unsigned int n, int bits);
+void pulpnn_threshold_quant_bulk(const int32_t *in, const int16_t *thr, int8_t *out, unsigned int n,
+                                 unsigned int channels, int bits);
+void pulp_nn_avg_and_replace_int8(int8_t *base, int8_t *target, uint16_t length);
+
+/*
  * pulpnn_linear_out_32_static_scratch -- no counterpart in the reference.
  *
  * The arithmetic of pulp_nn_linear_out_32 (int32 accumulators, bias read as int32 words, no

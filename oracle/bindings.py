@@ -223,6 +223,40 @@ class CompiledReference:
         self.last_seconds = 0.0
         self.last_glue_seconds = 0.0
 
+    # -- the scalar helpers of pulp_nn_utils.c, called element by element (small cases only) --------
+    def scalar_bn_quant(self, out_bits, phi, k, lam, d):
+        """pulp_nn_bn_quant_u8/u4/u2 over arrays: element i uses channel i % len(k)."""
+        fn = getattr(self.lib, "pulp_nn_bn_quant_u%d" % out_bits)
+        bn_t = C.c_int32 if self.bits == 32 else C.c_int64
+        fn.restype = C.c_uint8
+        fn.argtypes = [C.c_int32, bn_t, bn_t, C.c_int8]
+        ch = len(k)
+        return np.array([fn(int(p), int(k[i % ch]), int(lam[i % ch]), int(d)) for i, p in enumerate(phi)], np.uint8)
+
+    def scalar_quant(self, out_bits, phi, m, d):
+        """pulp_nn_quant_u8/u4/u2 over an array."""
+        fn = getattr(self.lib, "pulp_nn_quant_u%d" % out_bits)
+        fn.restype = C.c_uint8
+        fn.argtypes = [C.c_int32, C.c_int16, C.c_int8]
+        return np.array([fn(int(p), int(m), int(d)) for p in phi], np.uint8)
+
+    def scalar_threshold_quant(self, out_bits, x, thr):
+        """pulp_nn_i4_quant / pulp_nn_i2_quant over an array; thr is [channels][16 or 4] int16."""
+        fn = getattr(self.lib, "pulp_nn_i%d_quant" % out_bits)
+        fn.restype = C.c_int8
+        fn.argtypes = [C.c_int, C.c_void_p]
+        thr = np.ascontiguousarray(thr, np.int16)
+        ch = thr.shape[0]
+        return np.array([fn(int(v), thr[i % ch].ctypes.data) for i, v in enumerate(x)], np.int8)
+
+    def avg_and_replace(self, base, target):
+        """pulp_nn_avg_and_replace_int8; returns the updated copy of base."""
+        b = np.ascontiguousarray(base, np.int8).copy()
+        t = np.ascontiguousarray(target, np.int8)
+        self.lib.pulp_nn_avg_and_replace_int8.restype = None
+        self.lib.pulp_nn_avg_and_replace_int8(b.ctypes.data_as(_vp), t.ctypes.data_as(_vp), C.c_uint16(b.size))
+        return b
+
     def build_info(self):
         p = os.path.join(HERE, "_ref", "build_info%d.txt" % self.bits)
         return open(p).read().strip().replace("\n", "; ") if os.path.exists(p) else ""

@@ -247,6 +247,33 @@ pulpnn_i4_to_i8 = _unpack("pulpnn_i4_to_i8")
 pulpnn_i2_to_i8 = _unpack("pulpnn_i2_to_i8")
 
 
+def pulpnn_bn_quant_bulk(bits, phi, k, lambda_, d, out, n, channels, out_bits):
+    """clip((k*phi + lambda) >> d) element-wise: pulp_nn_bn_quant_u8/u4/u2 in bulk; `bits` picks the tree."""
+    getattr(_lib.load_library(), "pulpnn_bn_quant_bulk" + _sfx(bits))(
+        _ptr(phi), _ptr(k), _ptr(lambda_), C.c_int8(d), _ptr(out), C.c_uint(n), C.c_uint(channels), C.c_int(out_bits))
+    _check()
+
+
+def pulpnn_quant_bulk(bits, phi, m, d, out, n, out_bits):
+    """clip((m*phi) >> d) element-wise: pulp_nn_quant_u8/u4/u2 in bulk."""
+    getattr(_lib.load_library(), "pulpnn_quant_bulk" + _sfx(bits))(
+        _ptr(phi), C.c_int16(m), C.c_int8(d), _ptr(out), C.c_uint(n), C.c_int(out_bits))
+    _check()
+
+
+def pulpnn_threshold_quant_bulk(in_, thr, out, n, channels, out_bits):
+    """pulp_nn_i4_quant / pulp_nn_i2_quant in bulk: thr is int16 [channels][16] (4 bits) or [channels][4] (2 bits)."""
+    _lib.load_library().pulpnn_threshold_quant_bulk(_ptr(in_), _ptr(thr), _ptr(out), C.c_uint(n), C.c_uint(channels),
+                                                    C.c_int(out_bits))
+    _check()
+
+
+def pulp_nn_avg_and_replace_int8(base, target, length):
+    """32bit/include/pulp_nn_utils.h:39: base[i] = (base[i] + target[i]) >> 1 for length >> 2 whole words."""
+    _lib.load_library().pulp_nn_avg_and_replace_int8(_ptr(base), _ptr(target), C.c_uint16(length))
+    _check()
+
+
 def pulpnn_chw_to_hwc(Im_in, Im_out, dim_im_x, dim_im_y, ch_im):
     """[batch][C][H][W] -> [batch][H][W][C] (no counterpart in the reference)."""
     _lib.load_library().pulpnn_chw_to_hwc(_ptr(Im_in), _ptr(Im_out), C.c_uint16(dim_im_x),

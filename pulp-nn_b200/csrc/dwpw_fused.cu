@@ -11,17 +11,18 @@
 // the result equals the two-call chain bit for bit.
 //
 // A unit of work is a patch of TH x TW (<= 128) output pixels of one image, all C channels in,
-// all N channels out. Roles in a CTA (18 warps, persistent over units):
-//   warp 0, one lane    TMA: the resident weights once, then per unit (and per 128-channel chunk) the
+// all N channels out. Roles in a CTA (persistent over units; two TMA and two MMA warps that take units in
+// turn where a layer's units are short, one of each otherwise):
+//   TMA warp, one lane  TMA: the resident weights once, then per unit (and per 128-channel chunk) the
 //                       (TH+2) x (TW+2) input pixels the patch reads, one 4-D box; pixels outside the
 //                       image arrive as zeros, which is the zero padding
 //                       (32bit/src/pulp_nn_depthwise_generic.c:82-132)
-//   warp 1, one lane    tcgen05.mma kind::i8, M = 128, N = ch_out, K = 32 per instruction
-//   warps 2..9          depthwise builders, in groups of WPU warps that take units in turn: a thread
+//   MMA warp, one lane  tcgen05.mma kind::i8, M = 128, N = ch_out, K = 32 per instruction
+//   builder warps       depthwise builders, in groups of WPU warps that take units in turn: a thread
 //                       owns four channels and four adjacent columns and slides down the patch with
 //                       three accumulator sets (depthwise_regs.cuh); finished rows are requantised and
 //                       stored as the rows of the A tile
-//   warps 10..17        epilogue: tcgen05.ld (lane = pixel), per-channel k / lambda from shared
+//   epilogue warps      epilogue: tcgen05.ld (lane = pixel), per-channel k / lambda from shared
 //                       memory, pack, 32-byte global stores (a pixel's ch_out bytes are contiguous)
 // Every mbarrier wait is bounded (sm100_primitives.cuh).
 #include <cuda.h>
@@ -37,15 +38,22 @@ namespace {
 using namespace sm100;
 using namespace dwregs;
 
-constexpr int EPI_WARPS_N = 8;
-constexpr int FIRST_BUILD = 2;
+// One thread needs several hundred cycles per unit for its waits, its TMA or MMA issue and its commits
+// when busy warps share its scheduler; with the short units of a narrow layer that, not memory or
+// arithmetic, set the pace (measured: the kernel took as long with the depthwise arithmetic left out).
+// So where the rings allow it two TMA threads and two MMA threads take units in turn.
 constexpr int ST_F_TMA = 0x10000, ST_F_BUILD = 0x20000, ST_F_MMA = 0x40000, ST_F_EPI = 0x80000;
 
 // geometry, all compile-time: C input channels, N output channels, patch of TH x TW pixels
-template <int C, int N, int TW, int TH, int BW> struct FG {
+template <int C, int N, int TW, int TH, int BW, int EW> struct FG {
+  static constexpr int NSRV = (C <= 64) ? 2 : 1;              // TMA warps = MMA warps; they take units in turn
+  static constexpr int FIRST_MMA = NSRV, FIRST_BUILD = 2 * NSRV;
   static constexpr int BUILD_WARPS = BW;                      // depthwise builder warps
+  static constexpr int EPI_WARPS_N = EW;                      // epilogue warps: groups of four (one per TMEM lane quarter)
+  static constexpr int EPI_GROUPS = EW / 4;
   static constexpr int FIRST_EPI = FIRST_BUILD + BUILD_WARPS;
   static constexpr int THREADS = 32 * (FIRST_EPI + EPI_WARPS_N);
+  static_assert(EW % 4 == 0 && (N != 256 || EW == 8), "epilogue warps come in groups of four; 256 columns take two groups per tile");
   static constexpr int CI = C < 128 ? C : 128;               // channel bytes per chunk = K-slab width
   static constexpr int NCHUNK = C / CI;
   static constexpr int LPC = CI / 4;                          // lanes (channel words) per pixel
@@ -62,6 +70,11 @@ template <int C, int N, int TW, int TH, int BW> struct FG {
   static constexpr int A_TILE = NCHUNK * A_SLAB;
   static constexpr int NUM_ACC = 512 / N > 8 ? 8 : 512 / N;   // accumulators in tensor memory
   static constexpr int NA = NUM_ACC % NBG == 0 ? NUM_ACC : NBG;   // ring of A tiles: a multiple of the builder groups
+  // With all channels in one chunk the (TW+2) pixels of a box row are contiguous in memory: the box is
+  // described over [B][H][W*C/4] 32-bit elements, ROWS_IN runs of (TW+2)*C bytes instead of
+  // ROWS_IN*(TW+2) pieces of C bytes (the TMA unit works through a box piece by piece, and 32-byte
+  // pieces were what bounded the 32-channel kernel).
+  static constexpr bool ROW_RUNS = NCHUNK == 1 && WBOX * C / 4 <= 256;
   static constexpr int NIN = NBG == 1 ? 3 : (NBG * NCHUNK <= 4 ? 4 : 2 * NBG * NCHUNK);   // ring of input boxes
   static constexpr int W_BYTES = N * C;
   static constexpr int PARAM_BYTES = N * 16;                  // k and lambda (up to 8 bytes each) or bias
@@ -78,6 +91,8 @@ template <int C, int N, int TW, int TH, int BW> struct FG {
   static_assert(NBG == 1 || NIN % (NBG * NCHUNK) == 0, "an input slot must always be read by the same group");
   static_assert(N % 32 == 0 && N >= 32 && N <= 256, "ch_out: a multiple of 32 up to 256");
   static_assert(SMEM <= 232448, "shared memory of one CTA");
+  static_assert(NSRV == 1 || (NCHUNK == 1 && NIN % NSRV == 0 && NA % NSRV == 0 && NUM_ACC % NSRV == 0),
+                "a ring slot must always be served by the same TMA / MMA warp");
 };
 
 struct FusedParams {
@@ -87,6 +102,7 @@ struct FusedParams {
   Epilogue e_dw, e_pw;
   int B, H, W;             // stride 1, padding 1: the output has the input's size
   int tiles_x, tiles_y, units;
+  int ablate;              // measurement only (PULPNN_OPT_TUNE bits 8-10): 1 no stores, 2 no depthwise math, 4 no requantisation
   int *status;
 };
 
@@ -125,14 +141,15 @@ __device__ __forceinline__ void finalize_to_a(const int (&acc)[4][4], const Quan
   }
 }
 
-template <int MODE, int C, int N, int TW, int TH, int BW>
-__global__ void __launch_bounds__((FG<C, N, TW, TH, BW>::THREADS), 1)
+template <int MODE, int C, int N, int TW, int TH, int BW, int EW>
+__global__ void __launch_bounds__((FG<C, N, TW, TH, BW, EW>::THREADS), 1)
 dwpw_fused_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_constant__ CUtensorMap map_w,
                   const FusedParams g)
 {
-  using G = FG<C, N, TW, TH, BW>;
+  using G = FG<C, N, TW, TH, BW, EW>;
   constexpr int CI = G::CI;
-  constexpr int THREADS = G::THREADS, FIRST_EPI = G::FIRST_EPI;
+  constexpr int THREADS = G::THREADS, FIRST_EPI = G::FIRST_EPI, FIRST_BUILD = G::FIRST_BUILD, FIRST_MMA = G::FIRST_MMA;
+  constexpr int NSRV = G::NSRV;
   constexpr uint32_t TMEM_COLS = 512;
   extern __shared__ uint8_t smem_raw[];
   uint8_t *sm = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -168,7 +185,7 @@ dwpw_fused_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_const
     mbar_arrive_expect_tx(w_bar, (uint32_t)G::W_BYTES);
     for (int ch = 0; ch < G::NCHUNK; ch++) tma_load_2d(w_res + ch * N * CI, &map_w, w_bar, ch * CI, 0);
   }
-  if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+  if (warp == FIRST_MMA) tmem_alloc(tmem_slot, TMEM_COLS);
   // pointwise per-channel parameters -> shared memory, the bias folded into lambda:
   // k*(acc+b)+lambda == k*acc + (k*b+lambda) in wrap-around arithmetic
   for (int n = tid; n < N; n += THREADS) {
@@ -201,45 +218,46 @@ dwpw_fused_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_const
     y0 = (r - b * g.tiles_y) * TH;
   };
 
-  if (warp == 0) {
-    // ------------------------------ TMA ---------------------------------------------------------
+  if (warp < FIRST_MMA) {
+    // ------------------------------ TMA: warp w loads the units i = w, w + NSRV, ... ------------
     if (lane == 0) {
       pdl_wait();                       // the input is the previous kernel's output
-      pdl_launch_dependents();
-      int s = 0; uint32_t ph = 0; int issued = 0;
+      if (warp == 0) pdl_launch_dependents();
+      int issued = 0;
       bool ok = true;
-      for (int u = blockIdx.x; u < g.units && ok; u += gridDim.x) {
+      int i = 0;
+      for (int u = blockIdx.x; u < g.units && ok; u += gridDim.x, i++) {
+        if (NSRV > 1 && i % NSRV != warp) continue;
         int b, y0, x0;
         unit_pos(u, b, y0, x0);
         for (int ch = 0; ch < G::NCHUNK; ch++) {
+          const int item = i * G::NCHUNK + ch, s = item % G::NIN;
+          const uint32_t ph = ((uint32_t)(item / G::NIN)) & 1u;
           if (!mbar_wait(&in_empty[s], ph ^ 1, abort_flag, g.status, ST_F_TMA)) { ok = false; break; }
           mbar_arrive_expect_tx(&in_full[s], (uint32_t)G::IN_BYTES);
-          tma_load_4d(in_ring + s * G::IN_STRIDE, &map_in, &in_full[s], ch * CI, x0 - 1, y0 - 1, b);
+          if (G::ROW_RUNS)      // whole pixels: a row of the box is one run of (TW+2)*C bytes, in 32-bit elements
+            tma_load_3d(in_ring + s * G::IN_STRIDE, &map_in, &in_full[s], (x0 - 1) * (C / 4), y0 - 1, b);
+          else
+            tma_load_4d(in_ring + s * G::IN_STRIDE, &map_in, &in_full[s], ch * CI, x0 - 1, y0 - 1, b);
           issued++;
-          if (++s == G::NIN) { s = 0; ph ^= 1; }
         }
       }
-      if (*abort_flag) {
-        // something gave up: no TMA write may still be in flight when the CTA's memory is released
-        const int pending = issued < G::NIN ? issued : G::NIN;
-        for (int i = 0; i < pending; i++) {
-          if (--s < 0) { s = G::NIN - 1; ph ^= 1; }
-          const unsigned long long t0 = global_ns();
-          while (!mbar_try_wait(&in_full[s], ph))
-            if (global_ns() - t0 > WAIT_LIMIT_NS) break;
-        }
+      if (*abort_flag && issued) {
+        // something gave up: let the loads that are still in flight land before the CTA's memory goes
+        // (a load takes a few microseconds at most)
         const unsigned long long t0 = global_ns();
-        while (!mbar_try_wait(w_bar, 0))
-          if (global_ns() - t0 > WAIT_LIMIT_NS) break;
+        while (global_ns() - t0 < 200000ull) __nanosleep(1000);
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------ MMA ---------------------------------------------------------
+  } else if (warp < FIRST_BUILD) {
+    // ------------------------------ MMA: warp w issues the units i = w, w + NSRV, ... -----------
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc_u8s8(N);
+      const int me = warp - FIRST_MMA;
       bool ok = mbar_wait(w_bar, 0, abort_flag, g.status, ST_F_MMA);
       int i = 0;
       for (int u = blockIdx.x; u < g.units && ok; u += gridDim.x, i++) {
+        if (NSRV > 1 && i % NSRV != me) continue;
         const int slot = i % G::NA, acc = i % G::NUM_ACC;
         if (!mbar_wait(&t_empty[acc], (((uint32_t)(i / G::NUM_ACC)) & 1u) ^ 1u, abort_flag, g.status, ST_F_MMA)) break;
         if (!mbar_wait(&a_full[slot], ((uint32_t)(i / G::NA)) & 1u, abort_flag, g.status, ST_F_MMA)) break;
@@ -325,6 +343,7 @@ dwpw_fused_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_const
         int acc[3][4][4];
 #pragma unroll
         for (int ri = 0; ri < G::ROWS_IN; ri++) {
+          if (g.ablate & 2) break;
           unsigned cur[6]; Win1 w;
           load_row1<CI>(ia, ra, ri * G::IN_PITCH, cur);
           windows1(cur, rot, w);
@@ -354,7 +373,7 @@ dwpw_fused_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_const
     const int half = ew >> 2;                   // which group of four warps
     const int r = quad * 32 + lane;             // row of the tile = pixel of the patch
     const int py = r / TW, px = r - py * TW;
-    // N <= 128: the two groups take units in turn; N = 256: both work on every unit, 128 columns each
+    // N <= 128: the groups take units in turn; N = 256: two groups work on every unit, 128 columns each
     constexpr int COLS = N == 256 ? 128 : N;
     const int col0 = N == 256 ? half * 128 : 0;
     const int *p_k32 = reinterpret_cast<const int *>(params), *p_l32 = p_k32 + N;
@@ -363,7 +382,7 @@ dwpw_fused_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_const
     pdl_wait();                         // the output buffer may still be read by the previous kernel
     int i = 0;
     for (int u = blockIdx.x; u < g.units; u += gridDim.x, i++) {
-      if (N != 256 && (i & 1) != half) continue;
+      if (N != 256 && i % G::EPI_GROUPS != half) continue;
       const int acc = i % G::NUM_ACC;
       if (!mbar_wait(&t_full[acc], ((uint32_t)(i / G::NUM_ACC)) & 1u, abort_flag, g.status, ST_F_EPI)) break;
       tc_fence_after();
@@ -409,7 +428,7 @@ dwpw_fused_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_const
           }
           w[j >> 2] = pack4_sat_u8(qv[0], qv[1], qv[2], qv[3]);
         }
-        if (store)
+        if (store && !(g.ablate & 1))
           asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
                        ::"l"(orow + c0), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
                        : "memory");
@@ -422,17 +441,17 @@ dwpw_fused_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_const
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == FIRST_MMA) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
 
 // ---- host side ----------------------------------------------------------------------------------
-template <int MODE, int C, int N, int TW, int TH, int BW>
+template <int MODE, int C, int N, int TW, int TH, int BW, int EW>
 bool launch_geo(Context &c, const DepthwiseProblem &dw, const ConvProblem &pw)
 {
-  using G = FG<C, N, TW, TH, BW>;
+  using G = FG<C, N, TW, TH, BW, EW>;
   EncodeTiledFn enc = encode_tiled_fn();
   FusedParams g;
   g.in = dw.in; g.out = static_cast<uint8_t *>(pw.out); g.w_dw = dw.w;
@@ -445,9 +464,19 @@ bool launch_geo(Context &c, const DepthwiseProblem &dw, const ConvProblem &pw)
   g.units = (int)units;
   g.status = ctx_status_word(c);
   if (!g.status) return false;
+  g.ablate = (c.opt_tune >> 8) & 7;
 
   CUtensorMap map_in, map_w;
-  {
+  if (G::ROW_RUNS) {
+    cuuint64_t dims[3] = {(cuuint64_t)dw.W * C / 4, (cuuint64_t)dw.H, (cuuint64_t)dw.B};
+    cuuint64_t strides[2] = {(cuuint64_t)dw.W * C, (cuuint64_t)dw.H * dw.W * C};
+    cuuint32_t box[3] = {(cuuint32_t)(G::WBOX * C / 4), (cuuint32_t)G::ROWS_IN, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = enc(&map_in, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<uint8_t *>(dw.in), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { set_error(PULPNN_ERR_CUDA, "cuTensorMapEncodeTiled (fused input rows) failed with code %d", (int)r); return false; }
+  } else {
     cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)dw.W, (cuuint64_t)dw.H, (cuuint64_t)dw.B};
     cuuint64_t strides[3] = {(cuuint64_t)C, (cuuint64_t)dw.W * C, (cuuint64_t)dw.H * dw.W * C};
     cuuint32_t box[4] = {(cuuint32_t)G::CI, (cuuint32_t)G::WBOX, (cuuint32_t)G::ROWS_IN, 1};
@@ -470,7 +499,7 @@ bool launch_geo(Context &c, const DepthwiseProblem &dw, const ConvProblem &pw)
                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { set_error(PULPNN_ERR_CUDA, "cuTensorMapEncodeTiled (fused weights) failed with code %d", (int)r); return false; }
   }
-  auto kern = dwpw_fused_kernel<MODE, C, N, TW, TH, BW>;
+  auto kern = dwpw_fused_kernel<MODE, C, N, TW, TH, BW, EW>;
   static PerDeviceInt attr_set;
   if (!attr_set.get(c.device)) {
     if (!cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM),
@@ -492,9 +521,14 @@ bool launch_shape(Context &c, const DepthwiseProblem &dw, const ConvProblem &pw)
   const int C = dw.C, N = pw.Cout;
   // patch shapes: 16 x 8 tiles a 112-wide image exactly; 28 x 4 tiles 56- and 28-wide ones (measured
   // against 8 x 16 on 56 x 56 x 128: 0.243 ms against 0.272 ms at batch 1024)
-  if (C == 32 && N == 64) return launch_geo<MODE, 32, 64, 16, 8, 8>(c, dw, pw);
-  if (C == 128 && N == 128) return launch_geo<MODE, 128, 128, 28, 4, 14>(c, dw, pw);
-  if (C == 256 && N == 256) return launch_geo<MODE, 256, 256, 28, 4, 8>(c, dw, pw);
+  if (C == 32 && N == 64) {
+    if (c.opt_tune & 1) return launch_geo<MODE, 32, 64, 16, 8, 8, 12>(c, dw, pw);
+    return launch_geo<MODE, 32, 64, 16, 8, 8, 8>(c, dw, pw);
+  }
+  if (C == 128 && N == 128) {
+    return launch_geo<MODE, 128, 128, 28, 4, 14, 8>(c, dw, pw);
+  }
+  if (C == 256 && N == 256) return launch_geo<MODE, 256, 256, 28, 4, 8, 8>(c, dw, pw);
   set_error(PULPNN_ERR_UNSUPPORTED, "fused depthwise+pointwise: no kernel for %d -> %d channels", C, N);
   return false;
 }

@@ -419,6 +419,12 @@ void add_entry(uint8_t *a, uint8_t *b, uint8_t *out, int m1, int m2, int out_shi
 // contraction dispatch: tensor cores where the shape allows, CUDA cores otherwise
 bool launch_conv(Context &c, const ConvProblem &p)
 {
+  // The SM-pair kernel: measured equal to the one-CTA kernel for K = 512 (0.054 against 0.053 ms on
+  // 14x14x512 -> 512 at batch 1024) and 3-5 % faster for K = 1024 (0.047 against 0.049 ms on 7x7x1024 ->
+  // 1024), slower below a few hundred rows per SM pair: taken for K >= 1024 and large M, or on request.
+  if (!c.opt_force_generic && c.opt_split_k == 0 && igemm_tc2_supported(c, p) &&
+      ((c.opt_tune & 8) || (p.Cin >= 1024 && ((long long)p.B * p.Ho * p.Wo / 256) * (p.Cout / 256) >= 4LL * 74)))
+    return launch_igemm_tc2(c, p);
   if (!c.opt_force_generic && igemm_tc_supported(c, p)) return launch_igemm_tc(c, p);
   if (!c.opt_force_generic && conv_smallcin_tc_supported(p)) return launch_conv_smallcin_tc(c, p);
   if (!c.opt_force_generic && conv_smallcin_supported(p)) return launch_conv_smallcin(c, p);

@@ -222,6 +222,9 @@ bool conv_smallcin_supported(const ConvProblem &p);
 bool launch_conv_smallcin(Context &c, const ConvProblem &p);
 bool igemm_tc_supported(const Context &c, const ConvProblem &p);
 bool launch_igemm_tc(Context &c, const ConvProblem &p);
+// the same GEMM computed by pairs of SMs (tcgen05 cta_group::2), for wide layers with a long reduction
+bool igemm_tc2_supported(const Context &c, const ConvProblem &p);
+bool launch_igemm_tc2(Context &c, const ConvProblem &p);
 bool launch_depthwise(Context &c, const DepthwiseProblem &p);
 bool depthwise_hwc3x3_supported(const DepthwiseProblem &p);
 bool launch_depthwise_hwc3x3(Context &c, const DepthwiseProblem &p);

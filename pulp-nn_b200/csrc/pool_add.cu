@@ -363,7 +363,7 @@ bool launch_avgpool(Context &c, const PoolProblem &p)
   const int chunks = (p.C + 127) / 128;
   const long long blocks_w = (long long)p.B * p.Ho * p.Wo * chunks;
   const long long threads16 = (long long)p.B * p.Ho * p.Wo * (p.C / 16);
-  const bool fills_gpu = p.C % 16 == 0 && threads16 >= 256LL * 2 * (c.sm_count > 0 ? c.sm_count : 148);
+  const bool fills_gpu = p.C % 16 == 0 && threads16 >= 32768;      // measured: from batch 512 of a 7x7x1024 pool on
   if (vec && p.kx * p.ky >= 32 && blocks_w < 0x7fffffffLL && !fills_gpu) {
     const cudaError_t le = launch_pdl(avgpool_window_kernel, dim3((unsigned)blocks_w), dim3(256), 0, c.stream, p, chunks);
     count_launch();

@@ -5,6 +5,10 @@
 // "mixed" tree that would is not part of it); they are here so that a caller that stores
 // activations or weights packed can widen them on the device before calling the 8-bit kernels.
 //
+// The scalar requantisers and threshold quantisers of the same header (pulp_nn_bn_quant_u4/u2,
+// pulp_nn_quant_u4/u2, pulp_nn_i4_quant, pulp_nn_i2_quant) and pulp_nn_avg_and_replace_int8 follow as
+// element-wise bulk operations.
+//
 // One thread widens one aligned 32-bit word (8 or 16 results, one 8- or 16-byte store); a byte-wise
 // tail and unaligned buffers go one input byte per thread.
 #include "internal.cuh"
@@ -90,11 +94,189 @@ void unpack_entry(const char *who, const void *in, void *out, unsigned int n_out
   st.finish();
 }
 
+// ---- scalar requantisers of the reference as bulk operations -----------------------------------------
+// pulp_nn_bn_quant_u8/u4/u2 and pulp_nn_quant_u8/u4/u2 (32bit/src/pulp_nn_utils.c:35-45,148-199; the
+// 64-bit tree widens k, lambda and the product to int64 and narrows the multiplier form to int16,
+// 64bit/src/pulp_nn_utils.c:34-198). Element i uses the parameters of channel i % channels.
+template <typename BN_T>
+__global__ void __launch_bounds__(256) bn_quant_bulk_kernel(const int *phi, const BN_T *k, const BN_T *lambda, int d,
+                                                            uint8_t *out, unsigned n, unsigned channels, int hi)
+{
+  const unsigned stride = gridDim.x * blockDim.x;
+  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const unsigned c = i % channels;
+    int x;
+    if (sizeof(BN_T) == 4)
+      x = (int)((unsigned)(int)__ldg(k + c) * (unsigned)__ldg(phi + i) + (unsigned)(int)__ldg(lambda + c)) >> d;
+    else      // the clip builtin takes an int: the shifted 64-bit value is cut to 32 bits first
+      x = (int)((long long)((unsigned long long)__ldg(k + c) * (unsigned long long)(long long)__ldg(phi + i) +
+                            (unsigned long long)__ldg(lambda + c)) >> d);
+    out[i] = (uint8_t)min(max(x, 0), hi);
+  }
+}
+
+// bits 8: x is cut to int16 in both trees; bits 4 and 2: int32 in the 32-bit tree, int16 in the 64-bit one
+__global__ void __launch_bounds__(256) quant_bulk_kernel(const int *phi, int m, int d, uint8_t *out, unsigned n, int hi,
+                                                         int narrow16)
+{
+  const unsigned stride = gridDim.x * blockDim.x;
+  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    int x = (int)((unsigned)m * (unsigned)__ldg(phi + i)) >> d;
+    if (narrow16) x = (int)(short)x;
+    out[i] = (uint8_t)min(max(x, 0), hi);
+  }
+}
+
+// pulp_nn_i4_quant / pulp_nn_i2_quant (32bit/src/pulp_nn_utils.c:438-540): a binary search over
+// sorted thresholds; with sorted thresholds its result is (number of thresholds below the input) + the
+// lowest level, which is what is computed here by following the same comparisons
+__global__ void __launch_bounds__(256) threshold_quant_kernel(const int *in, const short *thr, int8_t *out, unsigned n,
+                                                              unsigned channels, int bits)
+{
+  const unsigned stride = gridDim.x * blockDim.x;
+  const int pitch = bits == 4 ? 16 : 4;
+  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const short *t = thr + (size_t)(i % channels) * pitch;
+    const int v = __ldg(in + i);
+    int lo = 0, width = bits == 4 ? 16 : 4;      // the search tree of the reference: compare with the middle threshold
+    while (width > 1) {
+      const int mid = lo + width / 2 - 1;
+      if (!(v <= (int)__ldg(t + mid))) lo += width / 2;
+      width /= 2;
+    }
+    out[i] = (int8_t)(lo - (bits == 4 ? 8 : 2));
+  }
+}
+
+// pulp_nn_avg_and_replace_int8 (32bit/src/pulp_nn_utils.c:95-115): base[i] = (base[i] + target[i]) >> 1 on
+// signed bytes, for whole words of four only (length >> 2 words)
+__global__ void __launch_bounds__(256) avg_replace_kernel(int8_t *base, const int8_t *target, unsigned n)
+{
+  const unsigned stride = gridDim.x * blockDim.x;
+  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+    base[i] = (int8_t)(((int)base[i] + (int)target[i]) >> 1);
+}
+
+unsigned bulk_blocks(const Context &c, unsigned n)
+{
+  const unsigned want = (n + 255) / 256, cap = (unsigned)(c.sm_count > 0 ? c.sm_count : 148) * 16;
+  return want < cap ? want : cap;
+}
+
+int level_max(const char *who, int bits)
+{
+  if (bits == 8) return 255;
+  if (bits == 4) return 15;
+  if (bits == 2) return 3;
+  set_error(PULPNN_ERR_INVALID_ARG, "%s: bits must be 8, 4 or 2", who);
+  return -1;
+}
+
+template <typename BN_T>
+void bn_quant_entry(const char *who, const int32_t *phi, const BN_T *k, const BN_T *lambda, int d, uint8_t *out,
+                    unsigned n, unsigned channels, int bits)
+{
+  Context &c = ctx();
+  if (!ensure_device(c) || n == 0) return;
+  const int hi = level_max(who, bits);
+  if (hi < 0) return;
+  if (!phi || !k || !lambda || !out || channels == 0 || d < 0 || d > (sizeof(BN_T) == 4 ? 31 : 63)) {
+    set_error(PULPNN_ERR_INVALID_ARG, "%s: NULL pointer, no channels or shift out of range", who);
+    return;
+  }
+  Stager st(c);
+  const int *dphi = static_cast<const int *>(st.in(phi, (size_t)n * 4));
+  const BN_T *dk = static_cast<const BN_T *>(st.in(k, (size_t)channels * sizeof(BN_T)));
+  const BN_T *dl = static_cast<const BN_T *>(st.in(lambda, (size_t)channels * sizeof(BN_T)));
+  uint8_t *dout = static_cast<uint8_t *>(st.out(out, n));
+  if (!st.ok()) return;
+  bn_quant_bulk_kernel<BN_T><<<bulk_blocks(c, n), 256, 0, c.stream>>>(dphi, dk, dl, d, dout, n, channels, hi);
+  count_launch();
+  if (!cuda_ok(cudaGetLastError(), "bn_quant launch")) return;
+  st.finish();
+}
+
+void quant_entry(const char *who, int tree_bits, const int32_t *phi, int16_t m, int d, uint8_t *out, unsigned n, int bits)
+{
+  Context &c = ctx();
+  if (!ensure_device(c) || n == 0) return;
+  const int hi = level_max(who, bits);
+  if (hi < 0) return;
+  if (!phi || !out || d < 0 || d > 31) { set_error(PULPNN_ERR_INVALID_ARG, "%s: NULL pointer or shift out of range", who); return; }
+  Stager st(c);
+  const int *dphi = static_cast<const int *>(st.in(phi, (size_t)n * 4));
+  uint8_t *dout = static_cast<uint8_t *>(st.out(out, n));
+  if (!st.ok()) return;
+  const int narrow16 = (bits == 8 || tree_bits == 64) ? 1 : 0;
+  quant_bulk_kernel<<<bulk_blocks(c, n), 256, 0, c.stream>>>(dphi, (int)m, d, dout, n, hi, narrow16);
+  count_launch();
+  if (!cuda_ok(cudaGetLastError(), "quant launch")) return;
+  st.finish();
+}
+
 }  // namespace
 
 }  // namespace pulpnn
 
 extern "C" {
+
+void pulpnn_bn_quant_bulk_bn32(const int32_t *phi, const int32_t *k, const int32_t *lambda, int8_t d, uint8_t *out,
+                               unsigned int n, unsigned int channels, int bits)
+{
+  pulpnn::bn_quant_entry<int32_t>("pulpnn_bn_quant_bulk_bn32", phi, k, lambda, d, out, n, channels, bits);
+}
+void pulpnn_bn_quant_bulk_bn64(const int32_t *phi, const int64_t *k, const int64_t *lambda, int8_t d, uint8_t *out,
+                               unsigned int n, unsigned int channels, int bits)
+{
+  pulpnn::bn_quant_entry<long long>("pulpnn_bn_quant_bulk_bn64", phi, reinterpret_cast<const long long *>(k),
+                                    reinterpret_cast<const long long *>(lambda), d, out, n, channels, bits);
+}
+void pulpnn_quant_bulk_bn32(const int32_t *phi, int16_t m, int8_t d, uint8_t *out, unsigned int n, int bits)
+{
+  pulpnn::quant_entry("pulpnn_quant_bulk_bn32", 32, phi, m, d, out, n, bits);
+}
+void pulpnn_quant_bulk_bn64(const int32_t *phi, int16_t m, int8_t d, uint8_t *out, unsigned int n, int bits)
+{
+  pulpnn::quant_entry("pulpnn_quant_bulk_bn64", 64, phi, m, d, out, n, bits);
+}
+void pulpnn_threshold_quant_bulk(const int32_t *in, const int16_t *thr, int8_t *out, unsigned int n, unsigned int channels,
+                                 int bits)
+{
+  using namespace pulpnn;
+  const char *who = "pulpnn_threshold_quant_bulk";
+  Context &c = ctx();
+  if (!ensure_device(c) || n == 0) return;
+  if (!in || !thr || !out || channels == 0 || (bits != 4 && bits != 2)) {
+    set_error(PULPNN_ERR_INVALID_ARG, "%s: NULL pointer, no channels, or bits other than 4 and 2", who);
+    return;
+  }
+  Stager st(c);
+  const int *din = static_cast<const int *>(st.in(in, (size_t)n * 4));
+  const short *dthr = static_cast<const short *>(st.in(thr, (size_t)channels * (bits == 4 ? 16 : 4) * 2));
+  int8_t *dout = static_cast<int8_t *>(st.out(out, n));
+  if (!st.ok()) return;
+  threshold_quant_kernel<<<bulk_blocks(c, n), 256, 0, c.stream>>>(din, dthr, dout, n, channels, bits);
+  count_launch();
+  if (!cuda_ok(cudaGetLastError(), "threshold_quant launch")) return;
+  st.finish();
+}
+void pulp_nn_avg_and_replace_int8(int8_t *base, int8_t *target, uint16_t length)
+{
+  using namespace pulpnn;
+  Context &c = ctx();
+  if (!ensure_device(c)) return;
+  const unsigned n = (unsigned)(length >> 2) * 4u;        // whole words only, as the reference
+  if (n == 0) return;
+  if (!base || !target) { set_error(PULPNN_ERR_INVALID_ARG, "pulp_nn_avg_and_replace_int8: NULL pointer"); return; }
+  Stager st(c);
+  int8_t *db = static_cast<int8_t *>(st.inout(base, n));
+  const int8_t *dt = static_cast<const int8_t *>(st.in(target, n));
+  if (!st.ok()) return;
+  avg_replace_kernel<<<bulk_blocks(c, n), 256, 0, c.stream>>>(db, dt, n);
+  count_launch();
+  if (!cuda_ok(cudaGetLastError(), "avg_and_replace launch")) return;
+  st.finish();
+}
 
 void pulp_nn_im2col_u4_to_u8(uint8_t *pInput, uint8_t *pOutput, unsigned int blockSize)
 {

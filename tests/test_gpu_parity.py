@@ -663,3 +663,84 @@ def test_rejects_what_the_reference_leaves_undefined(gpu):
     with pytest.raises(pulpnn.PulpNNError) as e:       # in-place x pass would read pooled values
         gpu.maxpool(x, out_hw=(8, 8), kernel=(3, 3), pads=(1, 1, 1, 1), strides=(1, 1))
     assert e.value.code == api.ERR_UNSUPPORTED
+
+
+# ---- the GEMM computed by pairs of SMs --------------------------------------------------------------
+@pytest.mark.parametrize("cin,cout,hw,batch", [(512, 512, 14, 5), (512, 1024, 7, 9), (1024, 1024, 7, 6), (512, 256, 16, 1),
+                                               (1024, 768, 9, 4), (640, 512, 14, 3), (512, 512, 14, 160)])
+def test_pointwise_sm_pair_kernel_shapes(cin, cout, hw, batch, gpu, restatement):
+    """Wide layers with a long reduction on the tcgen05 cta_group::2 kernel (two CTAs share a 256-row
+    tile, each holds half of the weight tile): one and two resident column tiles, one or several
+    column groups, row counts that leave the last pair of tiles ragged or half empty, more row pairs
+    than SM pairs."""
+    api.set_option(api.OPT_TUNE, 8)
+    try:
+        c = wl.pointwise_case(81, hw, hw, cin, cout, batch=batch, bits=32, out_shift=wl.ceil_log2(cin) + 3,
+                              w_range=(-128, 127))
+        want = restatement.pointwise(32, c["x"], c["w"], c["k"], c["lam"], **pw_kw(c))
+        assert np.count_nonzero(want) > want.size // 20
+        same(gpu.pointwise(32, c["x"], c["w"], c["k"], c["lam"], **pw_kw(c)), want)
+    finally:
+        api.set_option(api.OPT_TUNE, 0)
+    assert api.device_status() == 0
+
+
+@pytest.mark.parametrize("bits", [32, 64])
+@pytest.mark.parametrize("relu,bn", MODES)
+def test_pointwise_sm_pair_kernel_modes(bits, relu, bn, gpu, restatement):
+    api.set_option(api.OPT_TUNE, 8)
+    try:
+        c = wl.pointwise_case(82, 11, 13, 512, 512, batch=3, bits=bits, out_shift=12, with_bias=True, out_mult=3,
+                              relu=relu, bn=bn, w_range=(-128, 127))
+        want = restatement.pointwise(bits, c["x"], c["w"], c["k"], c["lam"], **pw_kw(c))
+        same(gpu.pointwise(bits, c["x"], c["w"], c["k"], c["lam"], **pw_kw(c)), want)
+    finally:
+        api.set_option(api.OPT_TUNE, 0)
+    assert api.device_status() == 0
+
+
+# ---- the scalar sub-byte requantisers of pulp_nn_utils.h as bulk operations -------------------------
+@pytest.mark.parametrize("bits", [32, 64])
+def test_bulk_quantisers_against_the_compiled_reference(bits, gpu_host, reference32, reference64):
+    """pulp_nn_bn_quant_u8/u4/u2, pulp_nn_quant_u8/u4/u2, pulp_nn_i4_quant / pulp_nn_i2_quant and
+    pulp_nn_avg_and_replace_int8 element by element from the reference's own compiled code, both
+    trees, device and host buffers, values that overflow 32 bits and cross every clip boundary."""
+    import torch
+    ref = reference32 if bits == 32 else reference64
+    rng = np.random.default_rng(90 + bits)
+    n, ch = 1537, 13
+    dt = np.int32 if bits == 32 else np.int64
+    phi = rng.integers(-2 ** 20, 2 ** 20, size=n).astype(np.int32)
+    phi[:8] = [0, 1, -1, 2 ** 31 - 1, -2 ** 31, 255, 256, -255]
+    for (krange, lrange, d) in (((1, 64), (-32768, 32767), 9), ((-2 ** 20, 2 ** 20), (-2 ** 30, 2 ** 30), 17)):
+        k = rng.integers(krange[0], krange[1] + 1, size=ch).astype(dt)
+        lam = rng.integers(lrange[0], lrange[1] + 1, size=ch).astype(dt)
+        for out_bits in (8, 4, 2):
+            want = ref.scalar_bn_quant(out_bits, phi, k, lam, d)
+            for dev in (True, False):
+                out = torch.zeros(n, dtype=torch.uint8, device="cuda") if dev else np.zeros(n, np.uint8)
+                args = [torch.from_numpy(a).cuda() if dev else a for a in (phi, k, lam)]
+                api.pulpnn_bn_quant_bulk(bits, args[0], args[1], args[2], d, out, n, ch, out_bits)
+                api.synchronize()
+                same(out.cpu().numpy() if dev else out, want)
+    for (m, d) in ((3, 4), (-7, 2), (32767, 15), (300, 0)):
+        for out_bits in (8, 4, 2):
+            want = ref.scalar_quant(out_bits, phi, m, d)
+            out = np.zeros(n, np.uint8)
+            api.pulpnn_quant_bulk(bits, phi, m, d, out, n, out_bits)
+            same(out, want)
+    x = rng.integers(-40000, 40000, size=n).astype(np.int32)
+    for out_bits, width in ((4, 16), (2, 4)):
+        thr = np.sort(rng.integers(-32768, 32768, size=(ch, width)), axis=1).astype(np.int16)
+        x[:ch * width] = thr.reshape(-1)                     # inputs equal to a threshold: "<=" decides
+        want = ref.scalar_threshold_quant(out_bits, x, thr)
+        out = np.zeros(n, np.int8)
+        api.pulpnn_threshold_quant_bulk(x, thr, out, n, ch, out_bits)
+        same(out, want)
+    base = rng.integers(-128, 128, size=1003).astype(np.int8)
+    target = rng.integers(-128, 128, size=1003).astype(np.int8)
+    want = ref.avg_and_replace(base, target)
+    got = base.copy()
+    api.pulp_nn_avg_and_replace_int8(got, target, got.size)
+    same(got, want)
+    assert np.array_equal(got[1000:], base[1000:])           # the last three bytes are not a whole word
