@@ -324,6 +324,15 @@ int  pulpnn_net_finalize(pulpnn_net_t *net, int micro_batch);
  * layer's output). Either may be host or device memory. Enqueues on the calling
  * thread's stream; synchronises only if a host buffer is involved. */
 int  pulpnn_net_run(pulpnn_net_t *net, const uint8_t *input, void *output, int n_images);
+/* The same with HOST buffers (pinned memory for real overlap), without waiting: the copies and the
+ * kernels of this batch are enqueued and the call returns a ticket (0 or 1; a negative value is
+ * minus an error code). pulpnn_net_wait(net, ticket) returns once the batch's results are in
+ * `output`. Two batches can be in flight, so in a loop that submits batch i+1 before it waits for
+ * batch i the input copy of one batch runs under the compute of the other and the step time is the
+ * longer of the two instead of their sum. `input` must stay valid and `output` untouched until the
+ * wait; submitting a third batch waits for the first by itself. */
+int  pulpnn_net_submit(pulpnn_net_t *net, const uint8_t *input, void *output, int n_images);
+int  pulpnn_net_wait(pulpnn_net_t *net, int ticket);
 /* Test hook: run the first n_layers layers only and copy that layer's output. */
 int  pulpnn_net_run_prefix(pulpnn_net_t *net, const uint8_t *input, void *output, int n_images,
                            int n_layers);

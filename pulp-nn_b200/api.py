@@ -359,6 +359,18 @@ class Net:
         if rc != OK:
             _check()
 
+    def submit(self, input_, output, n_images):
+        """Host buffers, no waiting: returns a ticket for wait(). Two batches may be in flight."""
+        t = self.lib.pulpnn_net_submit(self.handle, _ptr(input_), _ptr(output), int(n_images))
+        if t < 0:
+            _check()
+            raise PulpNNError(-t, "pulpnn_net_submit failed")
+        return t
+
+    def wait(self, ticket):
+        if self.lib.pulpnn_net_wait(self.handle, int(ticket)) != OK:
+            _check()
+
     def run_timed(self, input_, output, n_images):
         """Device buffers only. Returns the per-layer milliseconds of this run."""
         ms = (C.c_float * self.num_layers())()

@@ -45,8 +45,8 @@ using namespace dwregs;
 constexpr int ST_F_TMA = 0x10000, ST_F_BUILD = 0x20000, ST_F_MMA = 0x40000, ST_F_EPI = 0x80000;
 
 // geometry, all compile-time: C input channels, N output channels, patch of TH x TW pixels
-template <int C, int N, int TW, int TH, int BW, int EW> struct FG {
-  static constexpr int NSRV = (C <= 64) ? 2 : 1;              // TMA warps = MMA warps; they take units in turn
+template <int C, int N, int TW, int TH, int BW, int EW, int SRV> struct FG {
+  static constexpr int NSRV = SRV;            // TMA warps = MMA warps; they take units in turn
   static constexpr int FIRST_MMA = NSRV, FIRST_BUILD = 2 * NSRV;
   static constexpr int BUILD_WARPS = BW;                      // depthwise builder warps
   static constexpr int EPI_WARPS_N = EW;                      // epilogue warps: groups of four (one per TMEM lane quarter)
@@ -141,12 +141,12 @@ __device__ __forceinline__ void finalize_to_a(const int (&acc)[4][4], const Quan
   }
 }
 
-template <int MODE, int C, int N, int TW, int TH, int BW, int EW>
-__global__ void __launch_bounds__((FG<C, N, TW, TH, BW, EW>::THREADS), 1)
+template <int MODE, int C, int N, int TW, int TH, int BW, int EW, int SRV>
+__global__ void __launch_bounds__((FG<C, N, TW, TH, BW, EW, SRV>::THREADS), 1)
 dwpw_fused_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_constant__ CUtensorMap map_w,
                   const FusedParams g)
 {
-  using G = FG<C, N, TW, TH, BW, EW>;
+  using G = FG<C, N, TW, TH, BW, EW, SRV>;
   constexpr int CI = G::CI;
   constexpr int THREADS = G::THREADS, FIRST_EPI = G::FIRST_EPI, FIRST_BUILD = G::FIRST_BUILD, FIRST_MMA = G::FIRST_MMA;
   constexpr int NSRV = G::NSRV;
@@ -448,10 +448,10 @@ dwpw_fused_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_const
 }
 
 // ---- host side ----------------------------------------------------------------------------------
-template <int MODE, int C, int N, int TW, int TH, int BW, int EW>
+template <int MODE, int C, int N, int TW, int TH, int BW, int EW, int SRV>
 bool launch_geo(Context &c, const DepthwiseProblem &dw, const ConvProblem &pw)
 {
-  using G = FG<C, N, TW, TH, BW, EW>;
+  using G = FG<C, N, TW, TH, BW, EW, SRV>;
   EncodeTiledFn enc = encode_tiled_fn();
   FusedParams g;
   g.in = dw.in; g.out = static_cast<uint8_t *>(pw.out); g.w_dw = dw.w;
@@ -499,7 +499,7 @@ bool launch_geo(Context &c, const DepthwiseProblem &dw, const ConvProblem &pw)
                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { set_error(PULPNN_ERR_CUDA, "cuTensorMapEncodeTiled (fused weights) failed with code %d", (int)r); return false; }
   }
-  auto kern = dwpw_fused_kernel<MODE, C, N, TW, TH, BW, EW>;
+  auto kern = dwpw_fused_kernel<MODE, C, N, TW, TH, BW, EW, SRV>;
   static PerDeviceInt attr_set;
   if (!attr_set.get(c.device)) {
     if (!cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM),
@@ -520,15 +520,17 @@ bool launch_shape(Context &c, const DepthwiseProblem &dw, const ConvProblem &pw)
 {
   const int C = dw.C, N = pw.Cout;
   // patch shapes: 16 x 8 tiles a 112-wide image exactly; 28 x 4 tiles 56- and 28-wide ones (measured
-  // against 8 x 16 on 56 x 56 x 128: 0.243 ms against 0.272 ms at batch 1024)
+  // against 8 x 16 on 56 x 56 x 128: 0.243 ms against 0.272 ms at batch 1024). Measured and dropped on
+  // the 32-channel pair at batch 1024 (0.342 ms as configured): twelve builder warps (0.375 with one TMA
+  // and one MMA warp either way), three epilogue groups (0.345), four TMA and four MMA warps (0.362);
+  // on the 128-channel pair two TMA and two MMA warps (0.276 against 0.243)
   if (C == 32 && N == 64) {
-    if (c.opt_tune & 1) return launch_geo<MODE, 32, 64, 16, 8, 8, 12>(c, dw, pw);
-    return launch_geo<MODE, 32, 64, 16, 8, 8, 8>(c, dw, pw);
+    return launch_geo<MODE, 32, 64, 16, 8, 8, 8, 2>(c, dw, pw);
   }
   if (C == 128 && N == 128) {
-    return launch_geo<MODE, 128, 128, 28, 4, 14, 8>(c, dw, pw);
+    return launch_geo<MODE, 128, 128, 28, 4, 14, 8, 1>(c, dw, pw);
   }
-  if (C == 256 && N == 256) return launch_geo<MODE, 256, 256, 28, 4, 8, 8>(c, dw, pw);
+  if (C == 256 && N == 256) return launch_geo<MODE, 256, 256, 28, 4, 8, 8, 1>(c, dw, pw);
   set_error(PULPNN_ERR_UNSUPPORTED, "fused depthwise+pointwise: no kernel for %d -> %d channels", C, N);
   return false;
 }

@@ -419,6 +419,7 @@ void add_entry(uint8_t *a, uint8_t *b, uint8_t *out, int m1, int m2, int out_shi
 // contraction dispatch: tensor cores where the shape allows, CUDA cores otherwise
 bool launch_conv(Context &c, const ConvProblem &p)
 {
+  if (!c.opt_force_generic && c.opt_split_k == 0 && !(c.opt_tune & 16) && gemm_fewrows_supported(p)) return launch_gemm_fewrows(c, p);
   // The SM-pair kernel: measured equal to the one-CTA kernel for K = 512 (0.054 against 0.053 ms on
   // 14x14x512 -> 512 at batch 1024) and 3-5 % faster for K = 1024 (0.047 against 0.049 ms on 7x7x1024 ->
   // 1024), slower below a few hundred rows per SM pair: taken for K >= 1024 and large M, or on request.

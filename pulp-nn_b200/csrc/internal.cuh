@@ -225,6 +225,9 @@ bool launch_igemm_tc(Context &c, const ConvProblem &p);
 // the same GEMM computed by pairs of SMs (tcgen05 cta_group::2), for wide layers with a long reduction
 bool igemm_tc2_supported(const Context &c, const ConvProblem &p);
 bool launch_igemm_tc2(Context &c, const ConvProblem &p);
+// the same contraction for few rows (a fully connected layer at a small batch), on dp4a
+bool gemm_fewrows_supported(const ConvProblem &p);
+bool launch_gemm_fewrows(Context &c, const ConvProblem &p);
 bool launch_depthwise(Context &c, const DepthwiseProblem &p);
 bool depthwise_hwc3x3_supported(const DepthwiseProblem &p);
 bool launch_depthwise_hwc3x3(Context &c, const DepthwiseProblem &p);

@@ -40,6 +40,14 @@ struct pulpnn_net {
   uint8_t *stage_in = nullptr; size_t stage_in_cap = 0;
   uint8_t *stage_out = nullptr; size_t stage_out_cap = 0;
   cudaStream_t copy_stream = nullptr;
+  // pipelined host-buffer runs (pulpnn_net_submit / pulpnn_net_wait): two staging slots, so that the
+  // copies of one batch overlap the compute of the other
+  uint8_t *slot_in[2] = {nullptr, nullptr}, *slot_out[2] = {nullptr, nullptr};
+  size_t slot_in_cap[2] = {0, 0}, slot_out_cap[2] = {0, 0};
+  cudaStream_t out_stream = nullptr;
+  cudaEvent_t ev_compute[2] = {nullptr, nullptr}, ev_out[2] = {nullptr, nullptr};
+  bool slot_busy[2] = {false, false};
+  unsigned long long submitted = 0;
   unsigned long long launches_last_run = 0;
   std::vector<char> role_last_run;         // per layer: 0 own kernel, 1 / 2 first / second layer of a fused pair
   cudaEvent_t ev_in[2] = {nullptr, nullptr}, ev_done[2] = {nullptr, nullptr};
@@ -185,6 +193,37 @@ bool run_device(Context &c, pulpnn_net *net, const uint8_t *din, uint8_t *dout, 
   return true;
 }
 
+// Host input: copied in a few slices on a second stream, each slice going through the whole stack as
+// soon as it has landed, so that the copy of slice i+1 overlaps the compute of slice i. With a
+// micro-batch set, a slice is a whole number of micro-batches.
+bool enqueue_sliced(Context &c, pulpnn_net *net, const uint8_t *input, uint8_t *stage, uint8_t *dout, int n, int n_layers)
+{
+  const int micro = net->micro > 0 ? net->micro : n;
+  int sizes[64];
+  int n_slices = 0;
+  {
+    const int want = 4;        // measured at batch 1024: 5 slices lose 2 %, 6 lose 5 %, 8 lose 7 %
+    const int part = (n + want - 1) / want;
+    int slice = micro < part ? micro : part;
+    while (slice < n && slice * want < n) slice += micro;
+    for (int left = n; left > 0 && n_slices < 64; left -= slice) sizes[n_slices++] = left < slice ? left : slice;
+  }
+  const size_t img_in = net->layers.front().in_bytes, img_out = net->layers[n_layers - 1].out_bytes;
+  int i0 = 0;
+  for (int idx = 0; idx < n_slices; idx++) {
+    const int nb = sizes[idx];
+    cudaEvent_t ev = net->ev_in[idx & 1];
+    if (!cuda_ok(cudaMemcpyAsync(stage + (size_t)i0 * img_in, input + (size_t)i0 * img_in,
+                                 (size_t)nb * img_in, cudaMemcpyHostToDevice, net->copy_stream), "H2D copy"))
+      return false;
+    cudaEventRecord(ev, net->copy_stream);
+    cudaStreamWaitEvent(c.stream, ev, 0);
+    if (!run_device(c, net, stage + (size_t)i0 * img_in, dout + (size_t)i0 * img_out, nb, n_layers)) return false;
+    i0 += nb;
+  }
+  return true;
+}
+
 int run_impl(pulpnn_net *net, const uint8_t *input, void *output, int n, int n_layers)
 {
   Context &c = ctx();
@@ -222,36 +261,10 @@ int run_impl(pulpnn_net *net, const uint8_t *input, void *output, int n, int n_l
   if (in_dev) {
     if (!run_device(c, net, din, dout, n, n_layers)) return c.err;
   } else {
-    // Host input: copy in a few slices on a second stream, each slice going through the whole stack
-    // as soon as it has landed, so that the copy of slice i+1 overlaps the compute of slice i. The
-    // copy is the longer of the two (154 MB of images take longer to cross PCIe than to classify),
-    // so what the overlap cannot hide is the compute of the last slice; equal slices measured best
-    // (slices that shrink let the compute of the large early ones fall behind the copies: 252 K
-    // images/s against 274 K). With a micro-batch set, a slice is a whole number of micro-batches.
-    const int micro = net->micro > 0 ? net->micro : n;
-    int sizes[64];
-    int n_slices = 0;
-    {
-      const int want = 4;        // measured at batch 1024: 5 slices lose 2 %, 6 lose 5 %, 8 lose 7 %
-      const int part = (n + want - 1) / want;
-      int slice = micro < part ? micro : part;
-      while (slice < n && slice * want < n) slice += micro;
-      for (int left = n; left > 0 && n_slices < 64; left -= slice) sizes[n_slices++] = left < slice ? left : slice;
-    }
-    const size_t img_in = net->layers.front().in_bytes, img_out = net->layers[n_layers - 1].out_bytes;
-    int i0 = 0;
-    for (int idx = 0; idx < n_slices; idx++) {
-      const int nb = sizes[idx];
-      cudaEvent_t ev = net->ev_in[idx & 1];
-      if (!cuda_ok(cudaMemcpyAsync(net->stage_in + (size_t)i0 * img_in, input + (size_t)i0 * img_in,
-                                   (size_t)nb * img_in, cudaMemcpyHostToDevice, net->copy_stream), "H2D copy"))
-        return c.err;
-      cudaEventRecord(ev, net->copy_stream);
-      cudaStreamWaitEvent(c.stream, ev, 0);
-      if (!run_device(c, net, net->stage_in + (size_t)i0 * img_in, dout + (size_t)i0 * img_out, nb, n_layers))
-        return c.err;
-      i0 += nb;
-    }
+    // The copy is the longer of the two (154 MB of images take longer to cross PCIe than to classify),
+    // so what the overlap inside one call cannot hide is the compute of the last slice; equal slices
+    // measured best. pulpnn_net_submit / pulpnn_net_wait hide that too, under the next batch's copy.
+    if (!enqueue_sliced(c, net, input, net->stage_in, dout, n, n_layers)) return c.err;
   }
   net->launches_last_run = thread_launch_count() - launches0;
   if (!out_dev) {
@@ -395,6 +408,70 @@ int pulpnn_net_run(pulpnn_net_t *net, const uint8_t *input, void *output, int n_
   return run_impl(net, input, output, n_images, net ? (int)net->layers.size() : 0);
 }
 
+int pulpnn_net_submit(pulpnn_net_t *net, const uint8_t *input, void *output, int n_images)
+{
+  Context &c = ctx();
+  if (!ensure_device(c)) return -c.err;
+  if (!net || !net->finalized || !input || !output || n_images < 1 || n_images > net->max_batch) {
+    set_error(PULPNN_ERR_INVALID_ARG, "pulpnn_net_submit: bad arguments");
+    return -c.err;
+  }
+  if (is_device_ptr(input) || is_device_ptr(output)) {
+    set_error(PULPNN_ERR_INVALID_ARG, "pulpnn_net_submit is for host buffers; device buffers need no staging: use pulpnn_net_run");
+    return -c.err;
+  }
+  const int nl = (int)net->layers.size();
+  const int b = (int)(net->submitted & 1);
+  if (net->slot_busy[b]) {            // the caller did not collect this slot's previous batch: do it for him
+    if (!cuda_ok(cudaEventSynchronize(net->ev_out[b]), "cudaEventSynchronize")) return -c.err;
+    net->slot_busy[b] = false;
+  }
+  const size_t in_b = net->layers.front().in_bytes * n_images, out_b = net->layers[nl - 1].out_bytes * n_images;
+  if (!net->out_stream) {
+    if (!cuda_ok(cudaStreamCreateWithFlags(&net->out_stream, cudaStreamNonBlocking), "cudaStreamCreate")) return -c.err;
+    for (int i = 0; i < 2; i++) {
+      if (!cuda_ok(cudaEventCreateWithFlags(&net->ev_compute[i], cudaEventDisableTiming), "cudaEventCreate")) return -c.err;
+      if (!cuda_ok(cudaEventCreateWithFlags(&net->ev_out[i], cudaEventDisableTiming), "cudaEventCreate")) return -c.err;
+    }
+  }
+  if (net->slot_in_cap[b] < in_b) {
+    if (net->slot_in[b]) { cudaDeviceSynchronize(); cudaFree(net->slot_in[b]); net->slot_in[b] = nullptr; net->slot_in_cap[b] = 0; }
+    if (!cuda_ok(cudaMalloc(&net->slot_in[b], in_b), "cudaMalloc(input staging)")) return -c.err;
+    net->slot_in_cap[b] = in_b;
+  }
+  if (net->slot_out_cap[b] < out_b) {
+    if (net->slot_out[b]) { cudaDeviceSynchronize(); cudaFree(net->slot_out[b]); net->slot_out[b] = nullptr; net->slot_out_cap[b] = 0; }
+    if (!cuda_ok(cudaMalloc(&net->slot_out[b], out_b), "cudaMalloc(output staging)")) return -c.err;
+    net->slot_out_cap[b] = out_b;
+  }
+  // this slot's staging buffers were last used two batches ago: the copies wait for that batch's
+  // compute to have read the input, the compute for its results to have left
+  if (net->submitted >= 2) {
+    cudaStreamWaitEvent(net->copy_stream, net->ev_compute[b], 0);
+    cudaStreamWaitEvent(c.stream, net->ev_out[b], 0);
+  }
+  const unsigned long long launches0 = thread_launch_count();
+  if (!enqueue_sliced(c, net, input, net->slot_in[b], net->slot_out[b], n_images, nl)) return -c.err;
+  net->launches_last_run = thread_launch_count() - launches0;
+  cudaEventRecord(net->ev_compute[b], c.stream);
+  cudaStreamWaitEvent(net->out_stream, net->ev_compute[b], 0);
+  if (!cuda_ok(cudaMemcpyAsync(output, net->slot_out[b], out_b, cudaMemcpyDeviceToHost, net->out_stream), "D2H copy")) return -c.err;
+  cudaEventRecord(net->ev_out[b], net->out_stream);
+  net->slot_busy[b] = true;
+  net->submitted++;
+  return b;
+}
+
+int pulpnn_net_wait(pulpnn_net_t *net, int ticket)
+{
+  Context &c = ctx();
+  if (!net || ticket < 0 || ticket > 1) { set_error(PULPNN_ERR_INVALID_ARG, "pulpnn_net_wait: bad ticket"); return c.err; }
+  if (!net->slot_busy[ticket]) return PULPNN_OK;
+  if (!cuda_ok(cudaEventSynchronize(net->ev_out[ticket]), "cudaEventSynchronize")) return c.err;
+  net->slot_busy[ticket] = false;
+  return PULPNN_OK;
+}
+
 int pulpnn_net_run_prefix(pulpnn_net_t *net, const uint8_t *input, void *output, int n_images, int n_layers)
 {
   return run_impl(net, input, output, n_images, n_layers);
@@ -466,6 +543,13 @@ void pulpnn_net_destroy(pulpnn_net_t *net)
   }
   if (net->stage_in) cudaFree(net->stage_in);
   if (net->stage_out) cudaFree(net->stage_out);
+  for (int i = 0; i < 2; i++) {
+    if (net->slot_in[i]) cudaFree(net->slot_in[i]);
+    if (net->slot_out[i]) cudaFree(net->slot_out[i]);
+    if (net->ev_compute[i]) cudaEventDestroy(net->ev_compute[i]);
+    if (net->ev_out[i]) cudaEventDestroy(net->ev_out[i]);
+  }
+  if (net->out_stream) cudaStreamDestroy(net->out_stream);
   if (net->copy_stream) cudaStreamDestroy(net->copy_stream);
   delete net;
 }

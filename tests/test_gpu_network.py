@@ -113,3 +113,35 @@ def test_mobilenet_prefixes_at_a_large_batch(restatement):
         assert np.array_equal(got, w), "layer %d (%s) differs at batch %d" % (l, params[l]["name"], B)
     assert api.device_status() == 0
     net.close()
+
+
+def test_pipelined_host_batches_match_one_call_at_a_time(restatement):
+    """pulpnn_net_submit / pulpnn_net_wait with two batches in flight: five different batches (sizes
+    that change from one to the next) must give the logits of pulpnn_net_run, and the first image of
+    every batch the CPU checker's."""
+    import torch
+    pulpnn.GpuKernels()
+    params = wl.mobilenet_params(seed=4, bits=32, shift_bias=1)
+    net = api.build_mobilenet_v1(params, bits=32, max_batch=24)
+    sizes = [24, 7, 16, 24, 1]
+    xs = [torch.from_numpy(wl.mobilenet_input(30 + i, n)).pin_memory() for i, n in enumerate(sizes)]
+    outs = [torch.full((n, 1000), -1, dtype=torch.int32).pin_memory() for n in sizes]
+    prev = None
+    for x, o, n in zip(xs, outs, sizes):
+        t = net.submit(x, o, n)
+        if prev is not None:
+            net.wait(prev)
+        prev = t
+    net.wait(prev)
+    assert api.device_status() == 0
+    for i, (x, o, n) in enumerate(zip(xs, outs, sizes)):
+        want = np.zeros((n, 1000), np.int32)
+        net.run(x.numpy(), want, n)
+        assert np.array_equal(o.numpy(), want), "batch %d differs from the one-call-at-a-time run" % i
+        first = mobilenet_chain(restatement, params, x.numpy()[:1])[-1]
+        assert np.array_equal(o.numpy()[:1], first)
+    # device buffers are refused: they need no staging
+    d = torch.zeros((1, 224, 224, 3), dtype=torch.uint8, device="cuda")
+    with pytest.raises(pulpnn.PulpNNError):
+        net.submit(d, outs[4], 1)
+    net.close()

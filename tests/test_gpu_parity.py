@@ -744,3 +744,27 @@ def test_bulk_quantisers_against_the_compiled_reference(bits, gpu_host, referenc
     api.pulp_nn_avg_and_replace_int8(got, target, got.size)
     same(got, want)
     assert np.array_equal(got[1000:], base[1000:])           # the last three bytes are not a whole word
+
+
+@pytest.mark.parametrize("bits", [32, 64])
+@pytest.mark.parametrize("relu,bn", MODES)
+def test_linear_few_rows_kernel(bits, relu, bn, gpu, restatement):
+    """Few rows (M <= 256) and a long reduction take the dp4a kernel that keeps eight neurons' weights
+    per CTA: neuron counts that are not a multiple of eight, K that is not a multiple of 512, one row,
+    the largest row count; and the same calls on the tensor-core kernel (the switch bit 16) agree."""
+    for (K, N, B) in ((1024, 1000, 128), (272, 1001, 3), (4096, 67, 1), (2048, 256, 256), (1040, 8, 77)):
+        c = wl.linear_case(44, K, N, batch=B, bits=bits, out_shift=wl.ceil_log2(K) + 4, out_mult=3, relu=relu, bn=bn,
+                           w_range=(-128, 127))
+        kw = dict(bias=c["bias"], out_mult=c["out_mult"], out_shift=c["out_shift"], relu=relu, bn=bn)
+        want = restatement.linear(bits, c["x"], c["w"], c["k"], c["lam"], **kw)
+        launches = api.launch_count()
+        same(gpu.linear(bits, c["x"], c["w"], c["k"], c["lam"], **kw), want)
+        assert api.launch_count() - launches == 1, "expected the one-kernel few-rows path"
+        if (relu, bn) == (1, 1):
+            want32 = restatement.linear_out_32(c["x"], c["w"], bias32=c["bias32"])
+            same(gpu.linear_out_32(c["x"], c["w"], bias32=c["bias32"], bits=bits), want32)
+            api.set_option(api.OPT_TUNE, 16)
+            try:
+                same(gpu.linear_out_32(c["x"], c["w"], bias32=c["bias32"], bits=bits), want32)
+            finally:
+                api.set_option(api.OPT_TUNE, 0)
