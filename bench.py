@@ -409,9 +409,7 @@ def run_gpu_arm(args):
     while idx < len(params):
         L, r, t_ms = params[idx], rows[idx], float(layer_ms[idx])
         name, ops, nbytes = L["name"], r["ops"], r["bytes"]
-        kname = {"conv": "conv_smallcin_tc_kernel", "depthwise": "depthwise_hwc3x3_tma_kernel",
-                 "pointwise": "igemm_tc_kernel", "avgpool": "avgpool_kernel",
-                 "linear32": "igemm_tc_kernel"}[L["op"]]
+        kname = job.net.layer_kernel(idx) or L["op"]
         step = 1
         if roles[idx] == 1:
             # a depthwise + pointwise pair run as one kernel: one entry, the pair's operations, and as
@@ -422,7 +420,7 @@ def run_gpu_arm(args):
             t_ms += float(layer_ms[idx + 1])
             ops += r2["ops"]
             nbytes = L["H"] * L["W"] * L["Cin"] + params[idx + 1]["Ho"] * params[idx + 1]["Wo"] * params[idx + 1]["Cout"]
-            kname, step = "dwpw_fused_kernel", 2
+            step = 2
         gb, gop = nbytes * B / 1e9, ops * B / 1e9
         entry_ = {"layer": name, "ms": round(t_ms, 4),
                   "GOPs": round(gop / (t_ms / 1e3), 1), "GBs": round(gb / (t_ms / 1e3), 1),

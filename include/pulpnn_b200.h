@@ -346,6 +346,9 @@ size_t pulpnn_net_layer_output_bytes(const pulpnn_net_t *net, int layer);   /* p
 /* How layer `layer` ran in the most recent run: 0 = a kernel of its own, 1 / 2 = the first /
  * second layer of a pair executed as one fused kernel (PULPNN_OPT_FUSE_DWPW); -1 = no such layer. */
 int  pulpnn_net_layer_role(const pulpnn_net_t *net, int layer);
+/* The kernel family that ran layer `layer` in the most recent run ("igemm_tc_kernel", ...), for
+ * measurement tables; "" before the first run. */
+const char *pulpnn_net_layer_kernel(const pulpnn_net_t *net, int layer);
 /* Kernel launches the most recent pulpnn_net_run / _run_prefix / _run_timed of this network made
  * (0 before the first run). n_images is ignored. */
 unsigned long long pulpnn_net_launches_per_run(const pulpnn_net_t *net, int n_images);

@@ -110,6 +110,7 @@ def load_library():
     _lib.pulpnn_net_create.restype = C.c_void_p
     _lib.pulpnn_net_layer_output_bytes.restype = C.c_size_t
     _lib.pulpnn_net_launches_per_run.restype = C.c_ulonglong
+    _lib.pulpnn_net_layer_kernel.restype = C.c_char_p
     return _lib
 
 

@@ -385,6 +385,10 @@ class Net:
         """0: own kernel; 1 / 2: first / second layer of a fused pair (in the most recent run)."""
         return int(self.lib.pulpnn_net_layer_role(self.handle, int(layer)))
 
+    def layer_kernel(self, layer):
+        """Kernel family that ran the layer in the most recent run."""
+        return (self.lib.pulpnn_net_layer_kernel(self.handle, int(layer)) or b"").decode()
+
     def layer_output_bytes(self, layer):
         return int(self.lib.pulpnn_net_layer_output_bytes(self.handle, int(layer)))
 

@@ -25,6 +25,14 @@ void count_launch(unsigned n)
 }
 unsigned long long thread_launch_count() { return t_launches; }
 
+static thread_local const char *t_last_kernel = "";
+void count_launch(const char *kernel_name)
+{
+  count_launch(1u);
+  t_last_kernel = kernel_name;
+}
+const char *thread_last_kernel() { return t_last_kernel; }
+
 void set_error(int code, const char *fmt, ...)
 {
   Context &c = ctx();

@@ -184,7 +184,7 @@ bool launch_conv_generic(Context &c, const ConvProblem &p)
                      ((reinterpret_cast<uintptr_t>(p.w) & 3) == 0);
   if (words) launch_mode<true>(g, grid, c.stream);
   else       launch_mode<false>(g, grid, c.stream);
-  count_launch();
+  count_launch("conv_generic_kernel");
   return cuda_ok(cudaGetLastError(), "conv_generic launch");
 }
 

@@ -227,7 +227,7 @@ bool launch_conv_smallcin(Context &c, const ConvProblem &p)
     case EPI_BN32: conv_smallcin_kernel<EPI_BN32><<<grid, 256, smem, c.stream>>>(g); break;
     default:       conv_smallcin_kernel<EPI_BN64><<<grid, 256, smem, c.stream>>>(g); break;
   }
-  count_launch();
+  count_launch("conv_smallcin_kernel");
   return cuda_ok(cudaGetLastError(), "conv_smallcin launch");
 }
 

@@ -340,7 +340,7 @@ bool launch_cfg(Context &c, const CUtensorMap &map, const SmallTcParams &g)
   const int sms = c.sm_count > 0 ? c.sm_count : 148;
   const int grid = g.units < sms ? g.units : sms;
   const cudaError_t le = launch_pdl(kern, dim3(grid), dim3(THREADS), smem, c.stream, map, g);
-  count_launch();
+  count_launch("conv_smallcin_tc_kernel");
   return cuda_ok(le, "conv_smallcin_tc launch") && cuda_ok(cudaGetLastError(), "conv_smallcin_tc launch");
 }
 

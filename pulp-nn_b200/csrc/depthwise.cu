@@ -255,7 +255,7 @@ bool launch_dw_mode(Context &c, const DepthwiseProblem &p)
       depthwise_hwc1_kernel<MODE><<<(unsigned)((total + 255) / 256), 256, 0, c.stream>>>(p, total);
     }
   }
-  count_launch();
+  count_launch("depthwise_generic_kernel");
   return cuda_ok(cudaGetLastError(), "depthwise launch");
 }
 

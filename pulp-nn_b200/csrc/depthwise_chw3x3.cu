@@ -217,7 +217,7 @@ bool launch_mode(Context &c, const Chw3Params &g, dim3 grid, size_t smem)
 {
   if (g.p.sx == 1) depthwise_chw3x3_kernel<MODE, 1><<<grid, 256, smem, c.stream>>>(g);
   else             depthwise_chw3x3_kernel<MODE, 2><<<grid, 256, smem, c.stream>>>(g);
-  count_launch();
+  count_launch("depthwise_chw3x3_kernel");
   return cuda_ok(cudaGetLastError(), "depthwise_chw3x3 launch");
 }
 

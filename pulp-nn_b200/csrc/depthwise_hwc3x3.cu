@@ -258,7 +258,7 @@ bool launch_s(Context &c, const Hwc3x3Params &g)
 {
   const unsigned blocks = (g.total + 127u) / 128u;
   depthwise_hwc3x3_kernel<MODE, S><<<blocks, 128, 0, c.stream>>>(g);
-  count_launch();
+  count_launch("depthwise_hwc3x3_kernel");
   return cuda_ok(cudaGetLastError(), "depthwise_hwc3x3 launch");
 }
 

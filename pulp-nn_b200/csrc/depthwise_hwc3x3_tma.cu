@@ -657,7 +657,7 @@ bool launch_geo(Context &c, const DepthwiseProblem &p)
   if (!encode_4d(&map_in, p.in, p.C, p.W, p.H, p.B, CI, G::WBOX, G::ROWS_IN)) return false;
   if (!encode_4d(&map_out, p.out, p.C, p.Wo, p.Ho, p.B, CI, G::WT, G::ROWS_OUT)) return false;
   const cudaError_t le = launch_pdl(kern, dim3((unsigned)total), dim3(G::THREADS), G::SMEM, c.stream, map_in, map_out, g);
-  count_launch();
+  count_launch("depthwise_hwc3x3_tma_kernel");
   return cuda_ok(le, "depthwise_hwc3x3_tma launch") && cuda_ok(cudaGetLastError(), "depthwise_hwc3x3_tma launch");
 }
 
@@ -726,7 +726,7 @@ bool launch_chw_geo(Context &c, const DepthwiseProblem &p)
   CUtensorMap map_in;
   if (!encode_4d(&map_in, p.in, p.W, p.H, p.C, p.B, p.W, G::ROWS_IN, G::CT)) return false;
   const cudaError_t le = launch_pdl(kern, dim3((unsigned)total), dim3(G::THREADS), (size_t)smem, c.stream, map_in, g);
-  count_launch();
+  count_launch("depthwise_chw3x3_tma_kernel");
   return cuda_ok(le, "depthwise_chw3x3_tma launch") && cuda_ok(cudaGetLastError(), "depthwise_chw3x3_tma launch");
 }
 

@@ -510,7 +510,7 @@ bool launch_geo(Context &c, const DepthwiseProblem &dw, const ConvProblem &pw)
   const int sms = c.sm_count > 0 ? c.sm_count : 148;
   const int grid = g.units < sms ? g.units : sms;
   const cudaError_t le = launch_pdl(kern, dim3(grid), dim3(G::THREADS), (size_t)G::SMEM, c.stream, map_in, map_w, g);
-  count_launch();
+  count_launch("dwpw_fused_kernel");
   return cuda_ok(le, "dwpw_fused launch") && cuda_ok(cudaGetLastError(), "dwpw_fused launch");
 }
 

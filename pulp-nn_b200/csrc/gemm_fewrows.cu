@@ -97,7 +97,7 @@ bool launch_fr(Context &c, const ConvProblem &p, int M, int K)
     smem_set.set(c.device, (int)smem);
   }
   const cudaError_t le = launch_pdl(kern, dim3((unsigned)((p.Cout + NB - 1) / NB)), dim3(32 * FR_WARPS), smem, c.stream, p, M, K);
-  count_launch();
+  count_launch("gemm_fewrows_kernel");
   return cuda_ok(le, "gemm_fewrows launch") && cuda_ok(cudaGetLastError(), "gemm_fewrows launch");
 }
 

@@ -719,7 +719,7 @@ bool launch_cfg(Context &c, const TcMaps &m, const TcParams &g, int grid)
   // every configuration asks for more than half of an SM's shared memory, so exactly one CTA (and
   // its 512 tensor-memory columns) lives on an SM
   const cudaError_t le = launch_pdl(kern, dim3(grid), dim3(NUM_THREADS), L::TOTAL, c.stream, m.a, m.b, m.out, g);
-  count_launch();
+  count_launch("igemm_tc_kernel");
   return cuda_ok(le, "igemm_tc launch") && cuda_ok(cudaGetLastError(), "igemm_tc launch");
 }
 

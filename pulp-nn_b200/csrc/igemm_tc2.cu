@@ -404,7 +404,7 @@ bool launch_mode2(Context &c, const CUtensorMap &ma, const CUtensorMap &mw, Tc2P
   if (getenv("PULPNN_DEBUG")) fprintf(stderr, "igemm_tc2: %d resident pairs, grid %d, nt %d, stages %d\n",
                                       resident_pairs<MODE>(c, smem), grid, g.nt, g.n_stages);
   const cudaError_t le = cudaLaunchKernelEx(&cfg, kern, ma, mw, g);
-  count_launch();
+  count_launch("igemm_tc2_kernel");
   return cuda_ok(le, "igemm_tc2 launch") && cuda_ok(cudaGetLastError(), "igemm_tc2 launch");
 }
 

@@ -156,7 +156,9 @@ bool ensure_device(Context &c);
 void set_error(int code, const char *fmt, ...);
 bool cuda_ok(cudaError_t e, const char *what);
 void count_launch(unsigned n = 1);
+void count_launch(const char *kernel_name);     // one launch, and remembers which kernel family it was
 unsigned long long thread_launch_count();       // launches made by the calling thread so far
+const char *thread_last_kernel();               // the kernel family of the calling thread's latest named launch
 
 // Programmatic dependent launch. A kernel launched this way may become resident and run its
 // prologue while the previous kernel of the stream is still draining; it must execute pdl_wait()

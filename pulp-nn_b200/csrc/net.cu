@@ -50,6 +50,7 @@ struct pulpnn_net {
   unsigned long long submitted = 0;
   unsigned long long launches_last_run = 0;
   std::vector<char> role_last_run;         // per layer: 0 own kernel, 1 / 2 first / second layer of a fused pair
+  std::vector<const char *> kernel_last_run;   // per layer: the kernel family that ran it
   cudaEvent_t ev_in[2] = {nullptr, nullptr}, ev_done[2] = {nullptr, nullptr};
 };
 
@@ -173,6 +174,7 @@ bool run_device(Context &c, pulpnn_net *net, const uint8_t *din, uint8_t *dout, 
         cur = static_cast<const uint8_t *>(dst);
         cur_buf = other;
         net->role_last_run[l] = 1; net->role_last_run[l + 1] = 2;
+        net->kernel_last_run[l] = net->kernel_last_run[l + 1] = thread_last_kernel();
         l++;
         if (!mark()) return false;         // the pair's time is booked on the depthwise layer, none on the pointwise
         continue;
@@ -181,6 +183,7 @@ bool run_device(Context &c, pulpnn_net *net, const uint8_t *din, uint8_t *dout, 
       net->role_last_run[l] = 0;
       void *dst = dest(l);
       if (!run_layer(c, net, net->layers[l], cur, dst, nb)) return false;
+      net->kernel_last_run[l] = thread_last_kernel();
       cur = static_cast<const uint8_t *>(dst);
     }
   }
@@ -399,6 +402,7 @@ int pulpnn_net_finalize(pulpnn_net_t *net, int micro_batch)
   }
   if (!cuda_ok(cudaStreamCreateWithFlags(&net->copy_stream, cudaStreamNonBlocking), "cudaStreamCreate")) return c.err;
   net->role_last_run.assign(net->layers.size(), 0);
+  net->kernel_last_run.assign(net->layers.size(), "");
   net->finalized = true;
   return PULPNN_OK;
 }
@@ -521,6 +525,12 @@ int pulpnn_net_layer_role(const pulpnn_net_t *net, int layer)
 {
   if (!net || layer < 0 || layer >= (int)net->role_last_run.size()) return -1;
   return net->role_last_run[layer];
+}
+
+const char *pulpnn_net_layer_kernel(const pulpnn_net_t *net, int layer)
+{
+  if (!net || layer < 0 || layer >= (int)net->kernel_last_run.size()) return "";
+  return net->kernel_last_run[layer];
 }
 
 unsigned long long pulpnn_net_launches_per_run(const pulpnn_net_t *net, int n_images)

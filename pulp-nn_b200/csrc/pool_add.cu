@@ -366,7 +366,7 @@ bool launch_avgpool(Context &c, const PoolProblem &p)
   const bool fills_gpu = p.C % 16 == 0 && threads16 >= 32768;      // measured: from batch 512 of a 7x7x1024 pool on
   if (vec && p.kx * p.ky >= 32 && blocks_w < 0x7fffffffLL && !fills_gpu) {
     const cudaError_t le = launch_pdl(avgpool_window_kernel, dim3((unsigned)blocks_w), dim3(256), 0, c.stream, p, chunks);
-    count_launch();
+    count_launch("avgpool_window_kernel");
     return cuda_ok(le, "avgpool launch") && cuda_ok(cudaGetLastError(), "avgpool launch");
   }
   // windows of at least 16 pixels: fewer threads with more bytes in flight each
@@ -375,7 +375,7 @@ bool launch_avgpool(Context &c, const PoolProblem &p)
     const long long total16 = (long long)p.B * p.Ho * p.Wo * CW16;
     const cudaError_t le = launch_pdl(avgpool16_kernel, dim3((unsigned)((total16 + 255) / 256)), dim3(256), 0, c.stream,
                                       p, CW16, total16);
-    count_launch();
+    count_launch("avgpool16_kernel");
     return cuda_ok(le, "avgpool launch") && cuda_ok(cudaGetLastError(), "avgpool launch");
   }
   const int CW = vec ? p.C / 4 : p.C;
