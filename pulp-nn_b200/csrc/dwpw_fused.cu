@@ -1,4 +1,4 @@
-// dwpw_fused.cu -- a 3x3 depthwise layer (HWC input, padding 1, stride 1) and the pointwise layer that
+// dwpw_fused.cu -- a 3x3 depthwise layer (HWC input, padding 1, stride 1 or 2) and the pointwise layer that
 // follows it, in one kernel. The chain being fused is the reference's
 //     pulp_nn_depthwise_generic  -> Im_out  (32bit/src/pulp_nn_depthwise_generic.c:179)
 //     pulp_nn_pointwise_HoWo_parallel <- pInBuffer (32bit/src/pulp_nn_pointwise_HoWo_parallel.c:103)
@@ -45,7 +45,7 @@ using namespace dwregs;
 constexpr int ST_F_TMA = 0x10000, ST_F_BUILD = 0x20000, ST_F_MMA = 0x40000, ST_F_EPI = 0x80000;
 
 // geometry, all compile-time: C input channels, N output channels, patch of TH x TW pixels
-template <int C, int N, int TW, int TH, int BW, int EW, int SRV> struct FG {
+template <int C, int N, int TW, int TH, int BW, int EW, int SRV, int S> struct FG {
   static constexpr int NSRV = SRV;            // TMA warps = MMA warps; they take units in turn
   static constexpr int FIRST_MMA = NSRV, FIRST_BUILD = 2 * NSRV;
   static constexpr int BUILD_WARPS = BW;                      // depthwise builder warps
@@ -62,7 +62,9 @@ template <int C, int N, int TW, int TH, int BW, int EW, int SRV> struct FG {
   static constexpr int WPU = NG * LPC / 32;                   // warps that build one unit
   static constexpr int NBG = BUILD_WARPS / WPU;               // builder groups (units in the making); spare warps idle
   static constexpr int PIX = TW * TH;
-  static constexpr int WBOX = TW + 2, ROWS_IN = TH + 2;
+  static constexpr int WBOX = S == 1 ? TW + 2 : 2 * TW + 1;   // input columns / rows a patch reads (3x3, padding 1)
+  static constexpr int ROWS_IN = S == 1 ? TH + 2 : 2 * TH + 1;
+  static_assert(S == 1 || S == 2, "stride 1 or 2");
   static constexpr int IN_PITCH = WBOX * CI;
   static constexpr int IN_BYTES = ROWS_IN * IN_PITCH;         // one TMA box
   static constexpr int IN_STRIDE = (IN_BYTES + 127) / 128 * 128;
@@ -100,7 +102,7 @@ struct FusedParams {
   uint8_t *out;            // [B][H][W][N]
   const int8_t *w_dw;      // [C][3][3]
   Epilogue e_dw, e_pw;
-  int B, H, W;             // stride 1, padding 1: the output has the input's size
+  int B, H, W;             // OUTPUT rows and columns (the input's size lives in the tensor map)
   int tiles_x, tiles_y, units;
   int ablate;              // measurement only (PULPNN_OPT_TUNE bits 8-10): 1 no stores, 2 no depthwise math, 4 no requantisation
   int *status;
@@ -141,12 +143,12 @@ __device__ __forceinline__ void finalize_to_a(const int (&acc)[4][4], const Quan
   }
 }
 
-template <int MODE, int C, int N, int TW, int TH, int BW, int EW, int SRV>
-__global__ void __launch_bounds__((FG<C, N, TW, TH, BW, EW, SRV>::THREADS), 1)
+template <int MODE, int C, int N, int TW, int TH, int BW, int EW, int SRV, int S>
+__global__ void __launch_bounds__((FG<C, N, TW, TH, BW, EW, SRV, S>::THREADS), 1)
 dwpw_fused_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_constant__ CUtensorMap map_w,
                   const FusedParams g)
 {
-  using G = FG<C, N, TW, TH, BW, EW, SRV>;
+  using G = FG<C, N, TW, TH, BW, EW, SRV, S>;
   constexpr int CI = G::CI;
   constexpr int THREADS = G::THREADS, FIRST_EPI = G::FIRST_EPI, FIRST_BUILD = G::FIRST_BUILD, FIRST_MMA = G::FIRST_MMA;
   constexpr int NSRV = G::NSRV;
@@ -236,9 +238,9 @@ dwpw_fused_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_const
           if (!mbar_wait(&in_empty[s], ph ^ 1, abort_flag, g.status, ST_F_TMA)) { ok = false; break; }
           mbar_arrive_expect_tx(&in_full[s], (uint32_t)G::IN_BYTES);
           if (G::ROW_RUNS)      // whole pixels: a row of the box is one run of (TW+2)*C bytes, in 32-bit elements
-            tma_load_3d(in_ring + s * G::IN_STRIDE, &map_in, &in_full[s], (x0 - 1) * (C / 4), y0 - 1, b);
+            tma_load_3d(in_ring + s * G::IN_STRIDE, &map_in, &in_full[s], (S * x0 - 1) * (C / 4), S * y0 - 1, b);
           else
-            tma_load_4d(in_ring + s * G::IN_STRIDE, &map_in, &in_full[s], ch * CI, x0 - 1, y0 - 1, b);
+            tma_load_4d(in_ring + s * G::IN_STRIDE, &map_in, &in_full[s], ch * CI, S * x0 - 1, S * y0 - 1, b);
           issued++;
         }
       }
@@ -281,7 +283,7 @@ dwpw_fused_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_const
     const int grp = bw / G::WPU, wig = bw - grp * G::WPU;          // group, warp inside the group
     const int c4 = lane % G::LPC, sub = lane / G::LPC, gx = wig * G::NSUB + sub;
     const Rot rot = make_rot<CI>(sub);
-    const uint32_t in_thr = (uint32_t)(4 * gx) * CI + 4u * c4;     // thread's first staged pixel of a row
+    const uint32_t in_thr = (uint32_t)(4 * S * gx) * CI + 4u * c4; // thread's first staged pixel of a row
 
     // the thread's four channels of chunk ch: filter taps and requantisation parameters
     int wa[3][4], wb[3][4], init[4];
@@ -337,25 +339,49 @@ dwpw_fused_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_const
         uint32_t ra[4];
 #pragma unroll
         for (int t = 0; t < 4; t++) ra[t] = ia + CI + rot.off[t];
-        // Staged row ri holds input row y0-1+ri. It is filter row 2 of output row ri-2 (which it
-        // completes), row 1 of output row ri-1 and row 0 of output row ri (which it opens); the three
-        // accumulator sets rotate, at compile time.
-        int acc[3][4][4];
+        if constexpr (S == 1) {
+          // Staged row ri holds input row y0-1+ri. It is filter row 2 of output row ri-2 (which it
+          // completes), row 1 of output row ri-1 and row 0 of output row ri (which it opens); the three
+          // accumulator sets rotate, at compile time.
+          int acc[3][4][4];
 #pragma unroll
-        for (int ri = 0; ri < G::ROWS_IN; ri++) {
-          if (g.ablate & 2) break;
-          unsigned cur[6]; Win1 w;
-          load_row1<CI>(ia, ra, ri * G::IN_PITCH, cur);
-          windows1(cur, rot, w);
-          int (&X)[4][4] = acc[(ri + 1) % 3];     // output row ri-2
-          int (&Y)[4][4] = acc[(ri + 2) % 3];     // output row ri-1
-          int (&Z)[4][4] = acc[ri % 3];           // output row ri
-          if (ri == 0) mac1<false, false, true>(w, wa, wb, init, X, Y, Z);
-          else if (ri == 1) mac1<false, true, true>(w, wa, wb, init, X, Y, Z);
-          else if (ri < TH) mac1<true, true, true>(w, wa, wb, init, X, Y, Z);
-          else if (ri == TH) mac1<true, true, false>(w, wa, wb, init, X, Y, Z);
-          else mac1<true, false, false>(w, wa, wb, init, X, Y, Z);
-          if (ri >= 2) finalize_to_a<MODE, CI>(X, q, ed, k32, slab, (ri - 2) * TW + 4 * gx, c4);
+          for (int ri = 0; ri < G::ROWS_IN; ri++) {
+            if (g.ablate & 2) break;
+            unsigned cur[6]; Win1 w;
+            load_row1<CI>(ia, ra, ri * G::IN_PITCH, cur);
+            windows1(cur, rot, w);
+            int (&X)[4][4] = acc[(ri + 1) % 3];     // output row ri-2
+            int (&Y)[4][4] = acc[(ri + 2) % 3];     // output row ri-1
+            int (&Z)[4][4] = acc[ri % 3];           // output row ri
+            if (ri == 0) mac1<false, false, true>(w, wa, wb, init, X, Y, Z);
+            else if (ri == 1) mac1<false, true, true>(w, wa, wb, init, X, Y, Z);
+            else if (ri < TH) mac1<true, true, true>(w, wa, wb, init, X, Y, Z);
+            else if (ri == TH) mac1<true, true, false>(w, wa, wb, init, X, Y, Z);
+            else mac1<true, false, false>(w, wa, wb, init, X, Y, Z);
+            if (ri >= 2) finalize_to_a<MODE, CI>(X, q, ed, k32, slab, (ri - 2) * TW + 4 * gx, c4);
+          }
+        } else {
+          // Stride 2: staged row ri holds input row 2*y0-1+ri; output row r reads staged rows 2r, 2r+1,
+          // 2r+2 (filter rows 0, 1, 2), and row 2r+2 is also filter row 0 of output row r+1. One
+          // accumulator set; nine staged pixels per row feed four outputs.
+          int acc[4][4];
+          unsigned cur[9]; Win2 w;
+          if (!(g.ablate & 2)) {
+            load_row2<CI>(ia, ra, 0, cur);
+            windows2(cur, rot, w);
+            mac2<true>(w, wa[0], wb[0], init, acc);
+#pragma unroll
+            for (int r = 0; r < TH; r++) {
+              load_row2<CI>(ia, ra, (2 * r + 1) * G::IN_PITCH, cur);
+              windows2(cur, rot, w);
+              mac2<false>(w, wa[1], wb[1], init, acc);
+              load_row2<CI>(ia, ra, (2 * r + 2) * G::IN_PITCH, cur);
+              windows2(cur, rot, w);
+              mac2<false>(w, wa[2], wb[2], init, acc);
+              finalize_to_a<MODE, CI>(acc, q, ed, k32, slab, r * TW + 4 * gx, c4);
+              if (r + 1 < TH) mac2<true>(w, wa[0], wb[0], init, acc);
+            }
+          }
         }
         // the input box has been read: hand the slot back to the TMA warp
         __syncwarp();
@@ -448,17 +474,17 @@ dwpw_fused_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_const
 }
 
 // ---- host side ----------------------------------------------------------------------------------
-template <int MODE, int C, int N, int TW, int TH, int BW, int EW, int SRV>
+template <int MODE, int C, int N, int TW, int TH, int BW, int EW, int SRV, int S = 1>
 bool launch_geo(Context &c, const DepthwiseProblem &dw, const ConvProblem &pw)
 {
-  using G = FG<C, N, TW, TH, BW, EW, SRV>;
+  using G = FG<C, N, TW, TH, BW, EW, SRV, S>;
   EncodeTiledFn enc = encode_tiled_fn();
   FusedParams g;
   g.in = dw.in; g.out = static_cast<uint8_t *>(pw.out); g.w_dw = dw.w;
   g.e_dw = dw.epi; g.e_pw = pw.epi;
-  g.B = dw.B; g.H = dw.H; g.W = dw.W;
-  g.tiles_x = (dw.W + TW - 1) / TW;
-  g.tiles_y = (dw.H + TH - 1) / TH;
+  g.B = dw.B; g.H = dw.Ho; g.W = dw.Wo;
+  g.tiles_x = (dw.Wo + TW - 1) / TW;
+  g.tiles_y = (dw.Ho + TH - 1) / TH;
   const long long units = (long long)dw.B * g.tiles_x * g.tiles_y;
   if (units > 0x7fffffffLL) { set_error(PULPNN_ERR_UNSUPPORTED, "fused depthwise+pointwise: too many tiles"); return false; }
   g.units = (int)units;
@@ -499,7 +525,7 @@ bool launch_geo(Context &c, const DepthwiseProblem &dw, const ConvProblem &pw)
                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { set_error(PULPNN_ERR_CUDA, "cuTensorMapEncodeTiled (fused weights) failed with code %d", (int)r); return false; }
   }
-  auto kern = dwpw_fused_kernel<MODE, C, N, TW, TH, BW, EW, SRV>;
+  auto kern = dwpw_fused_kernel<MODE, C, N, TW, TH, BW, EW, SRV, S>;
   static PerDeviceInt attr_set;
   if (!attr_set.get(c.device)) {
     if (!cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM),
@@ -531,6 +557,7 @@ bool launch_shape(Context &c, const DepthwiseProblem &dw, const ConvProblem &pw)
     return launch_geo<MODE, 128, 128, 28, 4, 14, 8, 1>(c, dw, pw);
   }
   if (C == 256 && N == 256) return launch_geo<MODE, 256, 256, 28, 4, 8, 8, 1>(c, dw, pw);
+  if (C == 64 && N == 128 && dw.sx == 2) return launch_geo<MODE, 64, 128, 16, 8, 8, 8, 1, 2>(c, dw, pw);
   set_error(PULPNN_ERR_UNSUPPORTED, "fused depthwise+pointwise: no kernel for %d -> %d channels", C, N);
   return false;
 }
@@ -539,20 +566,26 @@ bool launch_shape(Context &c, const DepthwiseProblem &dw, const ConvProblem &pw)
 
 bool dwpw_fused_supported(const DepthwiseProblem &dw, const ConvProblem &pw)
 {
-  if (!dw.in_is_hwc || dw.ky != 3 || dw.kx != 3 || dw.pt != 1 || dw.pl != 1 || dw.sx != 1 || dw.sy != 1) return false;
-  if (dw.Ho != dw.H || dw.Wo != dw.W) return false;
+  if (!dw.in_is_hwc || dw.ky != 3 || dw.kx != 3 || dw.pt != 1 || dw.pl != 1 || dw.sx != dw.sy) return false;
+  if (dw.sx != 1 && dw.sx != 2) return false;
+  // the output size of a zero-padded 3x3 convolution with padding 1 on every side
+  if (dw.Ho != (dw.H - 1) / dw.sy + 1 || dw.Wo != (dw.W - 1) / dw.sx + 1) return false;
   if (pw.ky != 1 || pw.kx != 1 || pw.sx != 1 || pw.sy != 1 || pw.pt != 0 || pw.pl != 0) return false;
   if (pw.H != dw.Ho || pw.W != dw.Wo || pw.Ho != pw.H || pw.Wo != pw.W || pw.Cin != dw.C || pw.B != dw.B) return false;
   if (pw.epi.mode != dw.epi.mode || pw.epi.mode == EPI_RAW32) return false;      // one requantisation mode per kernel
   const int C = dw.C, N = pw.Cout;
-  if (!((C == 32 && N == 64) || (C == 128 && N == 128) || (C == 256 && N == 256))) return false;
-  // 256 -> 256 channels: measured on 28 x 28 images, the fused kernel wins up to batch 256 (0.049 ms
-  // against 0.052 ms for the two kernels; 0.027 against 0.030 at batch 128) and loses at batch 1024
-  // (0.171 against 0.165), where the two kernels' larger tiles pay
-  if (C == 256 && (long long)dw.B * dw.H * dw.W > 512LL * 28 * 28) return false;
+  if (dw.sx == 1) {
+    if (!((C == 32 && N == 64) || (C == 128 && N == 128) || (C == 256 && N == 256))) return false;
+    // 256 -> 256 channels: measured on 28 x 28 images, the fused kernel wins up to batch 256 (0.049 ms
+    // against 0.052 ms for the two kernels; 0.027 against 0.030 at batch 128) and loses at batch 1024
+    // (0.171 against 0.165), where the two kernels' larger tiles pay
+    if (C == 256 && (long long)dw.B * dw.H * dw.W > 512LL * 28 * 28) return false;
+  } else {
+    if (!(C == 64 && N == 128)) return false;
+  }
   if ((reinterpret_cast<uintptr_t>(dw.in) & 15) || (reinterpret_cast<uintptr_t>(pw.out) & 31)) return false;
   if ((reinterpret_cast<uintptr_t>(dw.w) & 3) || (reinterpret_cast<uintptr_t>(pw.w) & 15)) return false;
-  if (dw.W < 4 || dw.H < 1 || dw.W > 65535 || dw.H > 65535) return false;
+  if (dw.Wo < 4 || dw.Ho < 1 || dw.W > 65535 || dw.H > 65535) return false;
   return encode_tiled_fn() != nullptr;
 }
 

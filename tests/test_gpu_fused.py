@@ -11,7 +11,7 @@ wl = pulpnn.workloads
 api = pulpnn.api
 
 MODES = [(1, 1), (1, 0), (0, 0), (0, 1), (2, 0)]
-SHAPES = [(32, 64), (128, 128), (256, 256)]
+SHAPES = [(32, 64, 1), (128, 128, 1), (256, 256, 1), (64, 128, 2)]      # ch_in, ch_out, depthwise stride
 
 
 @pytest.fixture(autouse=True)
@@ -21,10 +21,11 @@ def _clean():
     assert api.device_status() == 0, "a bounded wait inside a kernel ran out"
 
 
-def _pair(seed, H, W, C, N, bits, relu, bn, dw_shift=9, pw_shift=None, with_bias=True):
-    dw = wl.depthwise_case(seed, H, W, C, batch=1, bits=bits, out_shift=dw_shift, with_bias=with_bias, out_mult=3,
-                           relu=relu, bn=bn, hwc=True)
-    pw = wl.pointwise_case(seed + 1, H, W, C, N, batch=1, bits=bits,
+def _pair(seed, H, W, C, N, bits, relu, bn, dw_shift=9, pw_shift=None, with_bias=True, stride=1):
+    dw = wl.depthwise_case(seed, H, W, C, strides=(stride, stride), batch=1, bits=bits, out_shift=dw_shift,
+                           with_bias=with_bias, out_mult=3, relu=relu, bn=bn, hwc=True)
+    Ho, Wo = dw["out_hw"]
+    pw = wl.pointwise_case(seed + 1, Ho, Wo, C, N, batch=1, bits=bits,
                            out_shift=(wl.ceil_log2(C) + 4) if pw_shift is None else pw_shift, with_bias=with_bias,
                            out_mult=5, relu=relu, bn=bn)
     return dw, pw
@@ -33,10 +34,12 @@ def _pair(seed, H, W, C, N, bits, relu, bn, dw_shift=9, pw_shift=None, with_bias
 def _net(dw, pw, H, W, C, N, bits, relu, bn, max_batch):
     dt = np.int32 if bits == 32 else np.int64
     net = api.Net(bits, max_batch)
-    net.add_layer(api.LAYER_DEPTHWISE, dim_in=(H, W), ch_in=C, dim_out=(H, W), ch_out=C, kernel=(3, 3),
-                  pads=(1, 1, 1, 1), out_mult=3, out_shift=dw["out_shift"], relu=relu, bn=bn, weights=dw["w"],
-                  bias=dw["bias"], k=np.ascontiguousarray(dw["k"], dt), lam=np.ascontiguousarray(dw["lam"], dt))
-    net.add_layer(api.LAYER_POINTWISE, dim_in=(H, W), ch_in=C, dim_out=(H, W), ch_out=N, out_mult=5,
+    Ho, Wo = dw["out_hw"]
+    net.add_layer(api.LAYER_DEPTHWISE, dim_in=(H, W), ch_in=C, dim_out=(Ho, Wo), ch_out=C, kernel=(3, 3),
+                  pads=(1, 1, 1, 1), strides=dw["strides"], out_mult=3, out_shift=dw["out_shift"], relu=relu, bn=bn,
+                  weights=dw["w"], bias=dw["bias"], k=np.ascontiguousarray(dw["k"], dt),
+                  lam=np.ascontiguousarray(dw["lam"], dt))
+    net.add_layer(api.LAYER_POINTWISE, dim_in=(Ho, Wo), ch_in=C, dim_out=(Ho, Wo), ch_out=N, out_mult=5,
                   out_shift=pw["out_shift"], relu=relu, bn=bn, weights=pw["w"], bias=pw["bias"],
                   k=np.ascontiguousarray(pw["k"], dt), lam=np.ascontiguousarray(pw["lam"], dt))
     net.finalize()
@@ -44,16 +47,18 @@ def _net(dw, pw, H, W, C, N, bits, relu, bn, max_batch):
 
 
 def _chain(cpu, dw, pw, x, bits, relu, bn):
-    H, W = x.shape[1:3]
     t = cpu.depthwise(bits, x, dw["w"], dw["k"], dw["lam"], bias=dw["bias"], out_mult=3, out_shift=dw["out_shift"],
-                      out_hw=(H, W), kernel=(3, 3), pads=(1, 1, 1, 1), strides=(1, 1), relu=relu, bn=bn, in_is_hwc=True)
+                      out_hw=dw["out_hw"], kernel=(3, 3), pads=(1, 1, 1, 1), strides=dw["strides"], relu=relu, bn=bn,
+                      in_is_hwc=True)
     return t, cpu.pointwise(bits, t, pw["w"], pw["k"], pw["lam"], bias=pw["bias"], out_mult=5,
                             out_shift=pw["out_shift"], relu=relu, bn=bn)
 
 
-def _run(net, x, N):
+def _run(net, x, N, out_hw=None):
     import torch
     B, H, W, _ = x.shape
+    if out_hw is not None:
+        H, W = out_hw
     out = torch.zeros((B, H, W, N), dtype=torch.uint8, device="cuda")
     net.run(torch.from_numpy(x).cuda(), out, B)
     api.synchronize()
@@ -62,19 +67,21 @@ def _run(net, x, N):
 
 @pytest.mark.parametrize("bits", [32, 64])
 @pytest.mark.parametrize("relu,bn", MODES)
-@pytest.mark.parametrize("C,N", SHAPES)
-def test_fused_pair_all_modes(C, N, relu, bn, bits, restatement):
+@pytest.mark.parametrize("C,N,stride", SHAPES)
+def test_fused_pair_all_modes(C, N, stride, relu, bn, bits, restatement):
     """Every requantisation mode in both trees, on images that are smaller than a patch, not a
     multiple of it, and several patches wide and high."""
     pulpnn.GpuKernels()
     rng = np.random.default_rng(70 + C)
     for (H, W, B) in ((5, 4, 2), (19, 37, 3), (33, 30, 2)):
-        dw, pw = _pair(71, H, W, C, N, bits, relu, bn)
+        if stride == 2 and W < 8:
+            W = 9
+        dw, pw = _pair(71, H, W, C, N, bits, relu, bn, stride=stride)
         x = rng.integers(0, 256, size=(B, H, W, C), dtype=np.uint8)
         mid, want = _chain(restatement, dw, pw, x, bits, relu, bn)
         net = _net(dw, pw, H, W, C, N, bits, relu, bn, B)
         api.set_option(api.OPT_FUSE_DWPW, 1)
-        got = _run(net, x, N)
+        got = _run(net, x, N, dw["out_hw"])
         # flag_relu = 2 selects different modes in the two layers (the depthwise kernel tests the flag's
         # truth, the pointwise one compares it with 1: 32bit/src/pulp_nn_depthwise_generic.c:171,
         # pulp_nn_matmul.c:178), and a pair whose layers requantise differently is not fused
@@ -82,24 +89,25 @@ def test_fused_pair_all_modes(C, N, relu, bn, bits, restatement):
         assert [net.layer_role(0), net.layer_role(1)] == ([1, 2] if fused else [0, 0]), "unexpected kernel choice"
         assert np.array_equal(got, want), "fused kernel differs from the chain of checker calls (%dx%d)" % (H, W)
         api.set_option(api.OPT_FUSE_DWPW, 0)
-        two = _run(net, x, N)
+        two = _run(net, x, N, dw["out_hw"])
         assert [net.layer_role(0), net.layer_role(1)] == [0, 0]
         assert np.array_equal(two, want)
         net.close()
 
 
-@pytest.mark.parametrize("C,N,H,B", [(32, 64, 112, 24), (128, 128, 56, 40), (256, 256, 28, 96)])
-def test_fused_pair_mobilenet_shapes_many_units(C, N, H, B, restatement, reference32):
-    """MobileNet's own pairs (dw1+pw1, dw3+pw3, dw5+pw5) with many more patches than SMs, live
+@pytest.mark.parametrize("C,N,H,B,stride", [(32, 64, 112, 24, 1), (128, 128, 56, 40, 1), (256, 256, 28, 96, 1),
+                                            (64, 128, 112, 20, 2)])
+def test_fused_pair_mobilenet_shapes_many_units(C, N, H, B, stride, restatement, reference32):
+    """MobileNet's own pairs (dw1+pw1, dw2+pw2, dw3+pw3, dw5+pw5) with many more patches than SMs, live
     requantisation; sampled images also against the reference's own code."""
     pulpnn.GpuKernels()
     rng = np.random.default_rng(72)
-    dw, pw = _pair(73, H, H, C, N, 32, 1, 1, with_bias=False)
+    dw, pw = _pair(73, H, H, C, N, 32, 1, 1, with_bias=False, stride=stride)
     x = rng.integers(0, 256, size=(B, H, H, C), dtype=np.uint8)
     mid, want = _chain(restatement, dw, pw, x, 32, 1, 1)
     assert np.count_nonzero(want) > want.size // 10
     net = _net(dw, pw, H, H, C, N, 32, 1, 1, B)
-    got = _run(net, x, N)
+    got = _run(net, x, N, dw["out_hw"])
     assert net.layer_role(0) == 1
     assert np.array_equal(got, want)
     for sl in (slice(0, 1), slice(B - 1, B)):
@@ -107,7 +115,7 @@ def test_fused_pair_mobilenet_shapes_many_units(C, N, H, B, restatement, referen
         assert np.array_equal(got[sl], ref)
     # the prefix that ends on the depthwise layer cannot be fused and must still be right
     import torch
-    out = torch.zeros((B, H, H, C), dtype=torch.uint8, device="cuda")
+    out = torch.zeros((B,) + tuple(dw["out_hw"]) + (C,), dtype=torch.uint8, device="cuda")
     net.run(torch.from_numpy(x).cuda(), out, B, 1)
     api.synchronize()
     assert np.array_equal(out.cpu().numpy(), mid)
