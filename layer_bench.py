@@ -67,6 +67,16 @@ def build_case(name, B, pkg):
         fn = lambda: call(bits, x, None, None, o, w, None, k, lam, 1, c["out_shift"], H, H, C, Ho, Ho, C,  # noqa: E731
                           3, 3, 1, 1, 1, 1, s, s, 1, 1)
         return fn, 2.0 * B * Ho * Ho * C * 9, B * C * (H * H + Ho * Ho), (x, w, k, lam, o)
+    if name == "net":
+        # MobileNetV1 through the network runner, literal parameters: the device-resident benchmark step
+        # alone (for a launch list of exactly one step's kernels)
+        params = wl.mobilenet_params(seed=4, bits=32, shift_bias=11)
+        net = api.build_mobilenet_v1(params, bits=32, max_batch=B)
+        x = torch.from_numpy(wl.mobilenet_input(100, B)).cuda()
+        o = out((B, 1000), torch.int32)
+        rows = wl.mobilenet_ops_bytes()
+        return ((lambda: net.run(x, o, B)), float(sum(r["ops"] for r in rows)) * B, sum(r["bytes"] for r in rows) * B,
+                (net, x, o))
     if name.startswith("dwpw"):
         # a depthwise layer and the pointwise layer behind it through the network runner: one fused
         # kernel where the library has one (PULPNN_OPT_FUSE_DWPW), else two kernels

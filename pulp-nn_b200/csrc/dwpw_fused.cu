@@ -77,7 +77,12 @@ template <int C, int N, int TW, int TH, int BW, int EW, int SRV, int S> struct F
   // ROWS_IN*(TW+2) pieces of C bytes (the TMA unit works through a box piece by piece, and 32-byte
   // pieces were what bounded the 32-channel kernel).
   static constexpr bool ROW_RUNS = NCHUNK == 1 && WBOX * C / 4 <= 256;
-  static constexpr int NIN = NBG == 1 ? 3 : (NBG * NCHUNK <= 4 ? 4 : 2 * NBG * NCHUNK);   // ring of input boxes
+  static constexpr int NIN_WANT = NBG == 1 ? 3 : (NBG * NCHUNK <= 4 ? 4 : 2 * NBG * NCHUNK);   // ring of input boxes
+  // ... as many as shared memory has room for beside the weights, the A tiles and the parameters
+  static constexpr int NIN_ROOM = (232448 - 4096 - ((N * C + 1023) / 1024 * 1024) - (512 / N > 8 ? 8 : 512 / N) * (C / CI) * 128 * CI -
+                                   N * 16) / ((ROWS_IN * WBOX * CI + 127) / 128 * 128);
+  static constexpr int NIN = NIN_WANT <= NIN_ROOM ? NIN_WANT : (NBG == 1 ? NIN_ROOM : NIN_ROOM / (NBG * NCHUNK) * (NBG * NCHUNK));
+  static_assert(NIN >= 2, "at least two input boxes: one being read, one on its way");
   static constexpr int W_BYTES = N * C;
   static constexpr int PARAM_BYTES = N * 16;                  // k and lambda (up to 8 bytes each) or bias
   static constexpr int W_OFF = 0;
@@ -558,6 +563,7 @@ bool launch_shape(Context &c, const DepthwiseProblem &dw, const ConvProblem &pw)
   }
   if (C == 256 && N == 256) return launch_geo<MODE, 256, 256, 28, 4, 8, 8, 1>(c, dw, pw);
   if (C == 64 && N == 128 && dw.sx == 2) return launch_geo<MODE, 64, 128, 16, 8, 8, 8, 1, 2>(c, dw, pw);
+  if (C == 128 && N == 256 && dw.sx == 2) return launch_geo<MODE, 128, 256, 28, 4, 7, 8, 1, 2>(c, dw, pw);
   set_error(PULPNN_ERR_UNSUPPORTED, "fused depthwise+pointwise: no kernel for %d -> %d channels", C, N);
   return false;
 }
@@ -581,7 +587,7 @@ bool dwpw_fused_supported(const DepthwiseProblem &dw, const ConvProblem &pw)
     // (0.171 against 0.165), where the two kernels' larger tiles pay
     if (C == 256 && (long long)dw.B * dw.H * dw.W > 512LL * 28 * 28) return false;
   } else {
-    if (!(C == 64 && N == 128)) return false;
+    if (!((C == 64 && N == 128) || (C == 128 && N == 256))) return false;
   }
   if ((reinterpret_cast<uintptr_t>(dw.in) & 15) || (reinterpret_cast<uintptr_t>(pw.out) & 31)) return false;
   if ((reinterpret_cast<uintptr_t>(dw.w) & 3) || (reinterpret_cast<uintptr_t>(pw.w) & 15)) return false;

@@ -11,7 +11,7 @@ wl = pulpnn.workloads
 api = pulpnn.api
 
 MODES = [(1, 1), (1, 0), (0, 0), (0, 1), (2, 0)]
-SHAPES = [(32, 64, 1), (128, 128, 1), (256, 256, 1), (64, 128, 2)]      # ch_in, ch_out, depthwise stride
+SHAPES = [(32, 64, 1), (128, 128, 1), (256, 256, 1), (64, 128, 2), (128, 256, 2)]      # ch_in, ch_out, depthwise stride
 
 
 @pytest.fixture(autouse=True)
@@ -96,7 +96,7 @@ def test_fused_pair_all_modes(C, N, stride, relu, bn, bits, restatement):
 
 
 @pytest.mark.parametrize("C,N,H,B,stride", [(32, 64, 112, 24, 1), (128, 128, 56, 40, 1), (256, 256, 28, 96, 1),
-                                            (64, 128, 112, 20, 2)])
+                                            (64, 128, 112, 20, 2), (128, 256, 56, 36, 2)])
 def test_fused_pair_mobilenet_shapes_many_units(C, N, H, B, stride, restatement, reference32):
     """MobileNet's own pairs (dw1+pw1, dw2+pw2, dw3+pw3, dw5+pw5) with many more patches than SMs, live
     requantisation; sampled images also against the reference's own code."""
