@@ -34,12 +34,13 @@ using namespace sm100;
 
 constexpr int ROWS_OUT = 4;        // output rows (= tiles) per unit
 constexpr int NA = 8;              // ring of im2col tiles = ring of accumulators
+constexpr int NU = NA / ROWS_OUT;  // ... handed over a unit (ROWS_OUT tiles) at a time: two units in flight
 constexpr int NIN = 3;             // ring of input-row stages
 constexpr int A_TILE_BYTES = 128 * 64;
 // a warp needs about a thousand cycles to drain its quarter of an accumulator (tcgen05.ld, 32 x
 // requantise, store: one dependent chain), so four groups keep four tiles in flight
 constexpr int BUILD_WARPS = 4, MMA_WARPS = 2, EPI_GROUP_WARPS = 4, EPI_GROUPS_N = 2;
-static_assert(NA % EPI_GROUPS_N == 0 && NA % MMA_WARPS == 0, "a ring slot must always meet the same warps");
+static_assert(NA % ROWS_OUT == 0 && NU % EPI_GROUPS_N == 0 && NU % MMA_WARPS == 0, "a ring slot must always meet the same warps");
 constexpr int FIRST_BUILD = 1, FIRST_MMA = FIRST_BUILD + BUILD_WARPS, FIRST_EPILOGUE = FIRST_MMA + MMA_WARPS;
 constexpr int THREADS = 32 * (FIRST_EPILOGUE + EPI_GROUP_WARPS * EPI_GROUPS_N);
 constexpr int ST_C1_TMA = 0x1000, ST_C1_BUILD = 0x2000, ST_C1_MMA = 0x4000, ST_C1_EPI = 0x8000;
@@ -92,7 +93,8 @@ conv_smallcin_tc_kernel(const __grid_constant__ CUtensorMap map_in, const SmallT
 
   if (tid == 0) {
     for (int s = 0; s < NIN; s++) { mbar_init(&in_full[s], 1); mbar_init(&in_empty[s], BUILD_WARPS); }
-    for (int s = 0; s < NA; s++) {
+    // the im2col tiles and the accumulators are handed over a UNIT (four tiles) at a time: slot = unit % NU
+    for (int s = 0; s < NU; s++) {
       mbar_init(&a_full[s], BUILD_WARPS); mbar_init(&a_empty[s], 1);
       mbar_init(&t_full[s], 1); mbar_init(&t_empty[s], EPI_GROUP_WARPS);
     }
@@ -203,18 +205,20 @@ conv_smallcin_tc_kernel(const __grid_constant__ CUtensorMap map_in, const SmallT
       __syncwarp();
       if (lane == 0) mbar_arrive(&in_empty[s]);            // the stage has been read into registers
       if (++s == NIN) { s = 0; ph ^= 1; }
+      // one hand-over per unit: wait for the unit's four tile slots, fill them, signal once
+      const int us = i % NU;
+      if (!mbar_wait(&a_empty[us], ((uint32_t)(i / NU) & 1u) ^ 1u, abort_flag, g.status, ST_C1_BUILD)) { ok = false; break; }
 #pragma unroll
-      for (int r = 0; r < ROWS_OUT; r++, i++) {
-        const int slot = i % NA;
-        if (!mbar_wait(&a_empty[slot], ((uint32_t)(i / NA) & 1u) ^ 1u, abort_flag, g.status, ST_C1_BUILD)) { ok = false; break; }
-        const uint32_t ta = a_addr + slot * A_TILE_BYTES;
+      for (int r = 0; r < ROWS_OUT; r++) {
+        const uint32_t ta = a_addr + (us * ROWS_OUT + r) * A_TILE_BYTES;
 #pragma unroll
         for (int fy = 0; fy < 3; fy++)
           sts128(ta + swz64(ox, fy), x[r * SY + fy][0], x[r * SY + fy][1], x[r * SY + fy][2], 0u);
-        fence_proxy_async();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&a_full[slot]);
       }
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&a_full[us]);
+      i++;
     }
   } else if (warp < FIRST_EPILOGUE) {
     // ------------------------------ MMA issuers: alternate tiles -------------------------------
@@ -224,21 +228,23 @@ conv_smallcin_tc_kernel(const __grid_constant__ CUtensorMap map_in, const SmallT
       const uint64_t db = umma_smem_desc<64>(smem_u32(w_tile));
       int i = 0;
       bool ok = true;
-      for (int u = blockIdx.x; u < g.units && ok; u += gridDim.x) {
-        for (int r = 0; r < ROWS_OUT; r++, i++) {
-          if ((i & (MMA_WARPS - 1)) != me) continue;
-          const int slot = i % NA;                           // also the accumulator
-          const uint32_t par = (uint32_t)(i / NA) & 1u;
-          if (!mbar_wait(&t_empty[slot], par ^ 1, abort_flag, g.status, ST_C1_MMA)) { ok = false; break; }
-          if (!mbar_wait(&a_full[slot], par, abort_flag, g.status, ST_C1_MMA)) { ok = false; break; }
-          tc_fence_after();
+      for (int u = blockIdx.x; u < g.units && ok; u += gridDim.x, i++) {
+        if ((i & (MMA_WARPS - 1)) != me) continue;
+        const int us = i % NU;                               // the unit's slot: four tiles, four accumulators
+        const uint32_t par = (uint32_t)(i / NU) & 1u;
+        if (!mbar_wait(&t_empty[us], par ^ 1, abort_flag, g.status, ST_C1_MMA)) { ok = false; break; }
+        if (!mbar_wait(&a_full[us], par, abort_flag, g.status, ST_C1_MMA)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int r = 0; r < ROWS_OUT; r++) {
+          const int slot = us * ROWS_OUT + r;
           const uint64_t da = umma_smem_desc<64>(smem_u32(a_ring) + slot * A_TILE_BYTES);
           const uint32_t d = tmem_base + (uint32_t)(slot * BN);
           umma_i8(d, da, db, idesc, 0u);
           umma_i8(d, da + 2, db + 2, idesc, 1u);            // K bytes 32..63: two 16-byte units further
-          umma_commit(&a_empty[slot]);
-          umma_commit(&t_full[slot]);
         }
+        umma_commit(&a_empty[us]);
+        umma_commit(&t_full[us]);
       }
     }
   } else {
@@ -259,13 +265,15 @@ conv_smallcin_tc_kernel(const __grid_constant__ CUtensorMap map_in, const SmallT
     }
     int i = 0;
     bool ok = true;
-    for (int u = blockIdx.x; u < g.units && ok; u += gridDim.x) {
+    for (int u = blockIdx.x; u < g.units && ok; u += gridDim.x, i++) {
+      if ((i & (EPI_GROUPS_N - 1)) != grp) continue;
       const int b = u / g.groups, gy = u - b * g.groups;
-      for (int r = 0; r < ROWS_OUT; r++, i++) {
-        if ((i & (EPI_GROUPS_N - 1)) != grp) continue;
-        const int slot = i % NA;
-        if (!mbar_wait(&t_full[slot], (uint32_t)(i / NA) & 1u, abort_flag, g.status, ST_C1_EPI)) { ok = false; break; }
-        tc_fence_after();
+      const int us = i % NU;
+      if (!mbar_wait(&t_full[us], (uint32_t)(i / NU) & 1u, abort_flag, g.status, ST_C1_EPI)) { ok = false; break; }
+      tc_fence_after();
+#pragma unroll 1
+      for (int r = 0; r < ROWS_OUT; r++) {
+        const int slot = us * ROWS_OUT + r;
         const int oy = gy * ROWS_OUT + r;
         const bool store = ox < p.Wo && oy < p.Ho;
         uint8_t *orow = reinterpret_cast<uint8_t *>(p.out) + (((size_t)b * p.Ho + (store ? oy : 0)) * p.Wo + (store ? ox : 0)) * BN;
@@ -311,10 +319,10 @@ conv_smallcin_tc_kernel(const __grid_constant__ CUtensorMap map_in, const SmallT
                          ::"l"(orow + c0), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
                          : "memory");
         }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&t_empty[slot]);
       }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&t_empty[us]);
     }
   }
 
