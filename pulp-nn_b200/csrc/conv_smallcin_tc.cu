@@ -32,15 +32,17 @@ namespace {
 
 using namespace sm100;
 
-constexpr int ROWS_OUT = 4;        // output rows (= tiles) per unit
-constexpr int NA = 8;              // ring of im2col tiles = ring of accumulators
-constexpr int NU = NA / ROWS_OUT;  // ... handed over a unit (ROWS_OUT tiles) at a time: two units in flight
+// Output rows (= tiles) per unit: the tiles and accumulators are handed from role to role a unit at a
+// time (measured with 32 filters: one hand-over per tile 0.198 ms, per four tiles 0.163 ms), and two
+// units are in flight, so a unit is as many tiles as half of tensor memory holds accumulators for.
+__host__ __device__ constexpr int rows_out_of(int bn) { return bn == 32 ? 8 : 4; }
+constexpr int NU = 2;              // units in flight: ring of 2 * rows_out im2col tiles = ring of accumulators
 constexpr int NIN = 3;             // ring of input-row stages
 constexpr int A_TILE_BYTES = 128 * 64;
 // a warp needs about a thousand cycles to drain its quarter of an accumulator (tcgen05.ld, 32 x
 // requantise, store: one dependent chain), so four groups keep four tiles in flight
 constexpr int BUILD_WARPS = 4, MMA_WARPS = 2, EPI_GROUP_WARPS = 4, EPI_GROUPS_N = 2;
-static_assert(NA % ROWS_OUT == 0 && NU % EPI_GROUPS_N == 0 && NU % MMA_WARPS == 0, "a ring slot must always meet the same warps");
+static_assert(NU % EPI_GROUPS_N == 0 && NU % MMA_WARPS == 0, "a ring slot must always meet the same warps");
 constexpr int FIRST_BUILD = 1, FIRST_MMA = FIRST_BUILD + BUILD_WARPS, FIRST_EPILOGUE = FIRST_MMA + MMA_WARPS;
 constexpr int THREADS = 32 * (FIRST_EPILOGUE + EPI_GROUP_WARPS * EPI_GROUPS_N);
 constexpr int ST_C1_TMA = 0x1000, ST_C1_BUILD = 0x2000, ST_C1_MMA = 0x4000, ST_C1_EPI = 0x8000;
@@ -69,8 +71,9 @@ template <int MODE, int SY, int BN>
 __global__ void __launch_bounds__(THREADS, 1)
 conv_smallcin_tc_kernel(const __grid_constant__ CUtensorMap map_in, const SmallTcParams g)
 {
+  constexpr int ROWS_OUT = rows_out_of(BN), NA = NU * ROWS_OUT;
   constexpr int ROWS_IN = (ROWS_OUT - 1) * SY + 3;
-  constexpr uint32_t TMEM_COLS = NA * BN;                 // 256 or 512: a power of two
+  constexpr uint32_t TMEM_COLS = NA * BN;                 // 512: all of tensor memory
   extern __shared__ uint8_t smem_raw[];
   uint8_t *sm = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint8_t *a_ring = sm;                                   // NA tiles of 128 rows x 64 bytes
@@ -80,10 +83,10 @@ conv_smallcin_tc_kernel(const __grid_constant__ CUtensorMap map_in, const SmallT
   uint64_t *in_full = reinterpret_cast<uint64_t *>(params + BN * 16);
   uint64_t *in_empty = in_full + NIN;
   uint64_t *a_full = in_empty + NIN;
-  uint64_t *a_empty = a_full + NA;
-  uint64_t *t_full = a_empty + NA;
-  uint64_t *t_empty = t_full + NA;
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(t_empty + NA);
+  uint64_t *a_empty = a_full + NU;
+  uint64_t *t_full = a_empty + NU;
+  uint64_t *t_empty = t_full + NU;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(t_empty + NU);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
   const ConvProblem &p = g.p;
@@ -93,7 +96,7 @@ conv_smallcin_tc_kernel(const __grid_constant__ CUtensorMap map_in, const SmallT
 
   if (tid == 0) {
     for (int s = 0; s < NIN; s++) { mbar_init(&in_full[s], 1); mbar_init(&in_empty[s], BUILD_WARPS); }
-    // the im2col tiles and the accumulators are handed over a UNIT (four tiles) at a time: slot = unit % NU
+    // the im2col tiles and the accumulators are handed over a UNIT at a time: slot = unit % NU
     for (int s = 0; s < NU; s++) {
       mbar_init(&a_full[s], BUILD_WARPS); mbar_init(&a_empty[s], 1);
       mbar_init(&t_full[s], 1); mbar_init(&t_empty[s], EPI_GROUP_WARPS);
@@ -335,13 +338,13 @@ conv_smallcin_tc_kernel(const __grid_constant__ CUtensorMap map_in, const SmallT
 }
 
 // ---- host side ----------------------------------------------------------------------------------
-int rows_in_of(int sy) { return (ROWS_OUT - 1) * sy + 3; }
+int rows_in_of(int sy, int bn) { return (rows_out_of(bn) - 1) * sy + 3; }
 
 template <int MODE, int SY, int BN>
 bool launch_cfg(Context &c, const CUtensorMap &map, const SmallTcParams &g)
 {
   auto kern = conv_smallcin_tc_kernel<MODE, SY, BN>;
-  const size_t smem = 1024 + (size_t)NA * A_TILE_BYTES + 4096 + (size_t)NIN * g.stage_bytes + BN * 16 + 512;
+  const size_t smem = 1024 + (size_t)NU * rows_out_of(BN) * A_TILE_BYTES + 4096 + (size_t)NIN * g.stage_bytes + BN * 16 + 512;
   if (!cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
                "cudaFuncSetAttribute(conv_smallcin_tc)"))
     return false;
@@ -371,9 +374,9 @@ bool conv_smallcin_tc_supported(const ConvProblem &p)
   if (p.sx < 1 || p.Wo > 128) return false;
   const long long row_bytes = (long long)p.W * p.Cin;
   if (row_bytes % 16 != 0 || row_bytes / 16 > 256) return false;        // one TMA box spans whole rows
-  if ((long long)rows_in_of(p.sy) * row_bytes > 48 * 1024) return false;
+  if ((long long)rows_in_of(p.sy, p.Cout) * row_bytes > 24 * 1024) return false;
   if ((reinterpret_cast<uintptr_t>(p.in) & 15) || (reinterpret_cast<uintptr_t>(p.out) & 31)) return false;
-  if ((long long)p.B * ((p.Ho + ROWS_OUT - 1) / ROWS_OUT) > 0x7fffffffLL) return false;
+  if ((long long)p.B * ((p.Ho + rows_out_of(p.Cout) - 1) / rows_out_of(p.Cout)) > 0x7fffffffLL) return false;
   return encode_tiled_fn() != nullptr;
 }
 
@@ -382,8 +385,8 @@ bool launch_conv_smallcin_tc(Context &c, const ConvProblem &p)
   SmallTcParams g;
   g.p = p;
   g.row_bytes = p.W * p.Cin;
-  g.stage_bytes = (rows_in_of(p.sy) * g.row_bytes + 127) & ~127;
-  g.groups = (p.Ho + ROWS_OUT - 1) / ROWS_OUT;
+  g.stage_bytes = (rows_in_of(p.sy, p.Cout) * g.row_bytes + 127) & ~127;
+  g.groups = (p.Ho + rows_out_of(p.Cout) - 1) / rows_out_of(p.Cout);
   g.units = p.B * g.groups;
   g.status = ctx_status_word(c);
   if (!g.status) return false;
@@ -393,7 +396,7 @@ bool launch_conv_smallcin_tc(Context &c, const ConvProblem &p)
   CUtensorMap map;
   cuuint64_t dims[4] = {piece, (cuuint64_t)(g.row_bytes / piece), (cuuint64_t)p.H, (cuuint64_t)p.B};
   cuuint64_t strides[3] = {piece, (cuuint64_t)g.row_bytes, (cuuint64_t)p.H * g.row_bytes};
-  cuuint32_t box[4] = {piece, (cuuint32_t)(g.row_bytes / piece), (cuuint32_t)rows_in_of(p.sy), 1};
+  cuuint32_t box[4] = {piece, (cuuint32_t)(g.row_bytes / piece), (cuuint32_t)rows_in_of(p.sy, p.Cout), 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   const CUresult r = encode_tiled_fn()(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<uint8_t *>(p.in), dims, strides, box,
                                        estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
