@@ -216,6 +216,38 @@ def run_case(name, B, reps, pkg, graph=False):
             "timed": "graph replay" if graph else "calls", "algorithmic_bytes": int(nbytes), "working_set_larger_than_L2": bool(nbytes > 126e6)}
 
 
+def print_trace(pkg):
+    """clock64 stamps of CTA 0's roles per tile, and globaltimer stamps of its stations per launch."""
+    import ctypes
+    import numpy as np
+    lib = pkg.load_library()
+    if not hasattr(lib, "pulpnn_trace_read"):
+        raise SystemExit("the library was built without -DPULPNN_TRACE")
+    t = np.zeros((3, 64, 8), dtype=np.int64)
+    lib.pulpnn_trace_read(t.ctypes.data_as(ctypes.c_void_p), t.size)
+    names = {0: ["empty_seen", "load_issued"],
+             1: ["start", "acc_free", "slab0", "slab1", "slab2", "slab3", "committed"],
+             2: ["enter", "acc_full", "acc_returned", "round0_barrier", "round0_stored", "round1_barrier", "round1_stored"]}
+    role_names = ["producer warp 0", "MMA warps", "epilogue warp 0"]
+    base = t[1, 4, 0]
+    for tile in range(4, 20):
+        for role in (0, 1, 2):
+            print("tile %2d %-16s" % (tile, role_names[role]),
+                  " ".join("%s=%d" % (n, t[role, tile, k] - base) for k, n in enumerate(names[role])))
+    print("cycles from tile to tile (MMA commit):", np.diff(t[1, 4:20, 6]).tolist())
+    k = np.zeros((8, 8), dtype=np.int64)
+    n = ctypes.c_int(0)
+    lib.pulpnn_ktrace_read(k.ctypes.data_as(ctypes.c_void_p), ctypes.byref(n))
+    stations = ["entry", "set up", "previous kernel complete", "first slab landed", "first tile committed",
+                "first accumulator seen", "stores have read", "tensor memory freed"]
+    previous = None
+    for s_ in sorted(range(8), key=lambda i: k[i, 0]):
+        r = k[s_]
+        print("launch: " + ", ".join("%s +%d ns" % (stations[j], r[j] - r[0]) for j in range(1, 8)) +
+              ("" if previous is None else "; entry %+d ns after the previous launch freed its tensor memory" % (r[0] - previous)))
+        previous = r[7]
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--case", default="c2")
@@ -226,6 +258,8 @@ def main():
     ap.add_argument("--split-k", type=int, default=0, help="force this many K-slices in the GEMM (0 = automatic)")
     ap.add_argument("--no-fuse", action="store_true", help="dwpwN cases: two kernels instead of the fused one")
     ap.add_argument("--tune", type=int, default=0, help="experimental kernel configurations (bit mask)")
+    ap.add_argument("--trace", action="store_true",
+                    help="print the per-role timing trace of igemm_tc_kernel (a library built with PULPNN_NVCC_FLAGS=-DPULPNN_TRACE)")
     args = ap.parse_args()
     import torch
     if not torch.cuda.is_available():
@@ -244,6 +278,8 @@ def main():
     for n in names:
         B = args.batch or DEFAULT_BATCH.get(n, 1024)
         print(json.dumps(run_case(n, B, args.reps, pkg, args.graph)), flush=True)
+    if args.trace:
+        print_trace(pkg)
 
 
 if __name__ == "__main__":

@@ -5,8 +5,10 @@ anything: if the shared object is missing, or there is no GPU when a kernel is c
 caller gets an error.
 """
 import ctypes as C
+import hashlib
 import os
 import re
+import shlex
 import shutil
 import subprocess
 from concurrent.futures import ThreadPoolExecutor
@@ -44,20 +46,32 @@ def _newer(target, deps):
 
 
 def build_library(verbose=False, force=False):
-    """Compile every .cu for sm_100a and link the three shared objects (in-tree)."""
+    """Compile every .cu for sm_100a and link the three shared objects (in-tree).
+
+    PULPNN_NVCC_FLAGS in the environment adds compiler flags (e.g. -DPULPNN_TRACE, the timing trace of
+    igemm_tc.cu); such objects are kept apart from the ordinary ones, and the library is relinked
+    whenever the flags differ from those of the library on disk."""
     os.makedirs(LIBDIR, exist_ok=True)
-    os.makedirs(OBJDIR, exist_ok=True)
+    extra = shlex.split(os.environ.get("PULPNN_NVCC_FLAGS", ""))
+    objdir = OBJDIR + ("_" + hashlib.sha1(" ".join(extra).encode()).hexdigest()[:8] if extra else "")
+    os.makedirs(objdir, exist_ok=True)
+    stamp = os.path.join(LIBDIR, "nvcc_flags.txt")
+    previous = open(stamp).read() if os.path.exists(stamp) else ""
+    if previous != " ".join(extra):
+        force_link = True
+    else:
+        force_link = False
     nvcc = _nvcc()
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
     headers += [os.path.join(INCLUDE, f) for f in os.listdir(INCLUDE)]
     sources = [s for s in CU_SOURCES if os.path.exists(os.path.join(CSRC, s))]
 
     def compile_one(src):
-        obj = os.path.join(OBJDIR, src.replace(".cu", ".o"))
+        obj = os.path.join(objdir, src.replace(".cu", ".o"))
         path = os.path.join(CSRC, src)
         if not force and _newer(obj, [path] + headers):
             return obj
-        cmd = [nvcc] + NVCC_FLAGS + ["-c", path, "-o", obj]
+        cmd = [nvcc] + NVCC_FLAGS + extra + ["-c", path, "-o", obj]
         if verbose:
             print(" ".join(cmd), flush=True)
         subprocess.run(cmd, check=True)
@@ -65,11 +79,13 @@ def build_library(verbose=False, force=False):
 
     with ThreadPoolExecutor(max_workers=4) as ex:
         objs = list(ex.map(compile_one, sources))
-    if force or not _newer(MAIN_SO, objs):
+    if force or force_link or not _newer(MAIN_SO, objs):
         cmd = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", MAIN_SO] + objs
         if verbose:
             print(" ".join(cmd), flush=True)
         subprocess.run(cmd, check=True)
+        with open(stamp, "w") as f:
+            f.write(" ".join(extra))
     dropin_src = os.path.join(CSRC, "dropin.c")
     for bits, so in DROPIN_SO.items():
         if force or not _newer(so, [dropin_src, MAIN_SO] + headers):

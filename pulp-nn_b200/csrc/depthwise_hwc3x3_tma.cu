@@ -304,7 +304,9 @@ depthwise_hwc3x3_tma_kernel(const __grid_constant__ CUtensorMap map_in, const __
     if (++grp == RING) { grp = 0; parity ^= 1; }
   }
   if (tid == 0) {
-    bulk_wait_all();
+    // the stores must have read the tile before the CTA's shared memory goes; their writes are
+    // complete when the grid is
+    bulk_wait_read_all();
     if (*abort_flag) {
       // no TMA write may still be in flight when the CTA's shared memory is released
       for (int qn = consumed; qn < issued; qn++) {

@@ -92,7 +92,24 @@ struct TcParams {
   int conv, tw_log2, tiles_x, tiles_y, chunks_per_tap, kx, sx, sy, pl, pt, Ho, Wo;
   int param_period;      // column n takes the per-channel parameters of channel n % param_period (folded rows)
   int *status;
+  int ablate;            // measurement only (PULPNN_OPT_TUNE bits 8-10): 1 no epilogue work, 2 no operand loads, 4 no MMAs
 };
+
+// Timing trace of the first CTA (a build with -DPULPNN_TRACE only: never in the shipped library):
+// role 0 the first producer warp, 1 the MMA warps, 2 the first epilogue warp; clock64 per tile and event.
+#ifdef PULPNN_TRACE
+__device__ long long g_trace[3][64][8];
+#define PULPNN_TRACE_AT(role, tile, ev) \
+  do { if (blockIdx.x == 0 && (tile) < 64) g_trace[role][tile][ev] = clock64(); } while (0)
+// per launch (the last eight): globaltimer at the stations of block 0
+__device__ long long g_ktrace[8][8];
+__device__ int g_klaunch;
+#define PULPNN_KTRACE(ev) \
+  do { if (blockIdx.x == 0) g_ktrace[ktrace_slot & 7][ev] = (long long)global_ns(); } while (0)
+#else
+#define PULPNN_TRACE_AT(role, tile, ev) do {} while (0)
+#define PULPNN_KTRACE(ev) do {} while (0)
+#endif
 
 // m-tile index of a convolution -> image and first output pixel of the patch
 __device__ __forceinline__ void conv_patch(const TcParams &g, int mt, int &b, int &y0, int &x0)
@@ -169,6 +186,13 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 {
   using L = SmemLayout<BN_TILE, TMA_OUT>;
   static_assert(!TMA_OUT || (!PARTIAL && MODE != EPI_RAW32), "TMA stores carry uint8 tiles");
+#ifdef PULPNN_TRACE
+  __shared__ int ktrace_slot_s;
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    ktrace_slot_s = atomicAdd(&g_klaunch, 1);
+    g_ktrace[ktrace_slot_s & 7][0] = (long long)global_ns();
+  }
+#endif
   constexpr int A_BYTES = BM * BKB, B_BYTES = BN_TILE * BKB;
   constexpr int NUM_ACC = L::NUM_ACC;
   constexpr uint32_t TMEM_COLS = 512;
@@ -223,8 +247,13 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+#ifdef PULPNN_TRACE
+  const int ktrace_slot = blockIdx.x == 0 ? ktrace_slot_s : 0;
+#endif
+  if (threadIdx.x == 0) PULPNN_KTRACE(1);
   // everything above overlapped the tail of the previous kernel; nothing below may
   pdl_wait();
+  if (threadIdx.x == 0) PULPNN_KTRACE(2);
   if (threadIdx.x == 0) pdl_launch_dependents();
 
   const int units = g.m_tiles * g.n_tiles * g.k_slices;
@@ -251,7 +280,9 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         for (int s = slab0; s < slab1; s++) {
           if ((st & (NPROD - 1)) == warp) {
             if (!mbar_wait(&empty_bar[st], ph ^ 1, abort_flag, g.status, ST_PRODUCER)) { ok = false; break; }
+            if (warp == 0 && s == slab0) PULPNN_TRACE_AT(0, i, 0);
             uint8_t *a_dst = ring + st * stage_bytes;
+            if (g.ablate & 2) { mbar_arrive(&full_bar[st]); issued_parity[st] = (uint8_t)(1u + ph); goto next_slab; }
             mbar_arrive_expect_tx(&full_bar[st], (uint32_t)stage_bytes);
             if (g.conv) {
               const int tap = s / g.chunks_per_tap, chunk = s - tap * g.chunks_per_tap;
@@ -262,7 +293,9 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             }
             if (!g.w_resident) tma_load_2d(a_dst + A_BYTES, &map_b, &full_bar[st], s * BKB, nt * BN_TILE);
             issued_parity[st] = (uint8_t)(1u + ph);
+            if (warp == 0 && s == slab0) PULPNN_TRACE_AT(0, i, 1);
           }
+        next_slab:
           if (++st == n_stages) { st = 0; ph ^= 1; }
         }
       }
@@ -329,11 +362,15 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         }
         const int acc = i % NUM_ACC;
         const uint32_t acc_phase = (uint32_t)(i / NUM_ACC) & 1u;
+        PULPNN_TRACE_AT(1, i, 0);
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, g.status, ST_MMA_TMEM)) break;
+        PULPNN_TRACE_AT(1, i, 1);
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN_TILE);
         for (int s = slab0; s < slab1; s++) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag, g.status, ST_MMA_FULL)) { ok = false; break; }
+          if (s - slab0 < 4) PULPNN_TRACE_AT(1, i, 2 + s - slab0);
+          if (i == 0 && s == slab0) PULPNN_KTRACE(3);
           if (NMMA > 1 && s == slab1 - 1) *tiles_landed = i + 1;    // the next tile's warp may go ahead
           tc_fence_after();
           const uint32_t a_addr = smem_u32(ring + stage * stage_bytes);
@@ -343,6 +380,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           const int kbytes = min(BKB, g.K - s * BKB);
           const int n_mma = (kbytes + UMMA_K - 1) / UMMA_K;
           for (int j = 0; j < n_mma; j++) {
+            if (g.ablate & 4) break;
             // advancing K inside the swizzle atom = advancing the start address (16-byte units)
             const uint64_t adv = (uint64_t)((j * UMMA_K) >> 4);
             umma_i8(d_tmem, da + adv, db + adv, idesc, (s > slab0 || j > 0) ? 1u : 0u);
@@ -352,6 +390,8 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         }
         if (!ok) break;
         umma_commit(&tmem_full[acc]);          // accumulator complete
+        PULPNN_TRACE_AT(1, i, 6);
+        if (i == 0) PULPNN_KTRACE(4);
       }
     }
   } else {
@@ -423,7 +463,16 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         // requantised bytes of this warp's columns, 8 words per 32-column chunk
         constexpr int NCHUNK = HALF_COLS / 32;
         unsigned w[NCHUNK][8];
+        if (warp == FIRST_EPI && lane == 0) PULPNN_TRACE_AT(2, i, 0);
         if (!dead && !mbar_wait(&tmem_full[acc], acc_phase, abort_flag, g.status, ST_EPILOGUE)) dead = true;
+        if (warp == FIRST_EPI && lane == 0) PULPNN_TRACE_AT(2, i, 1);
+        if (warp == FIRST_EPI && lane == 0 && i == 0) PULPNN_KTRACE(5);
+        if (!dead && (g.ablate & 1)) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+          continue;
+        }
         if (!dead) {
           tc_fence_after();
           const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN_TILE);
@@ -463,6 +512,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+          if (warp == FIRST_EPI && lane == 0) PULPNN_TRACE_AT(2, i, 2);
         }
         // The tile leaves in rounds of at most 128 columns (one round, or two for 256 columns).
         constexpr int ROUNDS = BN_TILE == 256 ? 2 : 1;
@@ -472,6 +522,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           // (A) the previous store from the staging tile has finished reading it
           if (elected) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
           asm volatile("bar.sync %0, %1;" ::"r"(1 + grp), "n"(GROUP_THREADS) : "memory");
+          if (warp == FIRST_EPI && lane == 0) PULPNN_TRACE_AT(2, i, 3 + 2 * rd);
           if (!dead) {
             // row r of the staging tile, 16-byte chunks cc, cc+1 of each 32-column chunk, swizzled
             // the way the TMA store expects (rows of OUT_ROW_BYTES with the matching swizzle): no
@@ -501,6 +552,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             }
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
           }
+          if (warp == FIRST_EPI && lane == 0) PULPNN_TRACE_AT(2, i, 4 + 2 * rd);
         }
         continue;
       }
@@ -599,7 +651,10 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       if (lane == 0) mbar_arrive(&tmem_empty[acc]);
     }
     // the staging tiles must outlive the stores that read them
-    if (TMA_OUT && elected) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    // (only until they have READ it: the writes themselves are complete, and visible to the next kernel
+    // in the stream, when the grid is: no thread of this kernel reads them back)
+    if (TMA_OUT && elected) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+    if (warp == FIRST_EPI && lane == 0) PULPNN_KTRACE(6);
   }
 
   tc_fence_before();
@@ -607,6 +662,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   if (warp == NPROD) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
+    if (lane == 0) PULPNN_KTRACE(7);
   }
 }
 
@@ -890,6 +946,7 @@ bool launch_igemm_tc(Context &c, const ConvProblem &p)
     if (!cuda_ok(cudaMemsetAsync(c.status_word, 0, sizeof(int), c.stream), "cudaMemset(status)")) return false;
   }
   g.status = c.status_word;
+  g.ablate = (c.opt_tune >> 8) & 7;
 
   TcMaps maps;
   const int tw = 1 << g.tw_log2, th = 128 >> g.tw_log2;
@@ -937,6 +994,21 @@ bool launch_igemm_tc(Context &c, const ConvProblem &p)
   count_launch();
   return cuda_ok(cudaGetLastError(), "splitk_reduce launch");
 }
+
+#ifdef PULPNN_TRACE
+}  // namespace pulpnn
+extern "C" int pulpnn_ktrace_read(long long *dst, int *launches)
+{
+  cudaMemcpyFromSymbol(launches, pulpnn::g_klaunch, sizeof(int));
+  return (int)cudaMemcpyFromSymbol(dst, pulpnn::g_ktrace, 64 * sizeof(long long));
+}
+extern "C" int pulpnn_trace_read(long long *dst, int n)
+{
+  if (n > 3 * 64 * 8) n = 3 * 64 * 8;
+  return (int)cudaMemcpyFromSymbol(dst, pulpnn::g_trace, (size_t)n * sizeof(long long));
+}
+namespace pulpnn {
+#endif
 
 // ---- fully connected layer with split K, for callers that must not allocate -------------------
 // The split-K path above parks its per-slice partial sums in device memory that the context

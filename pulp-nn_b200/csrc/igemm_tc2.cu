@@ -54,6 +54,7 @@ struct Tc2Params {
   int row_pairs;          // ceil(M / 256)
   int n_stages;
   int *status;
+  int ablate;             // measurement only (PULPNN_OPT_TUNE bits 8-11): 1 no epilogue work, 2 no loads of A, 4 no MMAs, 8 no stores
 };
 
 // shared-memory layout of one CTA (after 1024-byte alignment)
@@ -211,8 +212,12 @@ igemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const int row = rp * 2 * BM + (int)rank * BM;
         for (int s = 0; s < g.slabs; s++) {
           if (!mbar_wait(&empty_bar[st], ph ^ 1, abort_flag, g.status, ST2_PRODUCER)) { ok = false; break; }
-          if (rank == 0) mbar_arrive_expect_tx(&full_bar[st], (uint32_t)(2 * A_BYTES));
-          tma_load_2d_pair(ring + st * A_BYTES, &map_a, map_to_cta(smem_u32(&full_bar[st]), 0), s * BKB, row);
+          if (g.ablate & 2) {
+            if (rank == 0) mbar_arrive(&full_bar[st]);
+          } else {
+            if (rank == 0) mbar_arrive_expect_tx(&full_bar[st], (uint32_t)(2 * A_BYTES));
+            tma_load_2d_pair(ring + st * A_BYTES, &map_a, map_to_cta(smem_u32(&full_bar[st]), 0), s * BKB, row);
+          }
           issued++;
           if (++st == g.n_stages) { st = 0; ph ^= 1; }
         }
@@ -246,7 +251,7 @@ igemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             const uint64_t db = umma_smem_desc<BKB>(smem_u32(smem + (t * g.slabs + s) * WH_BYTES));
 #pragma unroll
             for (int j = 0; j < BKB / UMMA_K; j++)
-              umma_i8_pair(d, da + (uint64_t)(2 * j), db + (uint64_t)(2 * j), idesc, (s > 0 || j > 0) ? 1u : 0u);
+              if (!(g.ablate & 4)) umma_i8_pair(d, da + (uint64_t)(2 * j), db + (uint64_t)(2 * j), idesc, (s > 0 || j > 0) ? 1u : 0u);
             if (t == g.nt - 1) umma_commit_pair(&empty_bar[st]);       // both producers may refill the stage
             if (++st == g.n_stages) { st = 0; ph ^= 1; }
           }
@@ -278,6 +283,12 @@ igemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           if (!mbar_wait(&tmem_full[acc], ((uint32_t)(i >> 1)) & 1u, abort_flag, g.status, ST2_EPI)) { dead = true; break; }
           tc_fence_after();
           const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN);
+          if (g.ablate & 1) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(tmem_empty_leader0 + (uint32_t)(acc * 8));
+            continue;
+          }
           const int m = row + quad * 32 + lane;
           uint8_t *orow = reinterpret_cast<uint8_t *>(g.out) + (size_t)(m < g.M ? m : 0) * g.N + n_base + t * BN;
           uint32_t vb[NCHUNK][32];
@@ -319,7 +330,7 @@ igemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
               }
               w[j >> 2] = pack4_sat_u8(q[0], q[1], q[2], q[3]);
             }
-            if (m < g.M)
+            if (m < g.M && !(g.ablate & 8))
               asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
                            ::"l"(orow + c0), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
                            : "memory");
@@ -442,6 +453,7 @@ bool launch_igemm_tc2(Context &c, const ConvProblem &p)
   // with several passes the slabs of a tile stay in the ring for all of them
   if (n_stages < (g.nt > 1 ? g.slabs : 2)) { set_error(PULPNN_ERR_UNSUPPORTED, "igemm_tc2: operand ring too small"); return false; }
   g.n_stages = n_stages;
+  g.ablate = (c.opt_tune >> 8) & 15;
   g.status = ctx_status_word(c);
   if (!g.status) return false;
   const Smem2 L = smem2_layout(g.slabs, g.nt, g.n_stages);

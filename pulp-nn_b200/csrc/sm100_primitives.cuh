@@ -60,7 +60,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
   unsigned long long t0 = 0;
   for (unsigned spin = 1;; spin++) {
     if (mbar_try_wait(bar, parity)) return true;
-    __nanosleep(32);      // a waiting warp must not take issue slots from the working ones
     if ((spin & 255u) == 0) {
       if (*abort_flag) return false;
       if (t0 == 0) t0 = global_ns();
