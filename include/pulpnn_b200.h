@@ -73,9 +73,11 @@ enum {
   PULPNN_OPT_FUSE_DWPW = 4,       /* network runner: run a 3x3 stride-1 depthwise layer and   */
                                   /* the pointwise layer behind it as ONE kernel where a      */
                                   /* fused kernel exists (default 1); results are identical   */
-  PULPNN_OPT_TUNE = 5             /* measurement switch, a bit mask (0 = the defaults). Bits 3-4 */
+  PULPNN_OPT_TUNE = 5             /* measurement switch, a bit mask (0 = the defaults). Bits 3-5 */
                                   /* select alternative launch configurations (8: SM-pair GEMM   */
-                                  /* from K = 512 on, 16: no few-rows GEMM); results identical.  */
+                                  /* from K = 512 on, 16: no few-rows GEMM, 32: the 32-channel   */
+                                  /* fused pair with its depthwise sums on the tensor cores);    */
+                                  /* results identical.                                          */
                                   /* Bits 8-11 switch PARTS of the tensor-core kernels off to    */
                                   /* time the rest (epilogue, loads, MMAs, stores): the output   */
                                   /* is then wrong by design. Never set them outside a timing run */

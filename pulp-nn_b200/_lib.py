@@ -26,7 +26,7 @@ DROPIN_SO = {32: os.path.join(LIBDIR, "libpulpnn_b200_32.so"),
 CU_SOURCES = ["context.cu", "conv_generic.cu", "depthwise.cu", "pool_add.cu", "entry_points.cu",
               "igemm_tc.cu", "net.cu", "depthwise_hwc3x3.cu",
               "conv_smallcin.cu", "depthwise_chw3x3.cu", "depthwise_hwc3x3_tma.cu",
-              "conv_smallcin_tc.cu", "layout.cu", "subbyte.cu", "diagnostics.cu", "dwpw_fused.cu", "igemm_tc2.cu", "gemm_fewrows.cu"]
+              "conv_smallcin_tc.cu", "layout.cu", "subbyte.cu", "diagnostics.cu", "dwpw_fused.cu", "igemm_tc2.cu", "gemm_fewrows.cu", "dwpw_tcdw.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC"]
 

@@ -240,6 +240,9 @@ bool launch_depthwise_chw3x3_tma(Context &c, const DepthwiseProblem &p);
 // a 3x3 stride-1 depthwise layer and the pointwise layer behind it in one kernel (dwpw_fused.cu)
 bool dwpw_fused_supported(const DepthwiseProblem &dw, const ConvProblem &pw);
 bool launch_dwpw_fused(Context &c, const DepthwiseProblem &dw, const ConvProblem &pw);
+// the 32 -> 64 channel pair with the depthwise layer on the tensor cores too (dwpw_tcdw.cu)
+bool dwpw_tcdw_supported(const DepthwiseProblem &dw, const ConvProblem &pw);
+bool launch_dwpw_tcdw(Context &c, const DepthwiseProblem &dw, const ConvProblem &pw);
 bool depthwise_chw3x3_supported(const DepthwiseProblem &p);
 bool launch_depthwise_chw3x3(Context &c, const DepthwiseProblem &p);
 int *ctx_status_word(Context &c);               // allocated on first use; nullptr on failure

@@ -122,6 +122,32 @@ def test_fused_pair_mobilenet_shapes_many_units(C, N, H, B, stride, restatement,
     net.close()
 
 
+@pytest.mark.parametrize("bits", [32, 64])
+@pytest.mark.parametrize("relu,bn", [(1, 1), (0, 0), (1, 0)])
+def test_32_channel_pair_has_two_fused_kernels(bits, relu, bn, restatement):
+    """The 32 -> 64 pair runs with its depthwise sums made by the builders' dp4a (the default) or by
+    tensor-core MMAs (PULPNN_OPT_TUNE bit 5): both must equal the chain of checker calls, on images that are
+    not a multiple of the 28 x 16 patch and on more patches than SMs (the tensor-core form takes widths that
+    are a multiple of four pixels)."""
+    pulpnn.GpuKernels()
+    rng = np.random.default_rng(76)
+    try:
+        for (H, W, B) in ((21, 12, 3), (35, 60, 2), (112, 112, 4)):
+            dw, pw = _pair(77, H, W, 32, 64, bits, relu, bn)
+            x = rng.integers(0, 256, size=(B, H, W, 32), dtype=np.uint8)
+            x[0, :3] = 255                      # saturated rows: the largest sums the layer can make
+            _, want = _chain(restatement, dw, pw, x, bits, relu, bn)
+            net = _net(dw, pw, H, W, 32, 64, bits, relu, bn, B)
+            for tune, kernel in ((32, "dwpw_tcdw_kernel"), (0, "dwpw_fused_kernel")):
+                api.set_option(api.OPT_TUNE, tune)
+                got = _run(net, x, 64)
+                assert net.layer_kernel(0) == kernel
+                assert np.array_equal(got, want), "%s differs from the checker (%dx%d)" % (kernel, H, W)
+            net.close()
+    finally:
+        api.set_option(api.OPT_TUNE, 0)
+
+
 def test_mixed_modes_fall_back_to_two_kernels(restatement):
     """A pair whose layers requantise differently has no fused kernel: the runner must use two."""
     pulpnn.GpuKernels()
