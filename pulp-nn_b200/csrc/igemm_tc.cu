@@ -473,52 +473,58 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           if (lane == 0) mbar_arrive(&tmem_empty[acc]);
           continue;
         }
-        if (!dead) {
-          tc_fence_after();
-          const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN_TILE);
-#pragma unroll
-          for (int ch = 0; ch < NCHUNK; ch++) {
-            const int lc = ch * 32, c0 = ch * (32 * NSPLIT) + half * 32;
-            uint32_t v[32];
-            tmem_ld_32(t_row + (uint32_t)c0, v);
-            tmem_wait_ld();
-#pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              int q[4];
-              if (MODE == EPI_BN32) {
-                const int4 kk = *reinterpret_cast<const int4 *>(p_k32 + lc + j);
-                const int4 ll = *reinterpret_cast<const int4 *>(p_l32 + lc + j);
-                q[0] = (int)((unsigned)kk.x * v[j + 0] + (unsigned)ll.x) >> e.shift;
-                q[1] = (int)((unsigned)kk.y * v[j + 1] + (unsigned)ll.y) >> e.shift;
-                q[2] = (int)((unsigned)kk.z * v[j + 2] + (unsigned)ll.z) >> e.shift;
-                q[3] = (int)((unsigned)kk.w * v[j + 3] + (unsigned)ll.w) >> e.shift;
-              } else {
-#pragma unroll
-                for (int t = 0; t < 4; t++) {
-                  const int a = (int)v[j + t];
-                  if (MODE == EPI_BN64)
-                    q[t] = (int)((long long)((unsigned long long)p_k64[lc + j + t] * (unsigned long long)(long long)a +
-                                             (unsigned long long)p_l64[lc + j + t]) >> e.shift);
-                  else if (MODE == EPI_MULT)
-                    q[t] = (int)(short)((int)((unsigned)e.out_mult * (unsigned)(a + p_bias[lc + j + t])) >> e.shift);
-                  else
-                    q[t] = (a + p_bias[lc + j + t]) >> e.shift;
-                }
-              }
-              w[ch][j >> 2] = pack4_sat_u8(q[0], q[1], q[2], q[3]);
-            }
-          }
-          // the accumulator is in registers: hand it back to the MMA warps before the stores
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&tmem_empty[acc]);
-          if (warp == FIRST_EPI && lane == 0) PULPNN_TRACE_AT(2, i, 2);
-        }
-        // The tile leaves in rounds of at most 128 columns (one round, or two for 256 columns).
+        // The tile leaves in rounds of at most 128 columns (one round, or two for 256 columns), and a round's
+        // chunks are fetched from tensor memory and requantised right before it: the arithmetic of the NEXT round
+        // (or tile) then runs while the TMA store of this one reads the staging tile, so the wait at (A) finds the
+        // store done (measured on 14x14x512 -> 512: the two rounds used to wait 500-700 cycles each).
         constexpr int ROUNDS = BN_TILE == 256 ? 2 : 1;
         constexpr int CPR = NCHUNK / ROUNDS;                 // 32-column chunks of this warp per round
+        if (!dead) tc_fence_after();
+        const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN_TILE);
 #pragma unroll
         for (int rd = 0; rd < ROUNDS; rd++) {
+          if (!dead) {
+#pragma unroll
+            for (int cr = 0; cr < CPR; cr++) {
+              const int ch = rd * CPR + cr;
+              const int lc = ch * 32, c0 = ch * (32 * NSPLIT) + half * 32;
+              uint32_t v[32];
+              tmem_ld_32(t_row + (uint32_t)c0, v);
+              tmem_wait_ld();
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                int q[4];
+                if (MODE == EPI_BN32) {
+                  const int4 kk = *reinterpret_cast<const int4 *>(p_k32 + lc + j);
+                  const int4 ll = *reinterpret_cast<const int4 *>(p_l32 + lc + j);
+                  q[0] = (int)((unsigned)kk.x * v[j + 0] + (unsigned)ll.x) >> e.shift;
+                  q[1] = (int)((unsigned)kk.y * v[j + 1] + (unsigned)ll.y) >> e.shift;
+                  q[2] = (int)((unsigned)kk.z * v[j + 2] + (unsigned)ll.z) >> e.shift;
+                  q[3] = (int)((unsigned)kk.w * v[j + 3] + (unsigned)ll.w) >> e.shift;
+                } else {
+#pragma unroll
+                  for (int t = 0; t < 4; t++) {
+                    const int a = (int)v[j + t];
+                    if (MODE == EPI_BN64)
+                      q[t] = (int)((long long)((unsigned long long)p_k64[lc + j + t] * (unsigned long long)(long long)a +
+                                               (unsigned long long)p_l64[lc + j + t]) >> e.shift);
+                    else if (MODE == EPI_MULT)
+                      q[t] = (int)(short)((int)((unsigned)e.out_mult * (unsigned)(a + p_bias[lc + j + t])) >> e.shift);
+                    else
+                      q[t] = (a + p_bias[lc + j + t]) >> e.shift;
+                  }
+                }
+                w[ch][j >> 2] = pack4_sat_u8(q[0], q[1], q[2], q[3]);
+              }
+            }
+            if (rd == ROUNDS - 1) {
+              // the accumulator is in registers: hand it back to the MMA warps before the stores
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+              if (warp == FIRST_EPI && lane == 0) PULPNN_TRACE_AT(2, i, 2);
+            }
+          }
           // (A) the previous store from the staging tile has finished reading it
           if (elected) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
           asm volatile("bar.sync %0, %1;" ::"r"(1 + grp), "n"(GROUP_THREADS) : "memory");
