@@ -223,14 +223,21 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   const int m0 = g.stationary ? (int)(blockIdx.x / (unsigned)g.n_tiles) : 0;
   const int m_step = g.stationary ? (int)(gridDim.x / (unsigned)g.n_tiles) : 0;
 
+  // the ring's barriers are set up by one thread each (the set-up is not hidden behind the previous kernel: two
+  // launches of this kernel cannot share an SM), thread 0 only does what its early weight fetch needs
+  if (threadIdx.x >= 32 && threadIdx.x < 32 + MAX_STAGES) {
+    const int s = threadIdx.x - 32;
+    if (s < g.n_stages) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    issued_parity[s] = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
   if (threadIdx.x == 0) {
-    for (int s = 0; s < MAX_STAGES; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
     // an accumulator is free again once every warp that drains it has arrived (see the epilogue)
     for (int b = 0; b < NUM_ACC; b++) { mbar_init(&tmem_full[b], 1); mbar_init(&tmem_empty[b], BN_TILE == 256 ? 16 : 8); }
     mbar_init(wres_bar, 1);
     *abort_flag = 0;
     *tiles_landed = 0;
-    for (int s = 0; s < MAX_STAGES; s++) issued_parity[s] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     // The resident slice of W is fetched right away, before the wait on the previous kernel:
